@@ -1,0 +1,246 @@
+"""ctypes front end of the CPU oracle (``oracle/argus_oracle.cpp``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by the smoke check and by the benchmark's
+CPU-baseline leg. The shipped package never imports it.
+
+Each wrapper takes/returns numpy arrays; shapes and strides follow the reference's conventions
+(K/V HeadMajor ``[Hkv, cap, D]`` or SeqMajor ``[T, Hkv, D]``; see the C++ file for the reference
+lines each function restates).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libargus_oracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside it (g++ only; a few seconds)."""
+    src = os.path.join(_HERE, "argus_oracle.cpp")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "libargus_oracle.so"], stdout=subprocess.DEVNULL)
+    return _SO
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        _lib = C.CDLL(_SO)
+        _lib.orc_kivi_new.restype = C.c_void_p
+        for n in ("orc_kivi_q_tokens", "orc_kivi_res_tokens", "orc_kivi_qk_bytes", "orc_kivi_qv_bytes",
+                  "orc_keep_top_k", "orc_h2o_keep"):
+            getattr(_lib, n).restype = C.c_long
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().orc_f32_to_f16(_p(x), _p(out), C.c_long(x.size))
+    return out
+
+
+def lcg(n: int, seed: int) -> np.ndarray:
+    out = np.empty(n, dtype=np.float32)
+    lib().orc_lcg_gen(_p(out), C.c_long(n), C.c_uint32(seed))
+    return out
+
+
+def _kv_args(k: np.ndarray, head_major: bool, hkv: int, d: int):
+    """Element strides (head_stride, pos_stride) for a contiguous K/V array."""
+    if head_major:  # [Hkv, cap, D]
+        cap = k.shape[-2]
+        return cap * d, d
+    return d, hkv * d  # [T, Hkv, D]
+
+
+def attention_gen(q, k, v, hq, hkv, d, T, head_major=True, want_scores=False, score_stride=None,
+                  guards=False, avx2=False, n_threads=0):
+    """Single-query GQA decode. k/v: float32 or uint16 (F16 bits). Returns (out[hq,d], scores|None)."""
+    q = _f32(q).reshape(hq, d)
+    is_f16 = k.dtype == np.uint16 or k.dtype == np.float16
+    k = np.ascontiguousarray(k)
+    v = np.ascontiguousarray(v)
+    hs, ps = _kv_args(k, head_major, hkv, d)
+    out = np.zeros((hq, d), dtype=np.float32)
+    scores = None
+    stride = 0
+    if want_scores:
+        stride = int(score_stride or T)
+        scores = np.zeros((hq, stride), dtype=np.float32)
+    if avx2:
+        rc = lib().orc_attention_gen_avx2(_p(q), _p(k), _p(v), int(is_f16), _p(out), hq, hkv, d, C.c_long(T),
+                                          C.c_long(hs), C.c_long(ps), _p(scores), C.c_long(stride),
+                                          int(n_threads))
+    else:
+        rc = lib().orc_attention_gen(_p(q), _p(k), _p(v), int(is_f16), _p(out), hq, hkv, d, C.c_long(T),
+                                     C.c_long(hs), C.c_long(ps), _p(scores), C.c_long(stride), int(guards))
+    if rc != 0:
+        raise ValueError("oracle attention_gen rejected the arguments")
+    return out, scores
+
+
+def flash_prefill(q, k, v, hq, hkv, S, T, d, cap, head_major=True, br=32, bc=32, window=0,
+                  bh_range=None, n_threads=0):
+    """Causal GQA prefill. q: [B,S,Hq,D] f32; k/v f32 [B,Hkv,cap,D] (HeadMajor) or [B,cap,Hkv,D]."""
+    q = _f32(q)
+    k = _f32(k)
+    v = _f32(v)
+    B = q.shape[0]
+    out = np.zeros_like(q)
+    b0, b1 = bh_range if bh_range else (0, 0)
+    rc = lib().orc_flash_prefill(_p(q), _p(k), _p(v), _p(out), B, hq, hkv, C.c_long(S), C.c_long(T), d,
+                                 C.c_long(cap), int(head_major), br, bc, C.c_long(window), C.c_long(b0),
+                                 C.c_long(b1), int(n_threads))
+    if rc != 0:
+        raise ValueError("oracle flash_prefill rejected the arguments")
+    return out
+
+
+def block_bytes(bits: int) -> int:
+    return int(lib().orc_kv_block_bytes(bits))
+
+
+def kv_quantize(x: np.ndarray, bits: int) -> np.ndarray:
+    x = _f32(x).reshape(-1)
+    assert x.size % 32 == 0
+    nb = x.size // 32
+    out = np.zeros(nb * block_bytes(bits), dtype=np.uint8)
+    assert lib().orc_kv_quantize(_p(x), C.c_long(nb), bits, _p(out)) == 0
+    return out
+
+
+def kv_dequantize(blocks: np.ndarray, bits: int) -> np.ndarray:
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    nb = blocks.size // block_bytes(bits)
+    out = np.zeros(nb * 32, dtype=np.float32)
+    assert lib().orc_kv_dequantize(_p(blocks), C.c_long(nb), bits, _p(out)) == 0
+    return out
+
+
+class KiviCache:
+    """Restated quantized recent-window container (ring + flush + view)."""
+
+    def __init__(self, hkv: int, d: int, res_cap: int, bits: int):
+        self.hkv, self.d, self.res_cap, self.bits = hkv, d, res_cap, bits
+        self._h = C.c_void_p(lib().orc_kivi_new(hkv, d, res_cap, bits))
+        if not self._h:
+            raise ValueError("bad KIVI geometry")
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().orc_kivi_free(self._h)
+            self._h = None
+
+    def update(self, new_k: np.ndarray, new_v: np.ndarray) -> None:
+        new_k = _f32(new_k).reshape(-1, self.hkv, self.d)
+        new_v = _f32(new_v).reshape(-1, self.hkv, self.d)
+        lib().orc_kivi_update(self._h, _p(new_k), _p(new_v), C.c_long(new_k.shape[0]))
+
+    @property
+    def q_tokens(self) -> int:
+        return int(lib().orc_kivi_q_tokens(self._h))
+
+    @property
+    def res_tokens(self) -> int:
+        return int(lib().orc_kivi_res_tokens(self._h))
+
+    def export(self):
+        """(qk bytes, qv bytes, res_k [Hkv,res_cap,D], res_v) as the device kernels index them."""
+        qk = np.zeros(int(lib().orc_kivi_qk_bytes(self._h)), dtype=np.uint8)
+        qv = np.zeros(int(lib().orc_kivi_qv_bytes(self._h)), dtype=np.uint8)
+        rk = np.zeros((self.hkv, self.res_cap, self.d), dtype=np.float32)
+        rv = np.zeros_like(rk)
+        lib().orc_kivi_export(self._h, _p(qk), _p(qv), _p(rk), _p(rv))
+        return qk, qv, rk, rv
+
+
+def kivi_assemble_view(qk, qv, res_k, res_v, hkv, d, res_cap, bits, q_tokens, res_tokens):
+    """F32 SeqMajor [T,Hkv,D] K and V views from raw container buffers."""
+    T = q_tokens + res_tokens
+    vk = np.zeros((T, hkv, d), dtype=np.float32)
+    vv = np.zeros((T, hkv, d), dtype=np.float32)
+    qk = np.ascontiguousarray(qk, dtype=np.uint8)
+    qv = np.ascontiguousarray(qv, dtype=np.uint8)
+    res_k = _f32(res_k)
+    res_v = _f32(res_v)
+    rc = lib().orc_kivi_assemble_view(_p(qk), _p(qv), _p(res_k), _p(res_v), hkv, d, res_cap, bits,
+                                      C.c_long(q_tokens), C.c_long(res_tokens), _p(vk), _p(vv))
+    assert rc == 0
+    return vk, vv
+
+
+def score_accumulate_layer(scores, T, hq, hkv, max_seq, step_flat, step_head, score_offset=0):
+    scores = _f32(scores)
+    stride = scores.shape[-1]
+    lib().orc_score_accumulate_layer(_p(scores), C.c_long(stride), C.c_long(T), hq, hkv,
+                                     C.c_long(score_offset), C.c_long(max_seq), _p(step_flat), _p(step_head))
+
+
+def score_begin_step(importance, head_importance, step_flat, step_head, hkv, max_seq, decay):
+    lib().orc_score_begin_step(_p(importance), _p(head_importance), _p(step_flat), _p(step_head), hkv,
+                               C.c_long(max_seq), C.c_float(decay))
+
+
+def score_end_step(importance, head_importance, step_flat, step_head, hkv, max_seq):
+    lib().orc_score_end_step(_p(importance), _p(head_importance), _p(step_flat), _p(step_head), hkv,
+                             C.c_long(max_seq))
+
+
+def score_fused_reduce(scores, importance, head_importance, decay_factor, n_layers, hq, hkv, T,
+                       score_stride, max_seq):
+    scores = _f32(scores)
+    lib().orc_score_fused_reduce(_p(scores), _p(importance), _p(head_importance), C.c_float(decay_factor),
+                                 n_layers, hq, hkv, C.c_long(T), C.c_long(score_stride), C.c_long(max_seq))
+
+
+def score_reduce_per_layer(scores, layer_flat, decay_factor, n_layers, hq, T, score_stride, max_seq):
+    scores = _f32(scores)
+    lib().orc_score_reduce_per_layer(_p(scores), _p(layer_flat), C.c_float(decay_factor), n_layers, hq,
+                                     C.c_long(T), C.c_long(score_stride), C.c_long(max_seq))
+
+
+def keep_top_k(current, prefix, recent, heavy, score=None):
+    keep = np.zeros(max(current, 1), dtype=np.int64)
+    s = None if score is None else _f32(score)
+    n = lib().orc_keep_top_k(C.c_long(current), C.c_long(prefix), C.c_long(recent), C.c_long(heavy), _p(s),
+                             C.c_long(0 if s is None else s.size), _p(keep))
+    return keep[:n].tolist()
+
+
+def h2o_keep(current, protected_prefix, hh_size, recent_size, score=None):
+    keep = np.zeros(max(current, 1), dtype=np.int64)
+    s = None if score is None else _f32(score)
+    n = lib().orc_h2o_keep(C.c_long(current), C.c_long(protected_prefix), C.c_long(hh_size),
+                           C.c_long(recent_size), _p(s), C.c_long(0 if s is None else s.size), _p(keep))
+    return None if n < 0 else keep[:n].tolist()
+
+
+def lse_merge(o: np.ndarray, lse: np.ndarray) -> np.ndarray:
+    """o: [n_parts, D] normalised partial outputs, lse: [n_parts]. Returns merged [D]."""
+    o = _f32(o)
+    lse = _f32(lse)
+    out = np.zeros(o.shape[1], dtype=np.float32)
+    lib().orc_lse_merge(_p(o), _p(lse), o.shape[0], o.shape[1], _p(out))
+    return out
