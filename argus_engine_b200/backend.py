@@ -1,0 +1,125 @@
+"""Host-side mirror of the reference's attention entry points over the C ABI.
+
+Method names, argument order and error behaviour follow ``trait Backend`` of the reference
+(engine/src/backend.rs:284-295 ``attention_gen``, :1011-1027 ``flash_attention_prefill``), so the parity
+tests read like the reference's own. torch is used only as the owner of device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from ._lib import ArgusB200Error, DecodeExtrasC, Seq, load_library
+
+KV_F32, KV_F16 = 0, 1
+
+
+@dataclass
+class DecodeExtras:
+    """Optional outputs of a decode call (see ``argus_b200_decode_extras`` in the C header)."""
+    scores: Optional[torch.Tensor] = None        # [B, Hq, stride] f32 device
+    head_scores: Optional[torch.Tensor] = None   # [B, Hkv, stride] f32 device
+    flat_scores: Optional[torch.Tensor] = None   # [B, stride] f32 device
+    lse: Optional[torch.Tensor] = None           # [B, Hq] f32 device
+    scores_host: Optional[torch.Tensor] = None   # [B, Hq, stride] f32 host (blocking read-back)
+    score_stride: int = 0
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class B200Backend:
+    """One per device; owns the library context (split-KV scratch)."""
+
+    def __init__(self, device: int = 0, workspace_bytes: int = 0):
+        self._lib = load_library()
+        if not torch.cuda.is_available():
+            raise RuntimeError("argus_engine_b200 needs a CUDA device (there is no CPU fallback)")
+        torch.cuda.set_device(device)
+        torch.cuda.init()
+        h = C.c_void_p()
+        rc = self._lib.argus_b200_create(device, workspace_bytes, C.byref(h))
+        if rc != 0:
+            raise ArgusB200Error(rc, "argus_b200_create failed (is this an sm_100 device?)")
+        self._h = h
+        self.device = device
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.argus_b200_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ── helpers ──
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise ArgusB200Error(rc, self._lib.argus_b200_last_error(self._h).decode())
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.argus_b200_launch_count(self._h))
+
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    @staticmethod
+    def _extras(ex: Optional[DecodeExtras]):
+        if ex is None:
+            return None
+        c = DecodeExtrasC(_ptr(ex.scores), _ptr(ex.head_scores), _ptr(ex.flat_scores), _ptr(ex.lse),
+                          _ptr(ex.scores_host), int(ex.score_stride))
+        return C.byref(c)
+
+    @staticmethod
+    def kv_strides(k_cache: torch.Tensor, num_heads_kv: int):
+        """(head_stride, pos_stride, is_head_major) by the reference's shape rule
+        (engine/src/backend.rs:336-339): HeadMajor iff rank>=3, shape[-3]==Hkv and shape[-3]!=shape[-2]."""
+        shp = k_cache.shape
+        d = shp[-1]
+        if len(shp) >= 3 and shp[-3] == num_heads_kv and shp[-3] != shp[-2]:
+            return shp[-2] * d, d, True
+        return d, num_heads_kv * d, False
+
+    # ── Backend::attention_gen ──
+    def attention_gen(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                      num_heads_q: int, num_heads_kv: int, head_dim: int, cache_seq_len: int,
+                      scores_out: Optional[torch.Tensor] = None, extras: Optional[DecodeExtras] = None) -> None:
+        """q [Hq,D] f32; K/V f16 HeadMajor [Hkv,cap,D] or SeqMajor [T,Hkv,D]; out [Hq,D] f32.
+        ``scores_out``: optional [Hq, stride] tensor (device, or host for the blocking read-back form)."""
+        hs, ps, _ = self.kv_strides(k_cache, num_heads_kv)
+        if scores_out is not None:
+            extras = extras or DecodeExtras()
+            extras.score_stride = scores_out.numel() // num_heads_q
+            if scores_out.is_cuda:
+                extras.scores = scores_out
+            else:
+                extras.scores_host = scores_out
+        dt = KV_F16 if k_cache.dtype == torch.float16 else KV_F32
+        self._check(self._lib.argus_b200_attention_gen(
+            self._h, self._stream(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+            num_heads_q, num_heads_kv, head_dim, cache_seq_len, dt, hs, ps, self._extras(extras)))
+
+    def attention_gen_batched(self, q: torch.Tensor, k_caches: Sequence[torch.Tensor],
+                              v_caches: Sequence[torch.Tensor], seq_lens: Sequence[int], out: torch.Tensor,
+                              num_heads_q: int, num_heads_kv: int, head_dim: int,
+                              extras: Optional[DecodeExtras] = None) -> None:
+        """Independent sequences of different lengths in one launch. q/out [B,Hq,D]."""
+        n = len(k_caches)
+        arr = (Seq * n)()
+        for i in range(n):
+            hs, ps, _ = self.kv_strides(k_caches[i], num_heads_kv)
+            arr[i] = Seq(k_caches[i].data_ptr(), v_caches[i].data_ptr(), int(seq_lens[i]), hs, ps)
+        dt = KV_F16 if k_caches[0].dtype == torch.float16 else KV_F32
+        self._check(self._lib.argus_b200_attention_gen_batched(
+            self._h, self._stream(), q.data_ptr(), arr, n, out.data_ptr(), num_heads_q, num_heads_kv, head_dim, dt,
+            self._extras(extras)))

@@ -1,0 +1,280 @@
+// Host side of the C ABI: context, scratch management, split planning and argument checking.
+//
+// This is the B200-native counterpart of the host code in CudaBackend::attention_gen
+// (engine/src/backend/cuda_pc.rs:1693-1885): pointer/dtype gates, launch shape, score-buffer binding
+// and the blocking score read-back — minus the run-time nvcc step, since kernels are ahead-of-time
+// sm_100a code, and with a split-KV plan instead of one CTA per query head.
+#include "context.h"
+
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+
+namespace argus {
+
+void Context::set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(err, sizeof(err), fmt, ap);
+    va_end(ap);
+}
+
+int Context::cuda_fail(cudaError_t e, const char* what) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return ARGUS_B200_E_CUDA;
+}
+
+// Scratch is carved from one allocation made at create time; nothing on the decode path allocates.
+float* Context::scratch(size_t* cursor, size_t bytes) {
+    const size_t at = (*cursor + 255) & ~size_t(255);
+    if (at + bytes > ws_bytes) return nullptr;
+    *cursor = at + bytes;
+    return reinterpret_cast<float*>(ws + at);
+}
+
+// Choose the split length (tokens per CTA) for a batch of sequences. Every (split, KV head) is a CTA;
+// the grid should cover all SMs several times so that ragged sequence tails balance out, while a split
+// stays long enough to amortise the pipeline fill. `cta_tok` is the kernel's token granularity.
+int plan_chunk(const int64_t* lens, int n, int hkv, int cta_tok, int num_sms, int ctas_per_sm, int waves) {
+    int64_t total = 0, longest = 0;
+    for (int i = 0; i < n; ++i) {
+        total += lens[i];
+        longest = std::max(longest, lens[i]);
+    }
+    if (longest <= 0) return cta_tok;
+    const int64_t target_items = std::max<int64_t>(1, (int64_t)num_sms * ctas_per_sm * waves / hkv);
+    int64_t chunk = (total + target_items - 1) / target_items;
+    const int64_t min_chunk = 2 * cta_tok;
+    chunk = std::max(chunk, min_chunk);
+    chunk = ((chunk + cta_tok - 1) / cta_tok) * cta_tok;
+    chunk = std::min<int64_t>(chunk, ((longest + cta_tok - 1) / cta_tok) * cta_tok);
+    return (int)chunk;
+}
+
+static int env_int(const char* name, int dflt) {
+    const char* s = getenv(name);
+    return (s && *s) ? atoi(s) : dflt;
+}
+
+int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_seq* seqs, int n_seqs,
+                     float* out, int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex) {
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    if (!q || !seqs || !out || n_seqs <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || d <= 0) {
+        ctx->set_error("attention_gen: null pointer or bad head counts (hq=%d hkv=%d d=%d n_seqs=%d)", hq, hkv, d, n_seqs);
+        return ARGUS_B200_E_INVALID;
+    }
+    if (n_seqs > kMaxBatch) {
+        ctx->set_error("attention_gen: %d sequences exceed the per-launch maximum of %d", n_seqs, kMaxBatch);
+        return ARGUS_B200_E_INVALID;
+    }
+    const int g = hq / hkv;
+    if (kv_dtype != ARGUS_B200_KV_F16 || (d != 64 && d != 128) || g > kMaxGroup) {
+        ctx->set_error("attention_gen: unsupported (kv_dtype=%d head_dim=%d group=%d)", kv_dtype, d, g);
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) {
+        ctx->set_error("attention_gen: q/out must be 16-byte aligned");
+        return ARGUS_B200_E_INVALID;
+    }
+
+    DecodeBatch bt;
+    memset(&bt, 0, sizeof(bt));
+    int64_t lens[kMaxBatch];
+    int64_t max_len = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+        const argus_b200_seq& s = seqs[i];
+        if (s.seq_len < 0 || s.seq_len > 0x7fffffff - 4096) {
+            ctx->set_error("attention_gen: sequence %d has an invalid length", i);
+            return ARGUS_B200_E_INVALID;
+        }
+        if (s.seq_len > 0) {
+            if (!s.k || !s.v || (reinterpret_cast<uintptr_t>(s.k) & 15) || (reinterpret_cast<uintptr_t>(s.v) & 15) ||
+                (s.head_stride & 7) || (s.pos_stride & 7) || s.pos_stride < d) {
+                ctx->set_error("attention_gen: sequence %d: K/V must be 16-byte aligned with strides that are multiples of 8 elements", i);
+                return ARGUS_B200_E_INVALID;
+            }
+        }
+        bt.k[i] = s.k;
+        bt.v[i] = s.v;
+        bt.head_stride[i] = s.head_stride;
+        bt.pos_stride[i] = s.pos_stride;
+        bt.seq_len[i] = (int32_t)s.seq_len;
+        lens[i] = s.seq_len;
+        max_len = std::max(max_len, s.seq_len);
+    }
+
+    const bool want_scores = ex && (ex->scores || ex->head_scores || ex->flat_scores || ex->scores_host);
+    if (want_scores && ex->score_stride < max_len) {
+        ctx->set_error("attention_gen: score_stride %lld is shorter than the longest sequence %lld",
+                       (long long)(ex ? ex->score_stride : 0), (long long)max_len);
+        return ARGUS_B200_E_INVALID;
+    }
+
+    const int cta_tok = decode_f16_cta_tokens(d);
+    const int waves = env_int("ARGUS_B200_DECODE_WAVES", 4);
+    const int chunk = plan_chunk(lens, n_seqs, hkv, cta_tok, ctx->num_sms, 2, waves);
+    int items = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+        bt.item_start[i] = items;
+        items += std::max<int64_t>(1, (lens[i] + chunk - 1) / chunk);
+    }
+    bt.item_start[n_seqs] = items;
+
+    // scratch carve-up
+    size_t cur = 0;
+    int* tickets = ctx->tickets;  // persistent, zero between calls
+    if ((size_t)n_seqs * hkv > ctx->n_tickets) {
+        ctx->set_error("attention_gen: %d ticket slots needed, %zu available", n_seqs * hkv, ctx->n_tickets);
+        return ARGUS_B200_E_WORKSPACE;
+    }
+    float* part_o = ctx->scratch(&cur, (size_t)items * hkv * 8 * d * sizeof(float));
+    float* part_ml = ctx->scratch(&cur, (size_t)items * hkv * 8 * sizeof(float2));
+    float* lse2 = ctx->scratch(&cur, (size_t)n_seqs * hq * sizeof(float));
+    float* logits = nullptr;
+    int64_t logit_stride = 0;
+    float* scores_dev = ex ? ex->scores : nullptr;
+    if (want_scores) {
+        logit_stride = ex->score_stride;
+        if (scores_dev) {
+            logits = scores_dev;   // probabilities replace the logits in place
+        } else {
+            logits = ctx->scratch(&cur, (size_t)n_seqs * hq * logit_stride * sizeof(float));
+            if (ex->scores_host) scores_dev = logits;
+        }
+    }
+    if (!part_o || !part_ml || !lse2 || (want_scores && !logits)) {
+        ctx->set_error("attention_gen: scratch of %zu bytes is too small for this call", ctx->ws_bytes);
+        return ARGUS_B200_E_WORKSPACE;
+    }
+
+    DecodeParams p;
+    memset(&p, 0, sizeof(p));
+    p.q = q;
+    p.out = out;
+    p.lse = ex ? ex->lse : nullptr;
+    p.n_seqs = n_seqs;
+    p.hq = hq;
+    p.hkv = hkv;
+    p.group = g;
+    p.chunk = chunk;
+    p.scale_log2 = (1.0f / sqrtf((float)d)) * 1.4426950408889634f;
+    p.part_o = part_o;
+    p.part_ml = reinterpret_cast<float2*>(part_ml);
+    p.tickets = tickets;
+    p.logits = logits;
+    p.logit_stride = logit_stride;
+    p.lse2 = lse2;
+
+    cudaError_t e = launch_decode_f16(p, bt, d, items, st);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "decode_f16 launch");
+    ctx->launches += 1;
+
+    if (want_scores) {
+        FinalizeParams f;
+        memset(&f, 0, sizeof(f));
+        f.logits = logits;
+        f.logit_stride = logit_stride;
+        f.lse2 = lse2;
+        f.scores = scores_dev;
+        f.head_scores = ex->head_scores;
+        f.flat_scores = ex->flat_scores;
+        f.score_stride = ex->score_stride;
+        f.n_seqs = n_seqs;
+        f.hq = hq;
+        f.hkv = hkv;
+        f.group = g;
+        for (int i = 0; i < n_seqs; ++i) f.seq_len[i] = bt.seq_len[i];
+        e = launch_finalize_scores(f, (int)max_len, st);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "finalize_scores launch");
+        ctx->launches += 1;
+        if (ex->scores_host) {
+            // Blocking read-back, as the reference does for a host `scores_out`.
+            e = cudaMemcpyAsync(ex->scores_host, scores_dev, (size_t)n_seqs * hq * ex->score_stride * sizeof(float),
+                                cudaMemcpyDeviceToHost, st);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+            if (e != cudaSuccess) return ctx->cuda_fail(e, "score read-back");
+        }
+    }
+    return ARGUS_B200_OK;
+}
+
+}  // namespace argus
+
+using argus::Context;
+
+extern "C" {
+
+int argus_b200_version(void) { return 1; }
+int argus_b200_sm_arch(void) { return 100; }
+
+int argus_b200_create(int device, size_t workspace_bytes, argus_b200_ctx** out) {
+    if (!out) return ARGUS_B200_E_INVALID;
+    *out = nullptr;
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return ARGUS_B200_E_CUDA;
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return ARGUS_B200_E_CUDA;
+    if (prop.major != 10) return ARGUS_B200_E_UNSUPPORTED;   // sm_100a code only
+    Context* c = new Context();
+    c->device = device;
+    c->num_sms = prop.multiProcessorCount;
+    c->ws_bytes = workspace_bytes ? workspace_bytes : (size_t(64) << 20);
+    c->n_tickets = 4096;
+    e = cudaMalloc(&c->ws, c->ws_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&c->tickets, c->n_tickets * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(c->tickets, 0, c->n_tickets * sizeof(int));
+    if (e != cudaSuccess) {
+        if (c->ws) cudaFree(c->ws);
+        if (c->tickets) cudaFree(c->tickets);
+        delete c;
+        return ARGUS_B200_E_CUDA;
+    }
+    *out = reinterpret_cast<argus_b200_ctx*>(c);
+    return ARGUS_B200_OK;
+}
+
+void argus_b200_destroy(argus_b200_ctx* ctx) {
+    Context* c = reinterpret_cast<Context*>(ctx);
+    if (!c) return;
+    cudaFree(c->ws);
+    cudaFree(c->tickets);
+    delete c;
+}
+
+const char* argus_b200_last_error(const argus_b200_ctx* ctx) {
+    return ctx ? reinterpret_cast<const Context*>(ctx)->err : "null context";
+}
+
+uint64_t argus_b200_launch_count(const argus_b200_ctx* ctx) {
+    return ctx ? reinterpret_cast<const Context*>(ctx)->launches : 0;
+}
+
+int argus_b200_attention_gen_batched(argus_b200_ctx* ctx, void* stream, const float* q, const argus_b200_seq* seqs,
+                                     int n_seqs, float* out, int num_heads_q, int num_heads_kv, int head_dim,
+                                     int kv_dtype, const argus_b200_decode_extras* extras) {
+    return argus::decode_f16_entry(reinterpret_cast<Context*>(ctx), static_cast<cudaStream_t>(stream), q, seqs, n_seqs,
+                                   out, num_heads_q, num_heads_kv, head_dim, kv_dtype, extras);
+}
+
+int argus_b200_attention_gen(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_cache,
+                             const void* v_cache, float* out, int num_heads_q, int num_heads_kv, int head_dim,
+                             int64_t cache_seq_len, int kv_dtype, int64_t head_stride, int64_t pos_stride,
+                             const argus_b200_decode_extras* extras) {
+    argus_b200_seq s;
+    s.k = k_cache;
+    s.v = v_cache;
+    s.seq_len = cache_seq_len;
+    s.head_stride = head_stride;
+    s.pos_stride = pos_stride;
+    return argus::decode_f16_entry(reinterpret_cast<Context*>(ctx), static_cast<cudaStream_t>(stream), q, &s, 1, out,
+                                   num_heads_q, num_heads_kv, head_dim, kv_dtype, extras);
+}
+
+}  // extern "C"

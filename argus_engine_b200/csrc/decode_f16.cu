@@ -1,0 +1,348 @@
+// Split-KV GQA decode attention over an F16 KV cache, sm_100a.
+//
+// Stands behind Backend::attention_gen (engine/src/backend.rs:284-295; the CUDA kernel it replaces is
+// attention_gen_f16kv_naive, engine/src/backend/cuda_pc/kernels.cu:471-540). Same math
+// (softmax(q·K^T/sqrt(D))·V per query head, optional post-softmax score export), different shape:
+//
+//  * one CTA per (sequence, KV head, split of the KV sequence) so that every SM streams K/V, and the
+//    whole GQA group of a KV head shares one pass over K/V (the reference re-reads K/V once per query head);
+//  * each warp owns 16-token tiles of its CTA's split and a private STAGES-deep cp.async ring
+//    (128-bit copies, XOR-swizzled rows), so the main loop has no block-wide barrier;
+//  * QK^T and PV run on the tensor cores (mma.sync m16n8k16, F32 accumulate). Rows 0..7 of the A
+//    operand carry the F16 rounding of q (resp. p), rows 8..15 the rounding residual, so both products
+//    keep ~22 bits of q and p although K/V stay F16;
+//  * online softmax in the log2 domain per warp, (max, sum, O) merged across warps in shared memory,
+//    across splits by the last CTA to arrive at a per-(sequence, KV head) ticket.
+//
+// Score export writes the scaled logits; finalize_scores_kernel turns them into probabilities once the
+// global log-sum-exp is known.
+#include "decode_params.h"
+#include "ptx.cuh"
+
+namespace argus {
+
+template <int D, int WARPS, int STAGES>
+struct DecodeF16Cfg {
+    static constexpr int WT = 16;                 // tokens per warp tile
+    static constexpr int ROW_B = D * 2;           // bytes per K/V row
+    static constexpr int CH = D / 8;              // 16-byte chunks per row
+    static constexpr int TILE_B = WT * ROW_B;     // one K (or V) tile
+    static constexpr int STAGE_B = 2 * TILE_B;    // K tile + V tile
+    static constexpr int PIPE_B = WARPS * STAGES * STAGE_B;
+    static constexpr int MERGE_B = WARPS * 8 * D * 4 + WARPS * 8 * 8 + 128;
+    static constexpr int SMEM_B = PIPE_B > MERGE_B ? PIPE_B : MERGE_B;
+    static constexpr int CTA_TOK = WARPS * WT;    // tokens consumed per CTA sweep
+};
+
+template <int D, int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, 2)
+decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ DecodeBatch bt) {
+    using Cfg = DecodeF16Cfg<D, WARPS, STAGES>;
+    constexpr int WT = Cfg::WT, ROW_B = Cfg::ROW_B, CH = Cfg::CH, TILE_B = Cfg::TILE_B, STAGE_B = Cfg::STAGE_B;
+    constexpr int KS = D / 16;   // k-steps of QK^T
+    constexpr int NT = D / 8;    // n-tiles of PV
+    extern __shared__ __align__(128) uint8_t smem[];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int quad = lane >> 2, qlane = lane & 3;
+
+    // ── which item ──
+    const int kv = blockIdx.x % p.hkv;
+    const int gs = blockIdx.x / p.hkv;
+    int b = 0;
+    while (b + 1 < p.n_seqs && bt.item_start[b + 1] <= gs) ++b;
+    const int split = gs - bt.item_start[b];
+    const int n_splits = bt.item_start[b + 1] - bt.item_start[b];
+    const int T = bt.seq_len[b];
+    const int t0 = split * p.chunk;
+    const int t1 = min(t0 + p.chunk, T);
+    const int n_tiles = t1 > t0 ? (t1 - t0 + WT - 1) / WT : 0;
+    const int my_tiles = warp < n_tiles ? (n_tiles - warp + WARPS - 1) / WARPS : 0;
+
+    const __half* kbase = static_cast<const __half*>(bt.k[b]) + (int64_t)kv * bt.head_stride[b];
+    const __half* vbase = static_cast<const __half*>(bt.v[b]) + (int64_t)kv * bt.head_stride[b];
+    const int64_t pos_stride = bt.pos_stride[b];
+    const uint32_t wsm = smem_u32(smem) + warp * STAGES * STAGE_B;
+
+    auto issue = [&](int j, int slot) {
+        const int tokb = t0 + (warp + j * WARPS) * WT;
+        const uint32_t sb = wsm + slot * STAGE_B;
+#pragma unroll
+        for (int i = 0; i < (WT * CH) / 32; ++i) {
+            const int id = lane + 32 * i;
+            const int row = id / CH, c = id % CH;
+            const int tok = tokb + row;
+            const bool ok = tok < t1;
+            const int64_t off = (int64_t)(ok ? tok : t0) * pos_stride + c * 8;
+            const uint32_t dst = sb + row * ROW_B + ((c ^ (row & 7)) << 4);
+            cp_async16(dst, kbase + off, ok);
+            cp_async16(dst + TILE_B, vbase + off, ok);
+        }
+    };
+
+    // ── prologue: start the ring, then fetch q while the copies fly ──
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < my_tiles) issue(s, s);
+        cp_async_commit();
+    }
+
+    // A-operand fragments of q*scale*log2(e): rows 0..7 = F16 rounding, rows 8..15 = residual.
+    const int head = kv * p.group + quad;          // query head of this lane's MMA row
+    const bool head_ok = quad < p.group;
+    uint32_t qf[KS][4];
+    {
+        const float* qp = p.q + ((int64_t)b * p.hq + (head_ok ? head : kv * p.group)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int c0 = ks * 16 + hf * 8 + qlane * 2;
+                float2 x = head_ok ? *reinterpret_cast<const float2*>(qp + c0) : make_float2(0.f, 0.f);
+                x.x *= p.scale_log2;
+                x.y *= p.scale_log2;
+                const uint32_t hi = pack_half2(x.x, x.y);
+                const float2 hif = unpack_half2(hi);
+                qf[ks][hf * 2 + 0] = hi;
+                qf[ks][hf * 2 + 1] = pack_half2(x.x - hif.x, x.y - hif.y);
+            }
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    float* logit_row = nullptr;
+    if (p.logits != nullptr && head_ok) logit_row = p.logits + ((int64_t)b * p.hq + head) * p.logit_stride;
+
+    // ldmatrix lane geometry
+    const int lm_mat = lane >> 3, lm_row = lane & 7;
+    // K (non-transposed): matrices (tok 0-7,k lo) (tok 0-7,k hi) (tok 8-15,k lo) (tok 8-15,k hi)
+    const int k_tok = (lm_mat >> 1) * 8 + lm_row, k_half = lm_mat & 1;
+    // V (transposed): matrices (tok 0-7,chunk j) (tok 8-15,chunk j) (tok 0-7,chunk j+1) (tok 8-15,chunk j+1)
+    const int v_tok = (lm_mat & 1) * 8 + lm_row, v_half = lm_mat >> 1;
+
+    for (int j = 0; j < my_tiles; ++j) {
+        cp_async_wait<STAGES - 2>();
+        __syncwarp();
+        {
+            const int jn = j + STAGES - 1;
+            if (jn < my_tiles) issue(jn, jn % STAGES);
+            cp_async_commit();
+        }
+        const uint32_t sb = wsm + (j % STAGES) * STAGE_B;
+        const int tokb = t0 + (warp + j * WARPS) * WT;
+
+        // S = q · K^T for 16 tokens
+        float c[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t kb[4];
+            ldmatrix_x4(kb, sb + k_tok * ROW_B + ((((ks << 1) | k_half) ^ (k_tok & 7)) << 4));
+            mma_f16_16816(c[0], qf[ks], kb[0], kb[1]);
+            mma_f16_16816(c[1], qf[ks], kb[2], kb[3]);
+        }
+        float s[2][2];
+        float tile_max = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int tok = tokb + n * 8 + qlane * 2 + i;
+                float x = c[n][i] + c[n][i + 2];
+                if (tok >= t1) x = -INFINITY;
+                else if (logit_row != nullptr) logit_row[tok] = x;
+                s[n][i] = x;
+                tile_max = fmaxf(tile_max, x);
+            }
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+        const float m_new = fmaxf(m_run, tile_max);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = fast_exp2(m_run - m_use);   // m_run = -inf -> 0
+        m_run = m_new;
+
+        uint32_t pa[4];
+        float psum = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const float p0 = fast_exp2(s[n][0] - m_use), p1 = fast_exp2(s[n][1] - m_use);
+            psum += p0 + p1;
+            const uint32_t hi = pack_half2(p0, p1);
+            const float2 hif = unpack_half2(hi);
+            pa[n * 2 + 0] = hi;
+            pa[n * 2 + 1] = pack_half2(p0 - hif.x, p1 - hif.y);
+        }
+        l_run = l_run * alpha + psum;
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                o[n][0] *= alpha; o[n][1] *= alpha; o[n][2] *= alpha; o[n][3] *= alpha;
+            }
+        }
+        // O += P · V
+#pragma unroll
+        for (int jn = 0; jn < NT / 2; ++jn) {
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, sb + TILE_B + v_tok * ROW_B + ((((jn << 1) | v_half) ^ (v_tok & 7)) << 4));
+            mma_f16_16816(o[2 * jn], pa, vb[0], vb[1]);
+            mma_f16_16816(o[2 * jn + 1], pa, vb[2], vb[3]);
+        }
+    }
+    cp_async_wait<0>();
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    __syncthreads();   // every warp is done with its ring: the space becomes the merge buffer
+
+    // ── merge the warps of this CTA ──
+    float* sm_o = reinterpret_cast<float*>(smem);                         // [WARPS][8][D]
+    float2* sm_ml = reinterpret_cast<float2*>(smem + WARPS * 8 * D * 4);  // [WARPS][8]
+    int* sm_flag = reinterpret_cast<int*>(smem + WARPS * 8 * D * 4 + WARPS * 8 * 8);
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        float2 v2 = make_float2(o[n][0] + o[n][2], o[n][1] + o[n][3]);
+        *reinterpret_cast<float2*>(sm_o + (warp * 8 + quad) * D + n * 8 + qlane * 2) = v2;
+    }
+    if (qlane == 0) sm_ml[warp * 8 + quad] = make_float2(m_run, l_run);
+    __syncthreads();
+
+    const int64_t item = (int64_t)gs * p.hkv + kv;
+    for (int e = threadIdx.x; e < p.group * D; e += WARPS * 32) {
+        const int h = e / D, d = e % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_ml[w * 8 + h].x);
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float2 ml = sm_ml[w * 8 + h];
+            const float f = fast_exp2(ml.x - Mu);
+            L += f * ml.y;
+            acc += f * sm_o[(w * 8 + h) * D + d];
+        }
+        if (n_splits == 1) {
+            const int64_t oh = (int64_t)b * p.hq + kv * p.group + h;
+            p.out[oh * D + d] = (L > 0.f) ? acc / L : 0.f;
+            if (d == 0) {
+                const float l2 = (L > 0.f) ? M + log2f(L) : -INFINITY;
+                if (p.lse != nullptr) p.lse[oh] = l2 * 0.6931471805599453f;
+                if (p.lse2 != nullptr) p.lse2[oh] = l2;
+            }
+        } else {
+            p.part_o[(item * 8 + h) * D + d] = acc;
+            if (d == 0) p.part_ml[item * 8 + h] = make_float2(M, L);
+        }
+    }
+    if (n_splits == 1) return;
+
+    // ── ticket: the last split of this (sequence, KV head) merges all of them ──
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(&p.tickets[b * p.hkv + kv], 1);
+        *sm_flag = (prev == n_splits - 1);
+    }
+    __syncthreads();
+    if (*sm_flag == 0) return;
+    __threadfence();
+
+    float2* sm_ML = sm_ml;   // reuse: [8] global (max, sum) per head
+    __syncthreads();
+    const int64_t item0 = (int64_t)bt.item_start[b] * p.hkv + kv;   // split s -> item0 + s*Hkv
+    for (int h = warp; h < p.group; h += WARPS) {
+        float M = -INFINITY;
+        for (int s = lane; s < n_splits; s += 32)
+            M = fmaxf(M, __ldcg(&p.part_ml[(item0 + (int64_t)s * p.hkv) * 8 + h]).x);
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+        float L = 0.f;
+        for (int s = lane; s < n_splits; s += 32) {
+            const float2 ml = __ldcg(&p.part_ml[(item0 + (int64_t)s * p.hkv) * 8 + h]);
+            L += fast_exp2(ml.x - Mu) * ml.y;
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) L += __shfl_xor_sync(0xffffffffu, L, sh);
+        if (lane == 0) sm_ML[h] = make_float2(M, L);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < p.group * D; e += WARPS * 32) {
+        const int h = e / D, d = e % D;
+        const float2 ML = sm_ML[h];
+        const float Mu = (ML.x == -INFINITY) ? 0.f : ML.x;
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const int64_t it = item0 + (int64_t)s * p.hkv;
+            const float f = fast_exp2(__ldcg(&p.part_ml[it * 8 + h]).x - Mu);
+            acc += f * __ldcg(&p.part_o[(it * 8 + h) * D + d]);
+        }
+        const int64_t oh = (int64_t)b * p.hq + kv * p.group + h;
+        p.out[oh * D + d] = (ML.y > 0.f) ? acc / ML.y : 0.f;
+        if (d == 0) {
+            const float l2 = (ML.y > 0.f) ? ML.x + log2f(ML.y) : -INFINITY;
+            if (p.lse != nullptr) p.lse[oh] = l2 * 0.6931471805599453f;
+            if (p.lse2 != nullptr) p.lse2[oh] = l2;
+        }
+    }
+    if (threadIdx.x == 0) p.tickets[b * p.hkv + kv] = 0;   // ready for the next call
+}
+
+// p_t = exp2(logit_t - lse2) per query head, plus the GQA reductions of the score policy
+// (crates/techniques/attn-score/src/lib.rs:262-287): flat = sum over heads (h ascending),
+// head[kv] = (sum over the group, r ascending) * (1/g). One thread per (sequence, token).
+__global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_constant__ FinalizeParams f) {
+    const int b = blockIdx.y;
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= f.seq_len[b]) return;
+    const float inv_g = 1.0f / (float)f.group;
+    float flat = 0.f;
+    for (int kv = 0; kv < f.hkv; ++kv) {
+        float gsum = 0.f;
+        for (int r = 0; r < f.group; ++r) {
+            const int64_t h = (int64_t)b * f.hq + kv * f.group + r;
+            const float pr = exp2f(f.logits[h * f.logit_stride + t] - f.lse2[h]);
+            if (f.scores != nullptr) f.scores[h * f.score_stride + t] = pr;
+            gsum += pr;
+            flat += pr;
+        }
+        if (f.head_scores != nullptr) f.head_scores[((int64_t)b * f.hkv + kv) * f.score_stride + t] = gsum * inv_g;
+    }
+    if (f.flat_scores != nullptr) f.flat_scores[(int64_t)b * f.score_stride + t] = flat;
+}
+
+// ── host-side launchers ──
+template <int D, int WARPS, int STAGES>
+static cudaError_t launch_decode_f16_t(const DecodeParams& p, const DecodeBatch& bt, int n_items, cudaStream_t st) {
+    using Cfg = DecodeF16Cfg<D, WARPS, STAGES>;
+    static bool attr_done = false;
+    auto kern = decode_f16_kernel<D, WARPS, STAGES>;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_B);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    kern<<<n_items * p.hkv, WARPS * 32, Cfg::SMEM_B, st>>>(p, bt);
+    return cudaGetLastError();
+}
+
+int decode_f16_cta_tokens(int head_dim) { return head_dim == 64 ? DecodeF16Cfg<64, 4, 4>::CTA_TOK : DecodeF16Cfg<128, 4, 3>::CTA_TOK; }
+
+cudaError_t launch_decode_f16(const DecodeParams& p, const DecodeBatch& bt, int head_dim, int n_items, cudaStream_t st) {
+    if (head_dim == 128) return launch_decode_f16_t<128, 4, 3>(p, bt, n_items, st);
+    if (head_dim == 64) return launch_decode_f16_t<64, 4, 4>(p, bt, n_items, st);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_finalize_scores(const FinalizeParams& f, int max_len, cudaStream_t st) {
+    if (max_len <= 0) return cudaSuccess;
+    dim3 grid((max_len + 255) / 256, f.n_seqs);
+    finalize_scores_kernel<<<grid, 256, 0, st>>>(f);
+    return cudaGetLastError();
+}
+
+}  // namespace argus

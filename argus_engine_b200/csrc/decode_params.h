@@ -1,0 +1,53 @@
+// Launch parameters shared by the split-KV decode kernels (F16 cache and KIVI-packed cache), the
+// score finalize kernel and the host planner.
+#pragma once
+#include <stdint.h>
+
+namespace argus {
+
+constexpr int kMaxBatch = 64;   // sequences per launch (descriptor table travels as a kernel parameter)
+constexpr int kMaxGroup = 8;    // query heads per KV head handled by one MMA row block
+
+// Work decomposition: item = (sequence b, split s of that sequence, kv head). Items of sequence b
+// start at item_start[b]; it has n_splits[b] splits of `chunk` tokens each (the last one ragged).
+// blockIdx.x enumerates items as ((item_start[b] + s) * Hkv + kv).
+struct DecodeBatch {
+    const void* k[kMaxBatch];
+    const void* v[kMaxBatch];
+    int64_t head_stride[kMaxBatch];  // elements
+    int64_t pos_stride[kMaxBatch];   // elements
+    int32_t seq_len[kMaxBatch];
+    int32_t item_start[kMaxBatch + 1];  // prefix sum of splits per sequence
+};
+
+struct DecodeParams {
+    const float* q;   // [B][Hq][D]
+    float* out;       // [B][Hq][D]
+    float* lse;       // [B][Hq] natural log, nullable
+    int n_seqs, hq, hkv, group;
+    int chunk;        // tokens per split (multiple of the CTA tile)
+    float scale_log2; // (1/sqrt(D)) * log2(e)
+    // split-KV scratch
+    float* part_o;    // [items][Hkv][group_pad=8][D] un-normalised partial outputs
+    float2* part_ml;  // [items][Hkv][8] (running max in log2 units, partial sum)
+    int* tickets;     // [B][Hkv] arrival counters, zero between calls
+    // score export: raw scaled logits (log2 units) written at logits[(b*Hq + h)*logit_stride + t]
+    float* logits;    // nullable
+    int64_t logit_stride;
+    float* lse2;      // [B][Hq] log2-domain lse for the finalize kernel (nullable unless logits set)
+};
+
+// Finalize: p = exp2(logit - lse2) and its reductions over the GQA group.
+struct FinalizeParams {
+    const float* logits;  // [B][Hq][logit_stride]; may alias `scores`
+    int64_t logit_stride;
+    const float* lse2;    // [B][Hq]
+    float* scores;        // [B][Hq][score_stride] nullable
+    float* head_scores;   // [B][Hkv][score_stride] nullable
+    float* flat_scores;   // [B][score_stride] nullable
+    int64_t score_stride;
+    int n_seqs, hq, hkv, group;
+    int32_t seq_len[kMaxBatch];
+};
+
+}  // namespace argus

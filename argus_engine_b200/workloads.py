@@ -1,0 +1,63 @@
+"""Seeded synthetic inputs with the shapes, dtypes and value distributions of the five benchmark
+configurations. BASELINE names no public dataset; these stand in for it. All draws use
+``numpy.random.Generator(PCG64(seed)).standard_normal(float32)`` in the stated order, so the CPU oracle and
+the GPU path see bit-identical inputs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List
+
+import numpy as np
+
+
+def _rng(seed: int) -> np.random.Generator:
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+def _normal_f16(rng: np.random.Generator, shape) -> np.ndarray:
+    return rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
+
+
+@dataclass
+class DecodeCase:
+    """q [B,Hq,D] f32; per sequence K/V f16 HeadMajor [Hkv,cap,D] (cap == T unless stated)."""
+    q: np.ndarray
+    k: List[np.ndarray]
+    v: List[np.ndarray]
+    lens: List[int]
+    hq: int
+    hkv: int
+    d: int
+
+
+def decode_case(seed: int, lens, hq: int, hkv: int, d: int, cap_extra: int = 0) -> DecodeCase:
+    """Draw order: q for all sequences, then per sequence K then V."""
+    rng = _rng(seed)
+    lens = [int(t) for t in lens]
+    q = rng.standard_normal((len(lens), hq, d), dtype=np.float32)
+    k, v = [], []
+    for t in lens:
+        k.append(_normal_f16(rng, (hkv, t + cap_extra, d)))
+        v.append(_normal_f16(rng, (hkv, t + cap_extra, d)))
+    return DecodeCase(q, k, v, lens, hq, hkv, d)
+
+
+def config1() -> DecodeCase:
+    """B=1, Hq=32, Hkv=8, D=64, T=2048, seed 0."""
+    return decode_case(0, [2048], 32, 8, 64)
+
+
+def config2_lengths(batch: int = 16, lo: int = 1024, hi: int = 8192, seed: int = 1) -> List[int]:
+    """Per-sequence KV lengths, uniform in [lo, hi] (first draw of the seed-1 stream)."""
+    return _rng(seed).integers(lo, hi, size=batch, endpoint=True).tolist()
+
+
+def config2(batch: int = 16, lo: int = 1024, hi: int = 8192) -> DecodeCase:
+    """Llama-3-8B layer shape: B=16, Hq=32, Hkv=8, D=128, lengths U[1024,8192], seed 1."""
+    rng = _rng(1)
+    lens = rng.integers(lo, hi, size=batch, endpoint=True).tolist()
+    q = rng.standard_normal((batch, 32, 128), dtype=np.float32)
+    k = [_normal_f16(rng, (8, t, 128)) for t in lens]
+    v = [_normal_f16(rng, (8, t, 128)) for t in lens]
+    return DecodeCase(q, k, v, lens, 32, 8, 128)

@@ -1,0 +1,156 @@
+"""GPU parity of the split-KV F16 decode kernel against the CPU oracle, through the C ABI.
+
+Tolerances are the ones the task states for attention outputs and H2O scores: max-abs 2e-3 / rel 1e-2
+against the F32 reference (np.allclose form |a-b| <= atol + rtol*|b|). Score probabilities are O(1/T),
+so they are checked with the relative bound and a tiny absolute floor.
+"""
+import numpy as np
+import pytest
+import torch
+
+from argus_engine_b200 import workloads as wl
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+OUT_ATOL, OUT_RTOL = 2e-3, 1e-2
+P_ATOL, P_RTOL = 1e-7, 1e-2
+
+
+@pytest.fixture(scope="module")
+def be():
+    from argus_engine_b200 import B200Backend
+
+    b = B200Backend(0)
+    yield b
+    b.close()
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _oracle(case, i, head_major=True, scores=False):
+    k, v = case.k[i].view(np.uint16), case.v[i].view(np.uint16)
+    return orc.attention_gen(case.q[i], k, v, case.hq, case.hkv, case.d, case.lens[i], head_major,
+                             want_scores=scores)
+
+
+def _run_single(be, case, i=0, seq_major=False, scores_stride=None, host_scores=False, lse=False):
+    from argus_engine_b200 import DecodeExtras
+
+    k, v = case.k[i], case.v[i]
+    if seq_major:
+        k, v = (np.ascontiguousarray(a.transpose(1, 0, 2)) for a in (k, v))
+    kd, vd, qd = _dev(k), _dev(v), _dev(case.q[i])
+    out = torch.full((case.hq, case.d), float("nan"), device="cuda")
+    ex = DecodeExtras()
+    sc = None
+    if scores_stride:
+        sc = torch.full((case.hq, scores_stride), -1.0, device="cpu" if host_scores else "cuda")
+    if lse:
+        ex.lse = torch.zeros(case.hq, device="cuda")
+    be.attention_gen(qd, kd, vd, out, case.hq, case.hkv, case.d, case.lens[i], scores_out=sc, extras=ex)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), None if sc is None else sc.cpu().numpy(), None if not lse else ex.lse.cpu().numpy()
+
+
+def test_config1_parity(be):
+    """BASELINE configs[0]: B=1, Hq=32, Hkv=8, D=64, T=2048, seed 0."""
+    case = wl.config1()
+    want, _ = _oracle(case, 0)
+    got, _, _ = _run_single(be, case)
+    np.testing.assert_allclose(got, want, atol=OUT_ATOL, rtol=OUT_RTOL)
+    assert np.max(np.abs(got - want)) < 2e-4   # what the hi/lo operand split actually delivers
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("g", [1, 2, 4, 8])
+@pytest.mark.parametrize("T", [1, 15, 16, 17, 63, 64, 65, 129, 1000, 2500])
+def test_shapes_and_ragged_lengths(be, d, g, T):
+    hkv = 2
+    case = wl.decode_case(100 + T + d + g, [T], hkv * g, hkv, d, cap_extra=7)
+    for a in (case.k[0], case.v[0]):
+        a[:, T:, :] = np.nan   # rows past cache_seq_len must never be read into the result
+    want, want_p = _oracle(case, 0, scores=True)
+    got, got_p, lse = _run_single(be, case, scores_stride=T + 3, lse=True)
+    np.testing.assert_allclose(got, want, atol=OUT_ATOL, rtol=OUT_RTOL)
+    np.testing.assert_allclose(got_p[:, :T], want_p, atol=P_ATOL, rtol=P_RTOL)
+    assert np.all(got_p[:, T:] == -1.0)   # padding of the score rows is left alone
+    kf = case.k[0][:, :T].astype(np.float64)
+    s = np.einsum("htd,hgd->hgt", kf, case.q[0].reshape(hkv, g, d).astype(np.float64)) / np.sqrt(d)
+    want_lse = np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1)
+    np.testing.assert_allclose(lse, want_lse.reshape(-1), atol=1e-3)
+
+
+@pytest.mark.parametrize("T", [333, 4096])
+def test_seq_major_layout(be, T):
+    case = wl.decode_case(7, [T], 8, 2, 128)
+    want, _ = _oracle(case, 0)
+    got, _, _ = _run_single(be, case, seq_major=True)
+    np.testing.assert_allclose(got, want, atol=OUT_ATOL, rtol=OUT_RTOL)
+
+
+def test_host_scores_blocking_readback(be):
+    """`scores_out` as a host slice: filled when the call returns (engine/src/backend/cuda_pc.rs:1867-1880)."""
+    case = wl.decode_case(11, [777], 8, 2, 64)
+    want, want_p = _oracle(case, 0, scores=True)
+    got, got_p, _ = _run_single(be, case, scores_stride=800, host_scores=True)
+    np.testing.assert_allclose(got, want, atol=OUT_ATOL, rtol=OUT_RTOL)
+    np.testing.assert_allclose(got_p[:, :777], want_p, atol=P_ATOL, rtol=P_RTOL)
+
+
+def test_batched_varlen_with_fused_group_scores(be):
+    """A scaled-down configs[1] (same head shape, lengths U[64,1500]) incl. an empty sequence."""
+    from argus_engine_b200 import DecodeExtras
+
+    lens = wl.config2_lengths(6, 64, 1500) + [0]
+    case = wl.decode_case(1, lens, 32, 8, 128)
+    B, stride = len(lens), 1536
+    qd = _dev(case.q)
+    kd = [_dev(a) if a.size else torch.zeros(8, 1, 128, dtype=torch.float16, device="cuda") for a in case.k]
+    vd = [_dev(a) if a.size else torch.zeros(8, 1, 128, dtype=torch.float16, device="cuda") for a in case.v]
+    out = torch.full((B, 32, 128), float("nan"), device="cuda")
+    ex = DecodeExtras(head_scores=torch.zeros(B, 8, stride, device="cuda"),
+                      flat_scores=torch.zeros(B, stride, device="cuda"),
+                      lse=torch.zeros(B, 32, device="cuda"), score_stride=stride)
+    be.attention_gen_batched(qd, kd, vd, lens, out, 32, 8, 128, extras=ex)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    for i, T in enumerate(lens):
+        if T == 0:
+            assert np.all(got[i] == 0.0) and np.all(np.isneginf(ex.lse[i].cpu().numpy()))
+            continue
+        want, want_p = _oracle(case, i, scores=True)
+        np.testing.assert_allclose(got[i], want, atol=OUT_ATOL, rtol=OUT_RTOL)
+        sf = np.zeros(stride, dtype=np.float32)
+        sh = np.zeros(8 * stride, dtype=np.float32)
+        orc.score_accumulate_layer(want_p, T, 32, 8, stride, sf, sh)
+        np.testing.assert_allclose(ex.head_scores[i].cpu().numpy()[:, :T], sh.reshape(8, stride)[:, :T],
+                                   atol=P_ATOL, rtol=P_RTOL)
+        np.testing.assert_allclose(ex.flat_scores[i].cpu().numpy()[:T], sf[:T], atol=P_ATOL, rtol=P_RTOL)
+
+
+def test_many_splits_and_determinism(be):
+    """Long sequence => many splits merged through the ticket path; two runs are bit-identical."""
+    case = wl.decode_case(5, [50000], 16, 2, 128)
+    want, _ = _oracle(case, 0)
+    a, _, _ = _run_single(be, case)
+    b, _, _ = _run_single(be, case)
+    np.testing.assert_allclose(a, want, atol=OUT_ATOL, rtol=OUT_RTOL)
+    assert np.array_equal(a, b)
+
+
+def test_argument_errors(be):
+    from argus_engine_b200 import ArgusB200Error
+
+    q = torch.zeros(8, 96, device="cuda")
+    k = torch.zeros(2, 16, 96, dtype=torch.float16, device="cuda")
+    with pytest.raises(ArgusB200Error) as e:   # head_dim 96 is declined, not faulted
+        be.attention_gen(q, k, k, torch.zeros_like(q), 8, 2, 96, 16)
+    assert e.value.code == -2
+    q = torch.zeros(8, 64, device="cuda")
+    k = torch.zeros(2, 16, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(ArgusB200Error) as e:   # 8 query heads over 3 KV heads
+        be.attention_gen(q, k, k, torch.zeros_like(q), 8, 3, 64, 16)
+    assert e.value.code == -1
