@@ -37,23 +37,43 @@ float* Context::scratch(size_t* cursor, size_t bytes) {
     return reinterpret_cast<float*>(ws + at);
 }
 
-// Choose the split length (tokens per CTA) for a batch of sequences. Every (split, KV head) is a CTA;
-// the grid should cover all SMs several times so that ragged sequence tails balance out, while a split
-// stays long enough to amortise the pipeline fill. `cta_tok` is the kernel's token granularity.
-int plan_chunk(const int64_t* lens, int n, int hkv, int cta_tok, int num_sms, int ctas_per_sm, int waves) {
-    int64_t total = 0, longest = 0;
+// Split planning. Every (split, KV head) is a CTA. The split budget S = slots*waves/Hkv is shared out in
+// proportion to the sequence lengths, so that all splits of a batch are close to the same length and a wave
+// of CTAs starts and ends together; leftover splits go to the sequences whose splits are longest. A split
+// is never shorter than `min_chunk` tokens (pipeline fill) and a sequence never has more than kMaxSplits.
+void plan_splits(const int64_t* lens, int n, int hkv, int slots, int waves, int min_chunk, int32_t* chunk,
+                 int32_t* nsplit) {
+    int64_t total = 0;
+    for (int i = 0; i < n; ++i) total += lens[i];
+    const int64_t S = std::max<int64_t>(1, (int64_t)slots * waves / hkv);
+    const double ideal = std::max<double>(min_chunk, (double)total / (double)S);
+    int64_t used = 0;
     for (int i = 0; i < n; ++i) {
-        total += lens[i];
-        longest = std::max(longest, lens[i]);
+        int64_t k = (int64_t)((double)lens[i] / ideal);
+        k = std::min<int64_t>(std::max<int64_t>(k, 1), kMaxSplits);
+        nsplit[i] = (int32_t)k;
+        used += k;
     }
-    if (longest <= 0) return cta_tok;
-    const int64_t target_items = std::max<int64_t>(1, (int64_t)num_sms * ctas_per_sm * waves / hkv);
-    int64_t chunk = (total + target_items - 1) / target_items;
-    const int64_t min_chunk = 2 * cta_tok;
-    chunk = std::max(chunk, min_chunk);
-    chunk = ((chunk + cta_tok - 1) / cta_tok) * cta_tok;
-    chunk = std::min<int64_t>(chunk, ((longest + cta_tok - 1) / cta_tok) * cta_tok);
-    return (int)chunk;
+    while (used < S) {
+        int best = -1;
+        double best_len = 0.0;
+        for (int i = 0; i < n; ++i) {
+            const double per = (double)lens[i] / nsplit[i];
+            if (per > best_len && nsplit[i] < kMaxSplits && lens[i] / (nsplit[i] + 1) >= min_chunk) {
+                best_len = per;
+                best = i;
+            }
+        }
+        if (best < 0) break;
+        nsplit[best] += 1;
+        used += 1;
+    }
+    for (int i = 0; i < n; ++i) {
+        int64_t c = (lens[i] + nsplit[i] - 1) / nsplit[i];
+        c = std::max<int64_t>(16, ((c + 15) / 16) * 16);
+        chunk[i] = (int32_t)c;
+        nsplit[i] = (int32_t)std::max<int64_t>(1, (lens[i] + c - 1) / c);
+    }
 }
 
 static int env_int(const char* name, int dflt) {
@@ -116,13 +136,14 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
         return ARGUS_B200_E_INVALID;
     }
 
-    const int cta_tok = decode_f16_cta_tokens(d);
-    const int waves = env_int("ARGUS_B200_DECODE_WAVES", 4);
-    const int chunk = plan_chunk(lens, n_seqs, hkv, cta_tok, ctx->num_sms, 2, waves);
+    const int waves = env_int("ARGUS_B200_DECODE_WAVES", 1);
+    const int min_chunk = env_int("ARGUS_B200_DECODE_MIN_CHUNK", 2 * decode_f16_cta_tokens(d));
+    int32_t nsplit[kMaxBatch];
+    plan_splits(lens, n_seqs, hkv, ctx->num_sms * 2, waves, min_chunk, bt.chunk, nsplit);
     int items = 0;
     for (int i = 0; i < n_seqs; ++i) {
         bt.item_start[i] = items;
-        items += std::max<int64_t>(1, (lens[i] + chunk - 1) / chunk);
+        items += nsplit[i];
     }
     bt.item_start[n_seqs] = items;
 
@@ -162,7 +183,6 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
     p.hq = hq;
     p.hkv = hkv;
     p.group = g;
-    p.chunk = chunk;
     p.scale_log2 = (1.0f / sqrtf((float)d)) * 1.4426950408889634f;
     p.part_o = part_o;
     p.part_ml = reinterpret_cast<float2*>(part_ml);

@@ -23,7 +23,8 @@ struct Context {
     float* scratch(size_t* cursor, size_t bytes);
 };
 
-int plan_chunk(const int64_t* lens, int n, int hkv, int cta_tok, int num_sms, int ctas_per_sm, int waves);
+void plan_splits(const int64_t* lens, int n, int hkv, int slots, int waves, int min_chunk, int32_t* chunk,
+                 int32_t* nsplit);
 
 // decode_f16.cu
 int decode_f16_cta_tokens(int head_dim);

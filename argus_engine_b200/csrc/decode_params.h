@@ -7,9 +7,10 @@ namespace argus {
 
 constexpr int kMaxBatch = 64;   // sequences per launch (descriptor table travels as a kernel parameter)
 constexpr int kMaxGroup = 8;    // query heads per KV head handled by one MMA row block
+constexpr int kMaxSplits = 512; // splits of one sequence (bounds the merge table in shared memory)
 
 // Work decomposition: item = (sequence b, split s of that sequence, kv head). Items of sequence b
-// start at item_start[b]; it has n_splits[b] splits of `chunk` tokens each (the last one ragged).
+// start at item_start[b]; it has item_start[b+1]-item_start[b] splits of chunk[b] tokens (the last one ragged).
 // blockIdx.x enumerates items as ((item_start[b] + s) * Hkv + kv).
 struct DecodeBatch {
     const void* k[kMaxBatch];
@@ -17,6 +18,7 @@ struct DecodeBatch {
     int64_t head_stride[kMaxBatch];  // elements
     int64_t pos_stride[kMaxBatch];   // elements
     int32_t seq_len[kMaxBatch];
+    int32_t chunk[kMaxBatch];           // tokens per split of this sequence (multiple of 16)
     int32_t item_start[kMaxBatch + 1];  // prefix sum of splits per sequence
 };
 
@@ -25,7 +27,6 @@ struct DecodeParams {
     float* out;       // [B][Hq][D]
     float* lse;       // [B][Hq] natural log, nullable
     int n_seqs, hq, hkv, group;
-    int chunk;        // tokens per split (multiple of the CTA tile)
     float scale_log2; // (1/sqrt(D)) * log2(e)
     // split-KV scratch
     float* part_o;    // [items][Hkv][group_pad=8][D] un-normalised partial outputs
