@@ -1,0 +1,335 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl b200|reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input (one layer-step). The default
+workload is the batched GQA decode of the Llama-3-8B layer shape (B=16, Hq=32, Hkv=8, D=128, per-sequence
+KV lengths U[1024,8192] from seed 1, F16 K/V in the engine's HeadMajor layout). Rank 0 prints ONE JSON line:
+
+  value     algorithmic HBM bytes per step / device time per step, inputs resident in HBM (TB/s)
+  e2e       the same metric through the C ABI with HOST buffers: per step the inputs are copied from pinned
+            host memory, the kernel runs, the output is copied back and read
+  roofline  the dominant kernel against the measured HBM copy bandwidth of this pool
+  cpu_baseline  the reference's AVX2 CPU attention (restated in oracle/) on the host cores, same inputs
+
+With --gpus N > 1 (under torch.distributed.run) every rank runs an independent replica of the workload
+(batched decode has no exchange step), timed as the max over ranks; the sequence-sharded 1M-token decode,
+which does have one gather, is reported beside it under "sharded".
+`--impl reference` times the reference's own CPU implementation of the same step on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode_attn_hbm_throughput"
+UNIT = "TB/s"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int, period: float = 0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop_evt = threading.Event()
+        self.window = [None, None]
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self._stop_evt.is_set():
+            try:
+                mhz = int(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                bits = int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                self.samples.append((time.perf_counter(), mhz, bits))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+
+    def summary(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        t0, t1 = self.window
+        inside = [s for s in self.samples if t0 is not None and t0 <= s[0] <= t1] or self.samples
+        mhz = sorted(s[1] for s in inside)
+        reasons = set()
+        for s in inside:
+            for bit, name in self.BITS.items():
+                if s[2] & bit:
+                    reasons.add(name)
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(reasons),
+                "samples": len(inside)}
+
+
+# ───────────────────────────── workloads ─────────────────────────────
+
+def c2_case():
+    from argus_engine_b200 import workloads as wl
+
+    return wl.config2()
+
+
+def decode_bytes(case) -> int:
+    """Algorithmic bytes of one decode step: K+V rows read once, q read, out written."""
+    kv = sum(case.lens) * case.hkv * case.d * 2 * 2
+    return kv + 2 * len(case.lens) * case.hq * case.d * 4
+
+
+def cpu_decode_step(case, seq_ids, threads=0):
+    """The reference's CPU decode (AVX2 arm, one task per query head, sequences looped serially)."""
+    from oracle import oracle as orc
+
+    out = None
+    for i in seq_ids:
+        out, _ = orc.attention_gen(case.q[i], case.k[i].view(np.uint16), case.v[i].view(np.uint16), case.hq, case.hkv,
+                                   case.d, case.lens[i], True, avx2=True, n_threads=threads)
+    return out
+
+
+def run_reference(args):
+    """--impl reference: the reference's own CPU implementation of the step on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+
+    case = c2_case()
+    n = len(case.lens)
+    cores = orc.num_threads()
+    t = time.perf_counter()
+    cpu_decode_step(case, range(n))
+    one = time.perf_counter() - t
+    total_steps = args.steps + args.warmup
+    # bounded sample: keep the whole run within ~2 minutes by timing a prefix of the batch per step
+    n_sample = n
+    if one * total_steps > 120.0:
+        n_sample = max(1, int(n * 120.0 / (one * total_steps)))
+    ids = list(range(n_sample))
+    sample_bytes = sum(case.lens[i] for i in ids) * case.hkv * case.d * 4 + 2 * n_sample * case.hq * case.d * 4
+    for _ in range(args.warmup):
+        cpu_decode_step(case, ids)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_decode_step(case, ids)
+    dt = (time.perf_counter() - t) / max(1, args.steps)
+    value = sample_bytes / dt / 1e12
+    sample = f"{n_sample} of {n} sequences of the batch per step ({sample_bytes / 1e6:.1f} MB algorithmic)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3 * n / n_sample, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config("c2", case),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, case):
+    return {"workload": f"{name}: batched GQA decode attention, Llama-3-8B layer shape", "batch": len(case.lens),
+            "heads_q": case.hq, "heads_kv": case.hkv, "head_dim": case.d, "kv_lens": "U[1024,8192] seed 1",
+            "kv_tokens_total": int(sum(case.lens)), "kv_dtype": "f16", "kv_layout": "HeadMajor [Hkv,cap,D]",
+            "l2": "inputs (310 MB) exceed the 126 MB L2; two KV copies are alternated between steps"}
+
+
+def run_b200(args):
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    from argus_engine_b200 import B200Backend
+
+    be = B200Backend(local)
+    peaks = measured_peaks()
+    case = c2_case()
+    B, hq, hkv, d = len(case.lens), case.hq, case.hkv, case.d
+    step_bytes = decode_bytes(case)
+
+    # device-resident inputs: two KV copies, alternated so that no step finds its K/V in L2
+    q = torch.from_numpy(case.q).cuda()
+    kv_sets = []
+    for _ in range(2):
+        kv_sets.append(([torch.from_numpy(a).cuda() for a in case.k], [torch.from_numpy(a).cuda() for a in case.v]))
+    out = torch.zeros(B, hq, d, device="cuda")
+
+    def step(i):
+        ks, vs = kv_sets[i & 1]
+        be.attention_gen_batched(q, ks, vs, case.lens, out, hq, hkv, d)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+    launches0 = be.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.window[0] = time.perf_counter()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    sampler.window[1] = time.perf_counter()
+    launches = be.launch_count - launches0
+    ms = e0.elapsed_time(e1) / max(1, args.steps)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = world * step_bytes / (ms * 1e-3) / 1e12
+
+    # parity of the timed configuration against the oracle on one sequence (cheap, outside the timed region)
+    parity = None
+    if rank == 0:
+        from oracle import oracle as orc
+
+        i = int(np.argmin(case.lens))
+        want, _ = orc.attention_gen(case.q[i], case.k[i].view(np.uint16), case.v[i].view(np.uint16), hq, hkv, d,
+                                    case.lens[i])
+        parity = float(np.max(np.abs(out[i].cpu().numpy() - want)))
+
+    # end-to-end through the C ABI with host buffers
+    hq_pin = torch.from_numpy(case.q).pin_memory()
+    hk_pin = [torch.from_numpy(a).pin_memory() for a in case.k]
+    hv_pin = [torch.from_numpy(a).pin_memory() for a in case.v]
+    out_pin = torch.zeros(B, hq, d).pin_memory()
+    dq = torch.empty_like(q)
+    dk, dv = kv_sets[0]
+    h2d = q.numel() * 4 + sum(a.numel() * 2 for a in hk_pin) * 2
+    d2h = out.numel() * 4
+    n_e2e = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        dq.copy_(hq_pin, non_blocking=True)
+        for i in range(B):
+            dk[i].copy_(hk_pin[i], non_blocking=True)
+            dv[i].copy_(hv_pin[i], non_blocking=True)
+        be.attention_gen_batched(dq, dk, dv, case.lens, out, hq, hkv, d)
+        out_pin.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+        return float(out_pin[0, 0, 0])
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    e2e_s = (time.perf_counter() - t0) / n_e2e
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_val = world * step_bytes / e2e_s / 1e12
+    sampler.stop()
+
+    cpu = None
+    if rank == 0 and world == 1:
+        from oracle import oracle as orc
+
+        cores = orc.num_threads()
+        cpu_decode_step(case, range(B))
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 50):
+            cpu_decode_step(case, range(B))
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        cpu = {"value": step_bytes / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"the whole step (16 sequences, {step_bytes / 1e6:.1f} MB algorithmic), mean of {reps} runs",
+               "ms_per_step": dt * 1e3}
+
+    if rank == 0:
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "us_per_layer_step": ms * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config("c2", case),
+            "roofline": {"bound": "hbm", "kernel": "decode_f16_kernel<128,4,3>", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "peak_source": peaks["source"], "traffic": None,
+                         "algorithmic_bytes_per_launch": step_bytes},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_s * 1e3, "steps": n_e2e},
+            "gpu_launches": int(launches),
+            "clocks": sampler.summary(),
+            "parity_max_abs_vs_oracle": parity,
+        }
+        print(json.dumps(line), flush=True)
+    be.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps == 2000:
+            args.steps = 20
+            args.warmup = min(args.warmup, 3)
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()
