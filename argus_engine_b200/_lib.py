@@ -24,6 +24,46 @@ class DecodeExtrasC(C.Structure):
                 ("lse", C.c_void_p), ("scores_host", C.c_void_p), ("score_stride", C.c_int64)]
 
 
+class QuantAttnArgs(C.Structure):
+    """CudaQuantAttnArgs (crates/argus-extension-api/src/lib.rs:3000-3026)."""
+    _fields_ = [("cu_stream", C.c_void_p), ("q_mem", C.c_uint64), ("qk_mem", C.c_uint64), ("qv_mem", C.c_uint64),
+                ("res_k_mem", C.c_uint64), ("res_v_mem", C.c_uint64), ("out_mem", C.c_uint64),
+                ("scores_out", C.c_void_p), ("scores_len", C.c_size_t), ("num_heads_q", C.c_size_t),
+                ("num_heads_kv", C.c_size_t), ("head_dim", C.c_size_t), ("q_tokens", C.c_size_t),
+                ("res_tokens", C.c_size_t), ("res_cap", C.c_size_t), ("scale", C.c_float), ("bits", C.c_uint8)]
+
+
+class QuantGatherArgs(C.Structure):
+    _fields_ = [("cu_stream", C.c_void_p), ("input_mem", C.c_uint64), ("residual_mem", C.c_uint64),
+                ("kv_heads", C.c_size_t), ("res_cap", C.c_size_t), ("head_dim", C.c_size_t), ("seq_len", C.c_size_t),
+                ("res_pos", C.c_size_t)]
+
+
+class QuantDequantFlushArgs(C.Structure):
+    _fields_ = [("cu_stream", C.c_void_p), ("q_blocks_mem", C.c_uint64), ("attn_mem", C.c_uint64),
+                ("kv_heads", C.c_size_t), ("head_dim", C.c_size_t), ("n_groups_or_tokens", C.c_size_t),
+                ("tok_base", C.c_size_t), ("block_start", C.c_size_t), ("bits", C.c_uint8), ("is_key", C.c_uint8)]
+
+
+class QuantScatterResidualArgs(C.Structure):
+    _fields_ = [("cu_stream", C.c_void_p), ("res_mem", C.c_uint64), ("attn_mem", C.c_uint64),
+                ("kv_heads", C.c_size_t), ("res_cap", C.c_size_t), ("head_dim", C.c_size_t), ("res_pos", C.c_size_t),
+                ("tok_base", C.c_size_t)]
+
+
+class KiviSeq(C.Structure):
+    _fields_ = [("qk", C.c_void_p), ("qv", C.c_void_p), ("res_k", C.c_void_p), ("res_v", C.c_void_p),
+                ("q_tokens", C.c_int64), ("res_tokens", C.c_int64)]
+
+
+class ScoreReduceArgs(C.Structure):
+    """CudaScoreReduceArgs (crates/argus-extension-api/src/lib.rs:2909-2933)."""
+    _fields_ = [("cu_stream", C.c_void_p), ("score_buf", C.c_uint64), ("importance", C.c_uint64),
+                ("head_importance", C.c_uint64), ("decay_factor", C.c_float), ("n_layers", C.c_size_t),
+                ("n_heads_q", C.c_size_t), ("n_kv_heads", C.c_size_t), ("cache_seq_len", C.c_size_t),
+                ("score_stride", C.c_size_t), ("max_seq_len", C.c_size_t), ("layer_flat_importance", C.c_uint64)]
+
+
 _lib = None
 
 
@@ -48,5 +88,16 @@ def load_library() -> C.CDLL:
                                              C.POINTER(DecodeExtrasC)]
     lib.argus_b200_attention_gen_batched.argtypes = [vp, vp, vp, C.POINTER(Seq), i32, vp, i32, i32, i32, i32,
                                                      C.POINTER(DecodeExtrasC)]
+    lib.argus_b200_kivi_has_quant_attn_kernel.argtypes = [vp, i32]
+    lib.argus_b200_kivi_attention_gen_quant.argtypes = [vp, C.POINTER(QuantAttnArgs)]
+    lib.argus_b200_kivi_gather_update_quant.argtypes = [vp, C.POINTER(QuantGatherArgs)]
+    lib.argus_b200_kivi_dequant_flush.argtypes = [vp, C.POINTER(QuantDequantFlushArgs)]
+    lib.argus_b200_kivi_scatter_residual.argtypes = [vp, C.POINTER(QuantScatterResidualArgs)]
+    lib.argus_b200_kivi_flush_pack.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i64]
+    lib.argus_b200_kivi_attention_batched.argtypes = [vp, vp, vp, C.POINTER(KiviSeq), i32, vp, i32, i32, i32, i32, i32,
+                                                      i32, C.c_float, C.POINTER(DecodeExtrasC)]
+    lib.argus_b200_score_reduce.argtypes = [vp, C.POINTER(ScoreReduceArgs)]
+    lib.argus_b200_score_reduce_per_layer.argtypes = [vp, C.POINTER(ScoreReduceArgs)]
+    lib.argus_b200_check_status.argtypes = [vp, vp]
     _lib = lib
     return lib

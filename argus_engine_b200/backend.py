@@ -12,7 +12,8 @@ from typing import Optional, Sequence
 
 import torch
 
-from ._lib import ArgusB200Error, DecodeExtrasC, Seq, load_library
+from ._lib import (ArgusB200Error, DecodeExtrasC, KiviSeq, QuantAttnArgs, QuantDequantFlushArgs, QuantGatherArgs,
+                   QuantScatterResidualArgs, ScoreReduceArgs, Seq, load_library)
 
 KV_F32, KV_F16 = 0, 1
 
@@ -123,3 +124,73 @@ class B200Backend:
         self._check(self._lib.argus_b200_attention_gen_batched(
             self._h, self._stream(), q.data_ptr(), arr, n, out.data_ptr(), num_heads_q, num_heads_kv, head_dim, dt,
             self._extras(extras)))
+
+    # ── CudaQuantAttnBackend (crates/argus-extension-api/src/lib.rs:3087-3104) ──
+    def has_quant_attn_kernel(self, bits: int) -> bool:
+        return bool(self._lib.argus_b200_kivi_has_quant_attn_kernel(self._h, bits))
+
+    def attention_gen_quant(self, q, qk, qv, res_k, res_v, out, num_heads_q, num_heads_kv, head_dim, q_tokens,
+                            res_tokens, res_cap, scale, bits, scores_out: Optional[torch.Tensor] = None) -> int:
+        """Argument meaning of CudaQuantAttnArgs; ``scores_out`` is a HOST tensor [Hq, stride] or None.
+        Returns the reference's status code (0 ok, negative on failure) instead of raising."""
+        a = QuantAttnArgs(self._stream(), q.data_ptr(), _ptr(qk) or 0, _ptr(qv) or 0, _ptr(res_k) or 0, _ptr(res_v) or 0,
+                          out.data_ptr(), _ptr(scores_out), 0 if scores_out is None else scores_out.numel(),
+                          num_heads_q, num_heads_kv, head_dim, q_tokens, res_tokens, res_cap, float(scale), bits)
+        return int(self._lib.argus_b200_kivi_attention_gen_quant(self._h, C.byref(a)))
+
+    def gather_update_quant(self, inp, residual, kv_heads, res_cap, head_dim, seq_len, res_pos) -> int:
+        a = QuantGatherArgs(self._stream(), inp.data_ptr(), residual.data_ptr(), kv_heads, res_cap, head_dim, seq_len,
+                            res_pos)
+        return int(self._lib.argus_b200_kivi_gather_update_quant(self._h, C.byref(a)))
+
+    def dequant_flush(self, q_blocks, attn, kv_heads, head_dim, n_groups_or_tokens, tok_base, block_start, bits,
+                      is_key) -> int:
+        a = QuantDequantFlushArgs(self._stream(), q_blocks.data_ptr(), attn.data_ptr(), kv_heads, head_dim,
+                                  n_groups_or_tokens, tok_base, block_start, bits, int(bool(is_key)))
+        return int(self._lib.argus_b200_kivi_dequant_flush(self._h, C.byref(a)))
+
+    def scatter_residual(self, res, attn, kv_heads, res_cap, head_dim, res_pos, tok_base) -> int:
+        a = QuantScatterResidualArgs(self._stream(), res.data_ptr(), attn.data_ptr(), kv_heads, res_cap, head_dim,
+                                     res_pos, tok_base)
+        return int(self._lib.argus_b200_kivi_scatter_residual(self._h, C.byref(a)))
+
+    def kivi_flush_pack(self, res_k, res_v, qk, qv, kv_heads, head_dim, res_cap, n_groups, bits, k_block_start,
+                        v_block_start) -> None:
+        """Device-side flush of the residual ring into packed blocks (bit-exact with the CPU codec)."""
+        self._check(self._lib.argus_b200_kivi_flush_pack(self._h, self._stream(), res_k.data_ptr(), res_v.data_ptr(),
+                                                         qk.data_ptr(), qv.data_ptr(), kv_heads, head_dim, res_cap,
+                                                         n_groups, bits, k_block_start, v_block_start))
+
+    def kivi_attention_batched(self, q, seqs, out, num_heads_q, num_heads_kv, head_dim, res_cap, bits, scale,
+                               res_f16: bool = False, extras: Optional[DecodeExtras] = None) -> None:
+        """seqs: list of (qk, qv, res_k, res_v, q_tokens, res_tokens) with device tensors (or None when empty)."""
+        n = len(seqs)
+        arr = (KiviSeq * n)()
+        for i, (qk, qv, rk, rv, qt, rt) in enumerate(seqs):
+            arr[i] = KiviSeq(_ptr(qk), _ptr(qv), _ptr(rk), _ptr(rv), int(qt), int(rt))
+        self._check(self._lib.argus_b200_kivi_attention_batched(
+            self._h, self._stream(), q.data_ptr(), arr, n, out.data_ptr(), num_heads_q, num_heads_kv, head_dim, res_cap,
+            bits, KV_F16 if res_f16 else KV_F32, float(scale), self._extras(extras)))
+
+    # ── CudaScoreReduceBackend (crates/argus-extension-api/src/lib.rs:2938-2948) ──
+    def _reduce_args(self, score_buf, importance, head_importance, decay_factor, n_layers, n_heads_q, n_kv_heads,
+                     cache_seq_len, score_stride, max_seq_len, layer_flat):
+        return ScoreReduceArgs(self._stream(), score_buf.data_ptr(), _ptr(importance) or 0, _ptr(head_importance) or 0,
+                               float(decay_factor), n_layers, n_heads_q, n_kv_heads, cache_seq_len, score_stride,
+                               max_seq_len, _ptr(layer_flat) or 0)
+
+    def score_reduce(self, score_buf, importance, head_importance, decay_factor, n_layers, n_heads_q, n_kv_heads,
+                     cache_seq_len, score_stride, max_seq_len, layer_flat=None) -> int:
+        a = self._reduce_args(score_buf, importance, head_importance, decay_factor, n_layers, n_heads_q, n_kv_heads,
+                              cache_seq_len, score_stride, max_seq_len, layer_flat)
+        return int(self._lib.argus_b200_score_reduce(self._h, C.byref(a)))
+
+    def score_reduce_per_layer(self, score_buf, layer_flat, decay_factor, n_layers, n_heads_q, n_kv_heads,
+                               cache_seq_len, score_stride, max_seq_len) -> int:
+        a = self._reduce_args(score_buf, None, None, decay_factor, n_layers, n_heads_q, n_kv_heads, cache_seq_len,
+                              score_stride, max_seq_len, layer_flat)
+        return int(self._lib.argus_b200_score_reduce_per_layer(self._h, C.byref(a)))
+
+    def check_status(self) -> int:
+        """Synchronises the current stream; non-zero if a kernel's bounded wait ran out since the last check."""
+        return int(self._lib.argus_b200_check_status(self._h, self._stream()))

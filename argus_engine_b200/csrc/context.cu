@@ -190,6 +190,7 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
     p.logits = logits;
     p.logit_stride = logit_stride;
     p.lse2 = lse2;
+    p.status = ctx->status;
 
     cudaError_t e = launch_decode_f16(p, bt, d, items, st);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "decode_f16 launch");
@@ -250,9 +251,12 @@ int argus_b200_create(int device, size_t workspace_bytes, argus_b200_ctx** out) 
     e = cudaMalloc(&c->ws, c->ws_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->tickets, c->n_tickets * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->tickets, 0, c->n_tickets * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&c->status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(int));
     if (e != cudaSuccess) {
         if (c->ws) cudaFree(c->ws);
         if (c->tickets) cudaFree(c->tickets);
+        if (c->status) cudaFree(c->status);
         delete c;
         return ARGUS_B200_E_CUDA;
     }
@@ -265,6 +269,7 @@ void argus_b200_destroy(argus_b200_ctx* ctx) {
     if (!c) return;
     cudaFree(c->ws);
     cudaFree(c->tickets);
+    cudaFree(c->status);
     delete c;
 }
 

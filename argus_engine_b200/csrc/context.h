@@ -1,5 +1,6 @@
 // Internal: the object behind argus_b200_ctx and the kernel launchers the entry points call.
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -15,6 +16,7 @@ struct Context {
     size_t ws_bytes = 0;
     int* tickets = nullptr;     // arrival counters of the split merge; all zero between calls
     size_t n_tickets = 0;
+    int* status = nullptr;      // device word set by a kernel whose bounded wait ran out
     uint64_t launches = 0;
     char err[512] = {0};
 
@@ -30,5 +32,25 @@ void plan_splits(const int64_t* lens, int n, int hkv, int slots, int waves, int 
 int decode_f16_cta_tokens(int head_dim);
 cudaError_t launch_decode_f16(const DecodeParams& p, const DecodeBatch& bt, int head_dim, int n_items, cudaStream_t st);
 cudaError_t launch_finalize_scores(const FinalizeParams& f, int max_len, cudaStream_t st);
+
+// kivi_ops.cu
+cudaError_t launch_kivi_pack(const float* res_k, const float* res_v, uint8_t* qk, uint8_t* qv, int hkv, int d,
+                             int res_cap, int n_groups, int bits, long long k_block_start, long long v_block_start,
+                             cudaStream_t st);
+cudaError_t launch_kivi_dequant_flush(const uint8_t* q, __half* attn, int hkv, int d, int n, int tok_base,
+                                      long long block_start, int bits, int is_key, cudaStream_t st);
+cudaError_t launch_kivi_scatter_residual(const float* res, __half* attn, int hkv, int res_cap, int d, int res_pos,
+                                         int tok_base, cudaStream_t st);
+cudaError_t launch_kivi_gather_update(const float* in, float* res, int hkv, int res_cap, int d, int seq_len, int res_pos,
+                                      cudaStream_t st);
+// score_reduce.cu
+cudaError_t launch_score_fused_reduce(const float* scores, float* importance, float* head_importance, float decay,
+                                      int n_layers, int hq, int hkv, int T, long long stride, long long max_seq,
+                                      cudaStream_t st);
+cudaError_t launch_score_reduce_per_layer(const float* scores, float* layer_flat, float decay, int n_layers, int hq,
+                                          int T, long long stride, long long max_seq, cudaStream_t st);
+// decode_kivi.cu
+cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int head_dim, int bits, int n_items,
+                               cudaStream_t st);
 
 }  // namespace argus

@@ -1,0 +1,150 @@
+// Shared tail of the split-KV decode kernels: merge the warps of a CTA, publish the CTA's partial, and let
+// the last CTA of a (sequence, KV head) merge all splits. Same algebra as the reference's chunk merge
+// (engine/src/backend/cpu/neon.rs:1028-1125): M = max m_c, L = sum exp(m_c-M) l_c, O = sum exp(m_c-M) O_c,
+// out = O / L, here in the log2 domain.
+#pragma once
+#include "decode_params.h"
+#include "ptx.cuh"
+
+namespace argus {
+
+template <int D, int WARPS>
+struct EpilogueSmem {
+    static constexpr int O_OFF = 0;                              // float [WARPS][8][D]
+    static constexpr int ML_OFF = WARPS * 8 * D * 4;             // float2 [WARPS][8]
+    static constexpr int FLAG_OFF = ML_OFF + WARPS * 8 * 8;      // int
+    static constexpr int WARP_MERGE_B = FLAG_OFF + 128;
+    static constexpr int SPLIT_MERGE_B = kMaxSplits * 8 * 8 + 8 * 8;   // (m,l) table + totals
+    static constexpr int BYTES = WARP_MERGE_B > SPLIT_MERGE_B ? WARP_MERGE_B : SPLIT_MERGE_B;
+};
+
+// Precondition: every warp has stored its un-normalised O tile at smem[O_OFF] as [warp][8][D] and its
+// (running max, sum) at smem[ML_OFF] as [warp][8], followed by __syncthreads().
+// item  = index of this CTA's partial, item0 = partial of split 0 of the same (sequence, KV head);
+// consecutive splits are p.hkv partials apart.
+template <int D, int WARPS>
+__device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParams& p, int b, int kv, int64_t item,
+                                                int64_t item0, int n_splits) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* sm_o = reinterpret_cast<float*>(smem + EpilogueSmem<D, WARPS>::O_OFF);
+    float2* sm_ml = reinterpret_cast<float2*>(smem + EpilogueSmem<D, WARPS>::ML_OFF);
+    int* sm_flag = reinterpret_cast<int*>(smem + EpilogueSmem<D, WARPS>::FLAG_OFF);
+    for (int e = threadIdx.x; e < p.group * D; e += WARPS * 32) {
+        const int h = e / D, d = e % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_ml[w * 8 + h].x);
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float2 ml = sm_ml[w * 8 + h];
+            const float f = fast_exp2(ml.x - Mu);
+            L += f * ml.y;
+            acc += f * sm_o[(w * 8 + h) * D + d];
+        }
+        if (n_splits == 1) {
+            const int64_t oh = (int64_t)b * p.hq + kv * p.group + h;
+            p.out[oh * D + d] = (L > 0.f) ? acc / L : 0.f;
+            if (d == 0) {
+                const float l2 = (L > 0.f) ? M + log2f(L) : -INFINITY;
+                if (p.lse != nullptr) p.lse[oh] = l2 * 0.6931471805599453f;
+                if (p.lse2 != nullptr) p.lse2[oh] = l2;
+            }
+        } else {
+            p.part_o[(item * 8 + h) * D + d] = acc;
+            if (d == 0) p.part_ml[item * 8 + h] = make_float2(M, L);
+        }
+    }
+    if (n_splits == 1) return;
+
+    // ── ticket: the last split of this (sequence, KV head) merges all of them ──
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(&p.tickets[b * p.hkv + kv], 1);
+        *sm_flag = (prev == n_splits - 1);
+    }
+    __syncthreads();
+    if (*sm_flag == 0) return;
+    __threadfence();
+
+    // All (max, sum) pairs of this (sequence, KV head) come into shared memory once; everything else
+    // is computed from there. The planner keeps n_splits <= kMaxSplits.
+    float2* sm_pm = reinterpret_cast<float2*>(smem);                       // [n_splits][8]
+    float2* sm_ML = reinterpret_cast<float2*>(smem + kMaxSplits * 8 * 8);  // [8]
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_splits * 8; idx += WARPS * 32) {
+        const int s = idx >> 3, h = idx & 7;
+        sm_pm[idx] = (h < p.group) ? __ldcg(&p.part_ml[(item0 + (int64_t)s * p.hkv) * 8 + h]) : make_float2(-INFINITY, 0.f);
+    }
+    __syncthreads();
+    for (int h = warp; h < p.group; h += WARPS) {
+        float M = -INFINITY;
+        for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, sm_pm[s * 8 + h].x);
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+        const float Mu = (M == -INFINITY) ? 0.f : M;
+        float L = 0.f;
+        for (int s = lane; s < n_splits; s += 32) {
+            const float2 ml = sm_pm[s * 8 + h];
+            const float f = fast_exp2(ml.x - Mu);
+            L += f * ml.y;
+            sm_pm[s * 8 + h].x = f;   // the max is no longer needed: keep the rescale factor instead
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) L += __shfl_xor_sync(0xffffffffu, L, sh);
+        if (lane == 0) sm_ML[h] = make_float2(M, L);
+    }
+    __syncthreads();
+    // out = sum_s f_s * O_s / L with splits in ascending order (fixed order => run-to-run identical bits).
+    // Each thread owns float4 slices of the [group][D] tile and keeps 8 loads per slice in flight.
+    constexpr int V4 = (8 * D / 4) / (WARPS * 32);   // float4 slices per thread at the full group of 8
+    float4 acc[V4];
+#pragma unroll
+    for (int k = 0; k < V4; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int n_vec = p.group * D / 4;
+    const float4* po = reinterpret_cast<const float4*>(p.part_o + item0 * 8 * D);
+    const int64_t sstride = (int64_t)p.hkv * 8 * D / 4;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+        float4 v[V4][8];
+#pragma unroll
+        for (int k = 0; k < V4; ++k) {
+            const int e = threadIdx.x + k * WARPS * 32;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[k][u] = (e < n_vec && s0 + u < n_splits) ? __ldcg(po + (s0 + u) * sstride + e)
+                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < V4; ++k) {
+            const int e = threadIdx.x + k * WARPS * 32;
+            const int h = (e * 4) / D;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float f = (e < n_vec && s0 + u < n_splits) ? sm_pm[(s0 + u) * 8 + h].x : 0.f;
+                acc[k].x += f * v[k][u].x; acc[k].y += f * v[k][u].y;
+                acc[k].z += f * v[k][u].z; acc[k].w += f * v[k][u].w;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < V4; ++k) {
+        const int e = threadIdx.x + k * WARPS * 32;
+        if (e >= n_vec) continue;
+        const int h = (e * 4) / D, d = (e * 4) % D;
+        const float2 ML = sm_ML[h];
+        const float inv = (ML.y > 0.f) ? 1.0f / ML.y : 0.f;
+        const int64_t oh = (int64_t)b * p.hq + kv * p.group + h;
+        *reinterpret_cast<float4*>(p.out + oh * D + d) =
+            make_float4(acc[k].x * inv, acc[k].y * inv, acc[k].z * inv, acc[k].w * inv);
+        if (d == 0) {
+            const float l2 = (ML.y > 0.f) ? ML.x + log2f(ML.y) : -INFINITY;
+            if (p.lse != nullptr) p.lse[oh] = l2 * 0.6931471805599453f;
+            if (p.lse2 != nullptr) p.lse2[oh] = l2;
+        }
+    }
+    if (threadIdx.x == 0) p.tickets[b * p.hkv + kv] = 0;   // ready for the next call
+}
+
+}  // namespace argus

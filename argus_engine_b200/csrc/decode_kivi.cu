@@ -1,0 +1,433 @@
+// Split-KV GQA decode attention over a KIVI-packed KV cache (Q2/Q4/Q8 blocks + full-precision residual
+// window), sm_100a, with dequantisation fused into the tile load.
+//
+// Stands behind CudaQuantAttnBackend::attention_gen_quant (crates/argus-extension-api/src/lib.rs:3087-3104;
+// the kernels it replaces are kernel_attn_gen_kivi_q{2,4,8}, crates/techniques/kivi/src/kivi_attn.cu:34,220,403).
+// Cache layout is the engine's, unchanged (engine/src/kv/quant_window_cache.rs:919-946):
+//   K blocks [flush][kv_head][group of 32 tokens][channel]  — one block = 32 TOKENS of one channel
+//   V blocks [flush][kv_head][token][channel block of 32]   — one block = 32 CHANNELS of one token
+//   block = {f16 d, f16 m, codes}, value = code*d + m        (crates/argus-kv-codec/src/lib.rs:115-202)
+//   residual ring F32 (or F16) [kv_head][res_cap][D], token q_tokens + r is row r.
+//
+// Both the K and the V bytes of one (kv_head, 32-token group) are contiguous (D*block_bytes each), so a
+// warp tile is fetched with two bulk async copies (cp.async.bulk + mbarrier) and stays in the packed form
+// in shared memory. Lanes pull 4-token (resp. 4-channel) code pieces of the two channels (tokens) that one
+// MMA operand register pairs, widen them with the 0x6400 magic-number trick, apply {d, m} with one HFMA2,
+// and feed mma.sync. Tokens of a group are visited in a permuted order that makes those pieces contiguous;
+// softmax does not care and P·V uses the same order. The residual window is a separate split handled in
+// plain F32 FMA. Everything after the main loop (warp merge, split merge, score finalize) is shared with
+// the F16 kernel.
+#include "decode_epilogue.cuh"
+#include "decode_params.h"
+#include "ptx.cuh"
+
+namespace argus {
+
+template <int BITS>
+struct KvBlock {
+    static constexpr int BYTES = BITS == 2 ? 12 : BITS == 4 ? 20 : 36;
+    static constexpr int PIECE = BITS / 2;   // bytes holding 4 consecutive codes
+};
+
+// codes (exact small integers as F16 pairs) of position j (0..3) inside a pair of 4-code pieces:
+// x = piece(lo element) | piece(hi element) << 16 for BITS 2/4; for BITS 8 the two pieces come separately.
+template <int BITS>
+__device__ __forceinline__ __half2 codes_of(uint32_t xa, uint32_t xb, int j) {
+    uint32_t v;
+    if constexpr (BITS == 8) {
+        // bytes j of xa and xb -> low bytes of the two halves, exponent byte 0x64 above each
+        uint32_t t;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(xa), "r"(xb), "r"((uint32_t)j | ((uint32_t)(4 + j) << 4)));
+        // t = [xa.bj, xb.bj, xa.b0, xa.b0] -> spread to the low bytes of the two halves
+        asm("prmt.b32 %0, %1, %2, 0x7170;" : "=r"(v) : "r"(t), "r"(0x64646464u));
+    } else if constexpr (BITS == 4) {
+        v = ((xa >> (4 * j)) & 0x000F000Fu) | 0x64006400u;
+    } else {
+        v = ((xa >> (2 * j)) & 0x00030003u) | 0x64006400u;
+    }
+    const __half2 h = *reinterpret_cast<__half2*>(&v);
+    return __hsub2(h, __half2half2(__ushort_as_half(0x6400)));   // exact: (1024 + c) - 1024
+}
+
+__device__ __forceinline__ uint32_t deq_pair(__half2 codes, uint32_t d2, uint32_t m2) {
+    const __half2 r = __hfma2(codes, *reinterpret_cast<__half2*>(&d2), *reinterpret_cast<__half2*>(&m2));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+template <int BITS>
+__device__ __forceinline__ uint32_t load_piece(const uint8_t* p) {
+    if constexpr (BITS == 2) return *p;
+    else if constexpr (BITS == 4) return *reinterpret_cast<const uint16_t*>(p);
+    else return *reinterpret_cast<const uint32_t*>(p);
+}
+
+// mbarrier / bulk-copy helpers. Every wait is bounded.
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int D, int BITS, int WARPS, int STAGES>
+struct DecodeKiviCfg {
+    static constexpr int BB = KvBlock<BITS>::BYTES;
+    static constexpr int TILE_B = D * BB;             // K bytes (== V bytes) of one (kv head, 32-token group)
+    static constexpr int STAGE_B = 2 * TILE_B;
+    static constexpr int RING_B = WARPS * STAGES * STAGE_B;
+    static constexpr int KH_N = D / 2;                // {d2, m2} per channel pair
+    static constexpr int VH_N = 16 * (D / 32);        // {d2, m2} per (token pair, channel block)
+    static constexpr int HDR_B = WARPS * (KH_N + VH_N) * 8;
+    static constexpr int BAR_OFF = RING_B + HDR_B;
+    static constexpr int PIPE_B = BAR_OFF + WARPS * STAGES * 8;
+    static constexpr int EPI_B = EpilogueSmem<D, WARPS>::BYTES;
+    static constexpr int SMEM_B = PIPE_B > EPI_B ? PIPE_B : EPI_B;
+};
+
+template <int D, int BITS, int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, 2)
+decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ KiviBatch bt) {
+    using Cfg = DecodeKiviCfg<D, BITS, WARPS, STAGES>;
+    constexpr int BB = Cfg::BB, TILE_B = Cfg::TILE_B, STAGE_B = Cfg::STAGE_B, PIECE = KvBlock<BITS>::PIECE;
+    constexpr int KS = D / 16, NT = D / 8, NB = D / 32;
+    extern __shared__ __align__(128) uint8_t smem[];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int quad = lane >> 2, qlane = lane & 3;
+
+    const int kv = blockIdx.x % p.hkv;
+    const int gs = blockIdx.x / p.hkv;
+    int b = 0;
+    while (b + 1 < p.n_seqs && bt.item_start[b + 1] <= gs) ++b;
+    const int split = gs - bt.item_start[b];
+    const int n_splits = bt.item_start[b + 1] - bt.item_start[b];
+    const int n_qsplits = bt.n_qsplits[b];
+    const int q_tokens = bt.q_tokens[b];
+
+    float* sm_o = reinterpret_cast<float*>(smem + EpilogueSmem<D, WARPS>::O_OFF);
+    float2* sm_ml = reinterpret_cast<float2*>(smem + EpilogueSmem<D, WARPS>::ML_OFF);
+    const int64_t item = (int64_t)gs * p.hkv + kv;
+    const int64_t item0 = (int64_t)bt.item_start[b] * p.hkv + kv;
+
+    if (split >= n_qsplits) {
+        // ───────── residual window: plain F32, one token per warp step, lanes split the channels ─────────
+        constexpr int EPL = D / 32;   // channels per lane
+        const int r0 = (split - n_qsplits) * bt.res_chunk, r1 = min(r0 + bt.res_chunk, bt.res_tokens[b]);
+        float qreg[kMaxGroup][EPL], oacc[kMaxGroup][EPL], m_h[kMaxGroup], l_h[kMaxGroup];
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h) {
+            m_h[h] = -INFINITY;
+            l_h[h] = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                oacc[h][e] = 0.f;
+                qreg[h][e] = (h < p.group) ? p.q[((int64_t)b * p.hq + kv * p.group + h) * D + lane * EPL + e] * p.scale_log2 : 0.f;
+            }
+        }
+        for (int r = r0 + warp; r < r1; r += WARPS) {
+            float kr[EPL], vr[EPL];
+            const int64_t off = ((int64_t)kv * bt.res_cap + r) * D + lane * EPL;
+            if (bt.res_is_f16) {
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) {
+                    kr[e] = __half2float(static_cast<const __half*>(bt.res_k[b])[off + e]);
+                    vr[e] = __half2float(static_cast<const __half*>(bt.res_v[b])[off + e]);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) {
+                    kr[e] = static_cast<const float*>(bt.res_k[b])[off + e];
+                    vr[e] = static_cast<const float*>(bt.res_v[b])[off + e];
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < kMaxGroup; ++h) {
+                if (h >= p.group) break;
+                float s = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) s += qreg[h][e] * kr[e];
+#pragma unroll
+                for (int sh = 16; sh > 0; sh >>= 1) s += __shfl_xor_sync(0xffffffffu, s, sh);
+                if (p.logits != nullptr && lane == 0)
+                    p.logits[((int64_t)b * p.hq + kv * p.group + h) * p.logit_stride + q_tokens + r] = s;
+                const float m_new = fmaxf(m_h[h], s);
+                const float alpha = fast_exp2(m_h[h] - m_new);
+                const float pr = fast_exp2(s - m_new);
+                m_h[h] = m_new;
+                l_h[h] = l_h[h] * alpha + pr;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) oacc[h][e] = oacc[h][e] * alpha + pr * vr[e];
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) sm_o[(warp * 8 + h) * D + lane * EPL + e] = oacc[h][e];
+            if (lane == 0) sm_ml[warp * 8 + h] = make_float2(m_h[h], l_h[h]);
+        }
+        __syncthreads();
+        decode_epilogue<D, WARPS>(smem, p, b, kv, item, item0, n_splits);
+        return;
+    }
+
+    // ───────── packed part: 32-token groups, two bulk copies per warp tile ─────────
+    const int gpf = bt.res_cap / 32;                       // groups per flush
+    const int g0 = split * bt.chunk_groups[b];
+    const int g1 = min(g0 + bt.chunk_groups[b], q_tokens / 32);
+    const int n_tiles = g1 > g0 ? g1 - g0 : 0;
+    const int my_tiles = warp < n_tiles ? (n_tiles - warp + WARPS - 1) / WARPS : 0;
+    const uint8_t* qk = bt.qk[b];
+    const uint8_t* qv = bt.qv[b];
+
+    uint8_t* ring = smem + warp * STAGES * STAGE_B;
+    uint2* kh = reinterpret_cast<uint2*>(smem + Cfg::RING_B) + warp * (Cfg::KH_N + Cfg::VH_N);
+    uint2* vh = kh + Cfg::KH_N;
+    const uint32_t bar0 = smem_u32(smem + Cfg::BAR_OFF) + warp * STAGES * 8;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + s * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    auto issue = [&](int j, int slot) {   // lane 0 only
+        const int gidx = g0 + warp + j * WARPS;
+        const int f = gidx / gpf, gif = gidx - f * gpf;
+        const int64_t kblk = (((int64_t)f * p.hkv + kv) * gpf + gif) * D;
+        const int64_t vblk = (((int64_t)f * p.hkv + kv) * bt.res_cap + gif * 32) * NB;
+        const uint32_t dst = smem_u32(ring + slot * STAGE_B);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar0 + slot * 8, STAGE_B);
+        bulk_g2s(dst, qk + kblk * BB, TILE_B, bar0 + slot * 8);
+        bulk_g2s(dst + TILE_B, qv + vblk * BB, TILE_B, bar0 + slot * 8);
+    };
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s)
+            if (s < my_tiles) issue(s, s);
+    }
+
+    const int head = kv * p.group + quad;
+    const bool head_ok = quad < p.group;
+    uint32_t qf[KS][4];
+    {
+        const float* qp = p.q + ((int64_t)b * p.hq + (head_ok ? head : kv * p.group)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int c0 = ks * 16 + hf * 8 + qlane * 2;
+                float2 x = head_ok ? *reinterpret_cast<const float2*>(qp + c0) : make_float2(0.f, 0.f);
+                x.x *= p.scale_log2;
+                x.y *= p.scale_log2;
+                const uint32_t hi = pack_half2(x.x, x.y);
+                const float2 hif = unpack_half2(hi);
+                qf[ks][hf * 2 + 0] = hi;
+                qf[ks][hf * 2 + 1] = pack_half2(x.x - hif.x, x.y - hif.y);
+            }
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    float* logit_row = nullptr;
+    if (p.logits != nullptr && head_ok) logit_row = p.logits + ((int64_t)b * p.hq + head) * p.logit_stride;
+    bool timed_out = false;
+
+    for (int j = 0; j < my_tiles; ++j) {
+        const int slot = j % STAGES;
+        if (!mbar_wait(bar0 + slot * 8, (j / STAGES) & 1)) {
+            timed_out = true;
+            break;
+        }
+        __syncwarp();   // everyone is past tile j-1: its slot may be refilled, and the header tables rewritten
+        if (lane == 0) {
+            const int jn = j + STAGES - 1;
+            if (jn < my_tiles) issue(jn, jn % STAGES);
+        }
+        const uint8_t* kt = ring + slot * STAGE_B;
+        const uint8_t* vt = kt + TILE_B;
+
+        // {d,d} / {m,m'} tables of the element pairs that share an MMA operand register
+        for (int i = lane; i < Cfg::KH_N; i += 32) {
+            const uint32_t h0 = *reinterpret_cast<const uint32_t*>(kt + (2 * i) * BB);
+            const uint32_t h1 = *reinterpret_cast<const uint32_t*>(kt + (2 * i + 1) * BB);
+            kh[i] = make_uint2(__byte_perm(h0, h1, 0x5410), __byte_perm(h0, h1, 0x7632));
+        }
+        for (int i = lane; i < Cfg::VH_N; i += 32) {
+            const int blk = i >> 4, tl = i & 15;
+            const int t = 8 * (tl >> 2) + (tl & 3);   // pairs (t, t+4)
+            const uint32_t h0 = *reinterpret_cast<const uint32_t*>(vt + (t * NB + blk) * BB);
+            const uint32_t h1 = *reinterpret_cast<const uint32_t*>(vt + ((t + 4) * NB + blk) * BB);
+            vh[i] = make_uint2(__byte_perm(h0, h1, 0x5410), __byte_perm(h0, h1, 0x7632));
+        }
+        __syncwarp();
+
+        // S[head][token]: MMA column `quad` of n-tile jp is token 4*quad + jp of the group
+        float c[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int cha = ks * 16 + 2 * qlane;
+            const uint2 ha = kh[cha >> 1], hb = kh[(cha >> 1) + 4];
+            const uint8_t* pk = kt + cha * BB + 4 + PIECE * quad;
+            uint32_t xa0 = load_piece<BITS>(pk), xa1 = load_piece<BITS>(pk + BB);
+            uint32_t xb0 = load_piece<BITS>(pk + 8 * BB), xb1 = load_piece<BITS>(pk + 9 * BB);
+            if constexpr (BITS != 8) {
+                xa0 |= xa1 << 16;
+                xb0 |= xb1 << 16;
+            }
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                const uint32_t b0 = deq_pair(codes_of<BITS>(xa0, xa1, jp), ha.x, ha.y);
+                const uint32_t b1 = deq_pair(codes_of<BITS>(xb0, xb1, jp), hb.x, hb.y);
+                mma_f16_16816(c[jp], qf[ks], b0, b1);
+            }
+        }
+        // accumulator column 2*qlane+i of n-tile jp  <->  token 8*qlane + 4*i + jp of the group
+        const int tokb = (g0 + warp + j * WARPS) * 32;
+        float s[4][2];
+        float tile_max = -INFINITY;
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float x = c[jp][i] + c[jp][i + 2];
+                if (logit_row != nullptr) logit_row[tokb + 8 * qlane + 4 * i + jp] = x;
+                s[jp][i] = x;
+                tile_max = fmaxf(tile_max, x);
+            }
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+        const float m_new = fmaxf(m_run, tile_max);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = fast_exp2(m_run - m_use);
+        m_run = m_new;
+        float psum = 0.f;
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                s[jp][i] = fast_exp2(s[jp][i] - m_use);
+                psum += s[jp][i];
+            }
+        l_run = l_run * alpha + psum;
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                o[n][0] *= alpha; o[n][1] *= alpha; o[n][2] *= alpha; o[n][3] *= alpha;
+            }
+        }
+        // O[head][channel] += P · V. k-step u: A columns 2q+i <- n-tile 2u, 8+2q+i <- n-tile 2u+1, i.e.
+        // tokens (8q+2u, 8q+4+2u | 8q+2u+1, 8q+5+2u); MMA column `quad` of n-tile (blk, jc) is channel 32blk+4quad+jc.
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            uint32_t pa[4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const float p0 = s[2 * u + n][0], p1 = s[2 * u + n][1];
+                const uint32_t hi = pack_half2(p0, p1);
+                const float2 hif = unpack_half2(hi);
+                pa[n * 2 + 0] = hi;
+                pa[n * 2 + 1] = pack_half2(p0 - hif.x, p1 - hif.y);
+            }
+            const int ta = 8 * qlane + 2 * u;   // b0b1 pairs tokens (ta, ta+4), b2b3 pairs (ta+1, ta+5)
+#pragma unroll
+            for (int blk = 0; blk < NB; ++blk) {
+                const uint2 ha = vh[blk * 16 + qlane * 4 + 2 * u], hb = vh[blk * 16 + qlane * 4 + 2 * u + 1];
+                const uint8_t* pv = vt + (ta * NB + blk) * BB + 4 + PIECE * quad;
+                uint32_t xa0 = load_piece<BITS>(pv), xa1 = load_piece<BITS>(pv + 4 * NB * BB);
+                uint32_t xb0 = load_piece<BITS>(pv + NB * BB), xb1 = load_piece<BITS>(pv + 5 * NB * BB);
+                if constexpr (BITS != 8) {
+                    xa0 |= xa1 << 16;
+                    xb0 |= xb1 << 16;
+                }
+#pragma unroll
+                for (int jc = 0; jc < 4; ++jc) {
+                    const uint32_t b0 = deq_pair(codes_of<BITS>(xa0, xa1, jc), ha.x, ha.y);
+                    const uint32_t b1 = deq_pair(codes_of<BITS>(xb0, xb1, jc), hb.x, hb.y);
+                    mma_f16_16816(o[blk * 4 + jc], pa, b0, b1);
+                }
+            }
+        }
+    }
+    if (timed_out) {
+        // A copy never landed. Give every outstanding copy one more bounded chance to finish so that none is
+        // in flight when shared memory is reused, report through the status word, and contribute nothing.
+        for (int s = 0; s < STAGES; ++s) (void)mbar_wait(bar0 + s * 8, 0);
+        if (p.status != nullptr) atomicExch(p.status, 1);
+#pragma unroll
+        for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        m_run = -INFINITY;
+        l_run = 0.f;
+    }
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    __syncthreads();
+
+    // accumulator (n-tile blk*4+jc, column 2*qlane+i) is channel 32*blk + 8*qlane + 4*i + jc
+#pragma unroll
+    for (int blk = 0; blk < NB; ++blk)
+#pragma unroll
+        for (int jc = 0; jc < 4; ++jc)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int n = blk * 4 + jc;
+                sm_o[(warp * 8 + quad) * D + 32 * blk + 8 * qlane + 4 * i + jc] = o[n][i] + o[n][i + 2];
+            }
+    if (qlane == 0) sm_ml[warp * 8 + quad] = make_float2(m_run, l_run);
+    __syncthreads();
+    decode_epilogue<D, WARPS>(smem, p, b, kv, item, item0, n_splits);
+}
+
+template <int D, int BITS, int WARPS, int STAGES>
+static cudaError_t launch_kivi_t(const DecodeParams& p, const KiviBatch& bt, int n_items, cudaStream_t st) {
+    using Cfg = DecodeKiviCfg<D, BITS, WARPS, STAGES>;
+    static bool attr_done = false;
+    auto kern = decode_kivi_kernel<D, BITS, WARPS, STAGES>;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_B);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    kern<<<n_items * p.hkv, WARPS * 32, Cfg::SMEM_B, st>>>(p, bt);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int head_dim, int bits, int n_items,
+                               cudaStream_t st) {
+    if (head_dim == 128) {
+        if (bits == 4) return launch_kivi_t<128, 4, 4, 4>(p, bt, n_items, st);
+        if (bits == 8) return launch_kivi_t<128, 8, 4, 3>(p, bt, n_items, st);
+        if (bits == 2) return launch_kivi_t<128, 2, 4, 4>(p, bt, n_items, st);
+    } else if (head_dim == 64) {
+        if (bits == 4) return launch_kivi_t<64, 4, 4, 4>(p, bt, n_items, st);
+        if (bits == 8) return launch_kivi_t<64, 8, 4, 4>(p, bt, n_items, st);
+        if (bits == 2) return launch_kivi_t<64, 2, 4, 4>(p, bt, n_items, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace argus

@@ -22,6 +22,23 @@ struct DecodeBatch {
     int32_t item_start[kMaxBatch + 1];  // prefix sum of splits per sequence
 };
 
+// KIVI-packed sequences. Splits [0, n_qsplits[b]) of sequence b cover chunk_groups[b] 32-token groups of the
+// packed part each; the remaining splits cover res_chunk tokens of the residual window each.
+struct KiviBatch {
+    const uint8_t* qk[kMaxBatch];
+    const uint8_t* qv[kMaxBatch];
+    const void* res_k[kMaxBatch];   // [Hkv][res_cap][D] F32 or F16
+    const void* res_v[kMaxBatch];
+    int32_t q_tokens[kMaxBatch];
+    int32_t res_tokens[kMaxBatch];
+    int32_t chunk_groups[kMaxBatch];
+    int32_t n_qsplits[kMaxBatch];
+    int32_t item_start[kMaxBatch + 1];
+    int32_t res_cap;
+    int32_t res_chunk;
+    int32_t res_is_f16;
+};
+
 struct DecodeParams {
     const float* q;   // [B][Hq][D]
     float* out;       // [B][Hq][D]
@@ -36,6 +53,7 @@ struct DecodeParams {
     float* logits;    // nullable
     int64_t logit_stride;
     float* lse2;      // [B][Hq] log2-domain lse for the finalize kernel (nullable unless logits set)
+    int* status;      // set to 1 by a kernel whose bounded wait ran out (nullable)
 };
 
 // Finalize: p = exp2(logit - lse2) and its reductions over the GQA group.

@@ -61,3 +61,70 @@ def config2(batch: int = 16, lo: int = 1024, hi: int = 8192) -> DecodeCase:
     k = [_normal_f16(rng, (8, t, 128)) for t in lens]
     v = [_normal_f16(rng, (8, t, 128)) for t in lens]
     return DecodeCase(q, k, v, lens, 32, 8, 128)
+
+
+@dataclass
+class KiviCase:
+    """KIVI-packed sequences as the engine's container holds them (built by feeding the tokens through the
+    restated ring/flush logic). Per sequence: packed K/V bytes, F32 residual ring [Hkv,res_cap,D] and counts."""
+    q: np.ndarray                 # [B,Hq,D] f32
+    qk: List[np.ndarray]
+    qv: List[np.ndarray]
+    res_k: List[np.ndarray]
+    res_v: List[np.ndarray]
+    q_tokens: List[int]
+    res_tokens: List[int]
+    hq: int
+    hkv: int
+    d: int
+    res_cap: int
+    bits: int
+
+
+def kivi_case(seed: int, lens, hq: int, hkv: int, d: int, res_cap: int = 128, bits: int = 4,
+              outlier_frac: float = 0.01, outlier_scale: float = 8.0, res_f16: bool = False) -> KiviCase:
+    """Draw order per sequence: K [T,Hkv,D], V [T,Hkv,D], the outlier (kv_head, channel) set; q after all
+    sequences. `outlier_frac` of the Hkv*D K channels are multiplied by `outlier_scale` for every token.
+    The tokens go through the oracle's container, whose flush order defines the packed layout.
+    With res_f16 the residual rows are rounded to F16 (and kept as such in res_k/res_v)."""
+    from oracle import oracle as orc   # container logic is test infrastructure; workloads are inputs only
+
+    rng = _rng(seed)
+    out = KiviCase(None, [], [], [], [], [], [], hq, hkv, d, res_cap, bits)
+    for t in lens:
+        k = rng.standard_normal((t, hkv, d), dtype=np.float32)
+        v = rng.standard_normal((t, hkv, d), dtype=np.float32)
+        n_out = int(round(outlier_frac * hkv * d))
+        if n_out > 0:
+            idx = rng.choice(hkv * d, n_out, replace=False)
+            k.reshape(t, hkv * d)[:, idx] *= outlier_scale
+        c = orc.KiviCache(hkv, d, res_cap, bits)
+        c.update(k, v)
+        qk, qv, rk, rv = c.export()
+        if res_f16:
+            rk, rv = rk.astype(np.float16), rv.astype(np.float16)
+        out.qk.append(qk)
+        out.qv.append(qv)
+        out.res_k.append(rk)
+        out.res_v.append(rv)
+        out.q_tokens.append(c.q_tokens)
+        out.res_tokens.append(c.res_tokens)
+    out.q = rng.standard_normal((len(lens), hq, d), dtype=np.float32)
+    return out
+
+
+def config3(batch: int = 8, T: int = 32768, res_f16: bool = True) -> KiviCase:
+    """KIVI Q4 decode with H2O scores: B=8, Hq=32, Hkv=8, D=128, T=32768 (32640 packed + 128 residual), seed 2."""
+    return kivi_case(2, [T] * batch, 32, 8, 128, 128, 4, res_f16=res_f16)
+
+
+def kivi_bytes(case: KiviCase, with_head_scores: bool = True) -> int:
+    """Algorithmic bytes of one KIVI decode step: packed blocks + residual rows read once, q read, out
+    written, and the [Hkv,T] F32 group-mean score vector written."""
+    total = 0
+    for i in range(len(case.q_tokens)):
+        total += case.qk[i].nbytes + case.qv[i].nbytes
+        total += 2 * case.hkv * case.res_tokens[i] * case.d * case.res_k[i].itemsize
+        if with_head_scores:
+            total += case.hkv * (case.q_tokens[i] + case.res_tokens[i]) * 4
+    return total + 2 * len(case.q_tokens) * case.hq * case.d * 4

@@ -112,6 +112,122 @@ ARGUS_B200_API int argus_b200_attention_gen_batched(argus_b200_ctx* ctx, void* s
                                      int num_heads_q, int num_heads_kv, int head_dim, int kv_dtype,
                                      const argus_b200_decode_extras* extras);
 
+/* ───────────── KIVI capability: CudaQuantAttnBackend (crates/argus-extension-api/src/lib.rs:3087-3104) ─────────────
+ * The four structs below are byte-for-byte the #[repr(C)] PODs of the reference (same field order and
+ * types; usize = size_t, u64 device pointers, bool = uint8_t); the Rust FFI crate passes them through
+ * unchanged. All buffers are engine-owned and borrowed for the call. */
+
+/* CudaQuantAttnArgs, lib.rs:3000-3026 */
+typedef struct argus_b200_quant_attn_args {
+    void* cu_stream;      /* NULL = default stream */
+    uint64_t q_mem;       /* [Hq][D] F32 */
+    uint64_t qk_mem;      /* packed K blocks [flush][Hkv][group][ch] */
+    uint64_t qv_mem;      /* packed V blocks [flush][Hkv][token][D/32] */
+    uint64_t res_k_mem;   /* F32 residual [Hkv][res_cap][D] */
+    uint64_t res_v_mem;
+    uint64_t out_mem;     /* [Hq][D] F32 */
+    float* scores_out;    /* HOST pointer [Hq][scores_len/Hq], NULL = skip; filled when the call returns */
+    size_t scores_len;
+    size_t num_heads_q, num_heads_kv, head_dim, q_tokens, res_tokens, res_cap;
+    float scale;
+    uint8_t bits;         /* 2, 4 or 8 */
+} argus_b200_quant_attn_args;
+
+/* CudaQuantAttnGatherArgs, lib.rs:3031-3043 */
+typedef struct argus_b200_quant_gather_args {
+    void* cu_stream;
+    uint64_t input_mem;    /* [seq_len][Hkv][D] F32 */
+    uint64_t residual_mem; /* [Hkv][res_cap][D] F32, rows res_pos.. written */
+    size_t kv_heads, res_cap, head_dim, seq_len, res_pos;
+} argus_b200_quant_gather_args;
+
+/* CudaQuantDequantFlushArgs, lib.rs:3048-3063 */
+typedef struct argus_b200_quant_dequant_flush_args {
+    void* cu_stream;
+    uint64_t q_blocks_mem;
+    uint64_t attn_mem;     /* F16 SeqMajor view [max_seq][Hkv][D] */
+    size_t kv_heads, head_dim;
+    size_t n_groups_or_tokens; /* K: groups per flush; V: flush tokens */
+    size_t tok_base, block_start;
+    uint8_t bits;
+    uint8_t is_key;
+} argus_b200_quant_dequant_flush_args;
+
+/* CudaQuantScatterResidualArgs, lib.rs:3069-3081 */
+typedef struct argus_b200_quant_scatter_residual_args {
+    void* cu_stream;
+    uint64_t res_mem;      /* F32 ring */
+    uint64_t attn_mem;     /* F16 SeqMajor view */
+    size_t kv_heads, res_cap, head_dim, res_pos, tok_base;
+} argus_b200_quant_scatter_residual_args;
+
+/* has_quant_attn_kernel(bits): 1 for bits in {2,4,8}, else 0. */
+ARGUS_B200_API int argus_b200_kivi_has_quant_attn_kernel(const argus_b200_ctx* ctx, int bits);
+/* attention_gen_quant — replaces KiviCudaBackend::attention_inner (crates/techniques/kivi/src/gpu_kivi_cuda.rs:126-223)
+ * and kernel_attn_gen_kivi_q{2,4,8} (crates/techniques/kivi/src/kivi_attn.cu). No per-call allocation. */
+ARGUS_B200_API int argus_b200_kivi_attention_gen_quant(argus_b200_ctx* ctx, const argus_b200_quant_attn_args* args);
+/* gather_update_quant — kivi_gather_update (crates/techniques/kivi/src/kivi_q2.cu:117-138). */
+ARGUS_B200_API int argus_b200_kivi_gather_update_quant(argus_b200_ctx* ctx, const argus_b200_quant_gather_args* args);
+/* dequant_flush — kivi_dequantize_{key,value}_q2_f16 (kivi_q2.cu:19-91); the reference supports bits==2
+ * only (gpu_kivi_cuda.rs:254-257), this one 2, 4 and 8. */
+ARGUS_B200_API int argus_b200_kivi_dequant_flush(argus_b200_ctx* ctx, const argus_b200_quant_dequant_flush_args* args);
+/* scatter_residual — kivi_scatter_residual_f16 (kivi_q2.cu:93-115). */
+ARGUS_B200_API int argus_b200_kivi_scatter_residual(argus_b200_ctx* ctx,
+                                                    const argus_b200_quant_scatter_residual_args* args);
+
+/* Flush of the residual ring on the device: quantises n_groups*32 ring tokens into K blocks (order
+ * `for h, for group, for ch`) at block index k_block_start and V blocks (`for h, for tok, for blk`) at
+ * v_block_start — the work QuantizedRecentWindowCache::flush_residual does on the CPU before uploading
+ * (engine/src/kv/quant_window_cache.rs:844-965, :1688-1866), bit-exact with BlockQ2_0/BlockKVQ4/BlockKVQ8::quantize
+ * (crates/argus-kv-codec/src/lib.rs:36-73,125-157,175-202). res_k/res_v: F32 [Hkv][res_cap][D]. */
+ARGUS_B200_API int argus_b200_kivi_flush_pack(argus_b200_ctx* ctx, void* stream, const float* res_k,
+                                              const float* res_v, void* qk, void* qv, int kv_heads, int head_dim,
+                                              int res_cap, int n_groups, int bits, int64_t k_block_start,
+                                              int64_t v_block_start);
+
+/* One KIVI-packed sequence of a batched call. */
+typedef struct argus_b200_kivi_seq {
+    const void* qk;
+    const void* qv;
+    const void* res_k;  /* [Hkv][res_cap][D], F32 or F16 (see res_dtype) */
+    const void* res_v;
+    int64_t q_tokens;   /* multiple of res_cap */
+    int64_t res_tokens; /* <= res_cap */
+} argus_b200_kivi_seq;
+
+/* Fused dequant + decode over n_seqs packed sequences in one launch, with the optional outputs of
+ * argus_b200_decode_extras (device score matrices, fused GQA group means for H2O, lse). `scale` is
+ * applied to q·k as in CudaQuantAttnArgs. res_dtype: ARGUS_B200_KV_F32 (the engine's ring) or
+ * ARGUS_B200_KV_F16. q/out [n_seqs][Hq][D] F32. */
+ARGUS_B200_API int argus_b200_kivi_attention_batched(argus_b200_ctx* ctx, void* stream, const float* q,
+                                                     const argus_b200_kivi_seq* seqs, int n_seqs, float* out,
+                                                     int num_heads_q, int num_heads_kv, int head_dim, int res_cap,
+                                                     int bits, int res_dtype, float scale,
+                                                     const argus_b200_decode_extras* extras);
+
+/* ───────────── Score reducer: CudaScoreReduceBackend (lib.rs:2938-2948) ───────────── */
+
+/* CudaScoreReduceArgs, lib.rs:2909-2933 (byte-for-byte). */
+typedef struct argus_b200_score_reduce_args {
+    void* cu_stream;
+    uint64_t score_buf;        /* [n_layers][Hq][score_stride] post-softmax scores */
+    uint64_t importance;       /* [max_seq_len], in place */
+    uint64_t head_importance;  /* [Hkv * max_seq_len], in place */
+    float decay_factor;        /* 1 - decay, clamped to [0,1] by the engine */
+    size_t n_layers, n_heads_q, n_kv_heads, cache_seq_len, score_stride, max_seq_len;
+    uint64_t layer_flat_importance; /* [n_layers * max_seq_len], 0 when unused */
+} argus_b200_score_reduce_args;
+
+/* reduce — kernel_score_fused_reduce (crates/techniques/attn-score/src/score_reduce.cu:13-64); no
+ * 16-KV-head limit. */
+ARGUS_B200_API int argus_b200_score_reduce(argus_b200_ctx* ctx, const argus_b200_score_reduce_args* args);
+/* reduce_per_layer — kernel_score_fused_reduce_per_layer (score_reduce.cu:66-91). */
+ARGUS_B200_API int argus_b200_score_reduce_per_layer(argus_b200_ctx* ctx, const argus_b200_score_reduce_args* args);
+
+/* Blocks until `stream` is idle and returns the status word the kernels set when one of their bounded
+ * waits ran out (0 = clean). The word is cleared by the call. */
+ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

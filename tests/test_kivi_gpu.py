@@ -1,0 +1,240 @@
+"""GPU parity of the KIVI path through the C ABI: bit-exact pack/unpack and container kernels, and the
+fused dequant+decode kernel against the oracle's F32 view + three-pass attention.
+
+Tolerances: pack/unpack and data movement bit-exact; attention outputs max-abs 2e-3 / rel 1e-2; scores
+rel 1e-2 (absolute floor 1e-7).
+"""
+import numpy as np
+import pytest
+import torch
+
+from argus_engine_b200 import workloads as wl
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+OUT_ATOL, OUT_RTOL = 2e-3, 1e-2
+P_ATOL, P_RTOL = 1e-7, 1e-2
+
+
+@pytest.fixture(scope="module")
+def be():
+    from argus_engine_b200 import B200Backend
+
+    b = B200Backend(0)
+    yield b
+    b.close()
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _adversarial_ring(rng, hkv, rc, d):
+    """Values that stress the codec's rounding: .5 ties, constant groups, signed zeros, tiny and huge ranges."""
+    x = rng.standard_normal((hkv, rc, d)).astype(np.float32)
+    x[0, :, 0] = 3.25                       # constant channel: d == 0
+    x[0, :, 1] = np.arange(rc) % 16 + 0.5   # ties at .5 when the scale is 1
+    x[0, :, 2] = 0.0                        # all-zero channel (a group mixing +0 and -0 is left out: the sign of
+                                            # a zero minimum is unspecified by IEEE minNum, hence by f32::min)
+    x[0, :, 3] = rng.standard_normal(rc) * 1e-30
+    x[0, :, 4] = rng.standard_normal(rc) * 7e4   # min overflows F16 -> inf in the stored field, like the CPU
+    x[0, 0, :] = 1.0                        # constant token for V
+    x[0, 1, :32] = np.arange(32) * 0.5      # .5 ties along channels
+    return x
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("d,rc", [(128, 128), (64, 32), (128, 64)])
+def test_flush_pack_bit_exact(be, bits, d, rc):
+    """KIVI pack: device flush == CPU codec bytes (crates/argus-kv-codec/src/lib.rs), in flush order."""
+    hkv = 3
+    rng = np.random.default_rng(bits * 100 + d)
+    rk, rv = _adversarial_ring(rng, hkv, rc, d), _adversarial_ring(rng, hkv, rc, d)
+    c = orc.KiviCache(hkv, d, rc, bits)
+    seq = np.ascontiguousarray(rk.transpose(1, 0, 2)), np.ascontiguousarray(rv.transpose(1, 0, 2))
+    c.update(*seq)
+    c.update(seq[0][:1], seq[1][:1])   # the next write triggers the flush
+    want_k, want_v, _, _ = c.export()
+    bb = orc.block_bytes(bits)
+    pad = 5   # blocks of padding in front: the entry appends at a block offset
+    qk = torch.full((want_k.size + pad * bb,), 0xEE, dtype=torch.uint8, device="cuda")
+    qv = torch.full((want_v.size + pad * bb,), 0xEE, dtype=torch.uint8, device="cuda")
+    be.kivi_flush_pack(_dev(rk), _dev(rv), qk, qv, hkv, d, rc, rc // 32, bits, pad, pad)
+    torch.cuda.synchronize()
+    for name, got, want in (("K", qk, want_k), ("V", qv, want_v)):
+        got = got.cpu().numpy()[pad * bb:]
+        bad = np.flatnonzero(got != want)
+        assert bad.size == 0, f"{name}: {bad.size} bytes differ, first in block {bad[0] // bb} at byte {bad[0] % bb}: " \
+                              f"got {got[bad[0] // bb * bb:(bad[0] // bb + 1) * bb].tolist()} want " \
+                              f"{want[bad[0] // bb * bb:(bad[0] // bb + 1) * bb].tolist()}"
+    assert np.all(qk.cpu().numpy()[:pad * bb] == 0xEE)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_container_kernels_round_trip(be, bits):
+    """gather_update, dequant_flush and scatter_residual against the oracle's view
+    (the round trips of engine/src/bin/test_cuda_quant_attn_device.rs, cases C-E)."""
+    hkv, d, rc, T = 2, 64, 64, 64 * 2 + 17
+    rng = np.random.default_rng(bits)
+    k = rng.standard_normal((T, hkv, d)).astype(np.float32)
+    v = rng.standard_normal((T, hkv, d)).astype(np.float32)
+    c = orc.KiviCache(hkv, d, rc, bits)
+    c.update(k, v)
+    qk, qv, rk, rv = c.export()
+    vk, vv = orc.kivi_assemble_view(qk, qv, rk, rv, hkv, d, rc, bits, c.q_tokens, c.res_tokens)
+    # gather_update: rows land at res_pos.. of the ring, F32 exact
+    ring = torch.zeros(hkv, rc, d, device="cuda")
+    assert be.gather_update_quant(_dev(k[128:]), ring, hkv, rc, d, T - 128, 0) == 0
+    assert np.array_equal(ring.cpu().numpy()[:, :17], rk[:, :17])
+    assert be.gather_update_quant(_dev(k[:rc]), ring, hkv, rc, d, rc, 1) == -1   # would overflow the ring
+    # dequant_flush + scatter_residual build the F16 SeqMajor view
+    attn_k = torch.zeros(T, hkv, d, dtype=torch.float16, device="cuda")
+    attn_v = torch.zeros(T, hkv, d, dtype=torch.float16, device="cuda")
+    qkd, qvd = _dev(qk), _dev(qv)
+    kbpf, vbpf = hkv * (rc // 32) * d, hkv * rc * (d // 32)
+    for f in range(2):
+        assert be.dequant_flush(qkd, attn_k, hkv, d, rc // 32, f * rc, f * kbpf, bits, True) == 0
+        assert be.dequant_flush(qvd, attn_v, hkv, d, rc, f * rc, f * vbpf, bits, False) == 0
+    assert be.scatter_residual(_dev(rk), attn_k, hkv, rc, d, 17, 128) == 0
+    assert be.scatter_residual(_dev(rv), attn_v, hkv, rc, d, 17, 128) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(attn_k.cpu().numpy(), vk.astype(np.float16))
+    assert np.array_equal(attn_v.cpu().numpy(), vv.astype(np.float16))
+
+
+def _oracle_kivi(case, i, scale=None, scores=False):
+    hkv, d = case.hkv, case.d
+    rk, rv = case.res_k[i].astype(np.float32), case.res_v[i].astype(np.float32)
+    vk, vv = orc.kivi_assemble_view(case.qk[i], case.qv[i], rk, rv, hkv, d, case.res_cap, case.bits,
+                                    case.q_tokens[i], case.res_tokens[i])
+    T = case.q_tokens[i] + case.res_tokens[i]
+    q = case.q[i]
+    if scale is not None:   # the oracle applies 1/sqrt(D); fold any other scale into q
+        q = q * np.float32(scale * np.sqrt(d))
+    return orc.attention_gen(q, vk, vv, case.hq, hkv, d, T, head_major=False, want_scores=scores)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("d,g", [(128, 4), (64, 8), (128, 1)])
+@pytest.mark.parametrize("T", [5, 128, 133, 128 * 3, 128 * 5 + 77])
+def test_attention_gen_quant_vs_oracle(be, bits, d, g, T):
+    """The reference-shaped entry (CudaQuantAttnArgs): packed + residual, host score read-back."""
+    hkv = 2
+    case = wl.kivi_case(1000 + bits + T, [T], hkv * g, hkv, d, 128, bits)
+    want, want_p = _oracle_kivi(case, 0, scores=True)
+    out = torch.full((case.hq, d), float("nan"), device="cuda")
+    stride = T + 5
+    sc = torch.full((case.hq, stride), -1.0)
+    qk = _dev(case.qk[0]) if case.qk[0].size else None
+    qv = _dev(case.qv[0]) if case.qv[0].size else None
+    rc = be.attention_gen_quant(_dev(case.q[0]), qk, qv, _dev(case.res_k[0]), _dev(case.res_v[0]), out, case.hq, hkv, d,
+                                case.q_tokens[0], case.res_tokens[0], 128, 1.0 / np.sqrt(d), bits, scores_out=sc)
+    assert rc == 0
+    np.testing.assert_allclose(out.cpu().numpy(), want, atol=OUT_ATOL, rtol=OUT_RTOL)
+    np.testing.assert_allclose(sc.numpy()[:, :T], want_p, atol=P_ATOL, rtol=P_RTOL)
+    assert be.check_status() == 0
+
+
+def test_residual_only_matches_f64(be):
+    """Case A of the reference's device harness (engine/src/bin/test_cuda_quant_attn_device.rs:108-200):
+    no packed tokens, residual ring only, against a host F64 reference at 1e-4."""
+    hq, hkv, d, rt = 8, 2, 64, 20
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((hq, d)).astype(np.float32)
+    rk = np.zeros((hkv, 128, d), dtype=np.float32)
+    rv = np.zeros_like(rk)
+    rk[:, :rt] = rng.standard_normal((hkv, rt, d))
+    rv[:, :rt] = rng.standard_normal((hkv, rt, d))
+    out = torch.zeros(hq, d, device="cuda")
+    scale = 0.37   # an arbitrary scale: the entry takes it from the caller
+    assert be.attention_gen_quant(_dev(q), None, None, _dev(rk), _dev(rv), out, hq, hkv, d, 0, rt, 128, scale, 4) == 0
+    want = np.zeros((hq, d))
+    for h in range(hq):
+        s = rk[h // 4, :rt].astype(np.float64) @ q[h].astype(np.float64) * scale
+        p = np.exp(s - s.max())
+        want[h] = (p / p.sum()) @ rv[h // 4, :rt].astype(np.float64)
+    np.testing.assert_allclose(out.cpu().numpy(), want, atol=1e-4)
+
+
+def test_exactly_representable_q2_blocks(be):
+    """Case B of the same harness: Q2 blocks whose values are exact (codes 0..3, d=1, m=0)."""
+    hq, hkv, d = 4, 1, 64
+    T = 128
+    k = (np.arange(T * d).reshape(T, 1, d) % 4).astype(np.float32)
+    v = ((np.arange(T * d).reshape(T, 1, d) // 3) % 4).astype(np.float32)
+    c = orc.KiviCache(hkv, d, 128, 2)
+    c.update(k, v)
+    c.update(k[:1], v[:1])
+    qk, qv, rk, rv = c.export()
+    q = orc.lcg(hq * d, 5).reshape(hq, d) * 0.1
+    out = torch.zeros(hq, d, device="cuda")
+    assert be.attention_gen_quant(_dev(q), _dev(qk), _dev(qv), _dev(rk), _dev(rv), out, hq, hkv, d, 128, 1, 128,
+                                  1 / 8.0, 2) == 0
+    kk = np.concatenate([k, k[:1]])[:, 0].astype(np.float64)
+    vv = np.concatenate([v, v[:1]])[:, 0].astype(np.float64)
+    s = kk @ q.astype(np.float64).T / 8.0
+    p = np.exp(s - s.max(0))
+    want = (p / p.sum(0)).T @ vv
+    np.testing.assert_allclose(out.cpu().numpy(), want, atol=1e-3)
+
+
+@pytest.mark.parametrize("res_f16", [False, True])
+def test_batched_c3_shape_reduced(be, res_f16):
+    """configs[2] scaled down (B=3, T in {4224, 2048+128, 777}): Q4, 1% of K channels x8, fused H2O
+    group-mean vector [B,Hkv,T] and flat sums; F32 ring (engine) and F16 residual (benchmark wording)."""
+    from argus_engine_b200 import DecodeExtras
+
+    lens = [4224, 2176, 777]
+    case = wl.kivi_case(2, lens, 32, 8, 128, 128, 4, res_f16=res_f16)
+    B, stride = len(lens), 4352
+    seqs = [(_dev(case.qk[i]), _dev(case.qv[i]), _dev(case.res_k[i]), _dev(case.res_v[i]), case.q_tokens[i],
+             case.res_tokens[i]) for i in range(B)]
+    out = torch.full((B, 32, 128), float("nan"), device="cuda")
+    ex = DecodeExtras(head_scores=torch.zeros(B, 8, stride, device="cuda"), flat_scores=torch.zeros(B, stride, device="cuda"),
+                      score_stride=stride)
+    be.kivi_attention_batched(_dev(case.q), seqs, out, 32, 8, 128, 128, 4, 1 / np.sqrt(128), res_f16=res_f16, extras=ex)
+    torch.cuda.synchronize()
+    assert be.check_status() == 0
+    for i, T in enumerate(lens):
+        want, want_p = _oracle_kivi(case, i, scores=True)
+        np.testing.assert_allclose(out[i].cpu().numpy(), want, atol=OUT_ATOL, rtol=OUT_RTOL)
+        sf = np.zeros(stride, dtype=np.float32)
+        sh = np.zeros(8 * stride, dtype=np.float32)
+        orc.score_accumulate_layer(want_p, T, 32, 8, stride, sf, sh)
+        np.testing.assert_allclose(ex.head_scores[i].cpu().numpy()[:, :T], sh.reshape(8, stride)[:, :T], atol=P_ATOL,
+                                   rtol=P_RTOL)
+        np.testing.assert_allclose(ex.flat_scores[i].cpu().numpy()[:T], sf[:T], atol=P_ATOL, rtol=P_RTOL)
+        # eviction index selection on these scores is identical (heavy hitters are well separated here)
+        got_keep = orc.h2o_keep(T, 4, 64, 128, ex.flat_scores[i].cpu().numpy()[:T])
+        assert got_keep == orc.h2o_keep(T, 4, 64, 128, sf[:T])
+
+
+@pytest.mark.parametrize("case_id", [0, 1])
+def test_score_reduce_vs_oracle(be, case_id):
+    """CudaScoreReduceBackend: the hand-computed case of engine/src/bin/test_cuda_gpu_score_device.rs:36-118
+    and a random multi-layer case, bit-identical to the restated reference kernel."""
+    if case_id == 0:
+        L, hq, hkv, max_seq, T = 2, 2, 1, 8, 3
+        s = np.zeros((L, hq, max_seq), dtype=np.float32)
+        s[0, 0, :3], s[0, 1, :3] = [0.1, 0.2, 0.7], [0.3, 0.3, 0.4]
+        s[1, 0, :3], s[1, 1, :3] = [0.5, 0.4, 0.1], [0.2, 0.2, 0.6]
+    else:
+        L, hq, hkv, max_seq, T = 5, 32, 8, 700, 611
+        s = np.random.default_rng(0).random((L, hq, max_seq), dtype=np.float32)
+    sd = _dev(s)
+    imp = torch.zeros(max_seq, device="cuda")
+    himp = torch.zeros(hkv * max_seq, device="cuda")
+    lflat = torch.zeros(L * max_seq, device="cuda")
+    w_imp, w_himp, w_lf = np.zeros(max_seq, np.float32), np.zeros(hkv * max_seq, np.float32), np.zeros(L * max_seq, np.float32)
+    for decay in (1.0, 0.5):
+        assert be.score_reduce(sd, imp, himp, decay, L, hq, hkv, T, max_seq, max_seq) == 0
+        assert be.score_reduce_per_layer(sd, lflat, decay, L, hq, hkv, T, max_seq, max_seq) == 0
+        orc.score_fused_reduce(s, w_imp, w_himp, decay, L, hq, hkv, T, max_seq, max_seq)
+        orc.score_reduce_per_layer(s, w_lf, decay, L, hq, T, max_seq, max_seq)
+    torch.cuda.synchronize()
+    assert np.array_equal(imp.cpu().numpy(), w_imp)
+    assert np.array_equal(himp.cpu().numpy(), w_himp)
+    assert np.array_equal(lflat.cpu().numpy(), w_lf)
+    if case_id == 0:
+        np.testing.assert_allclose(w_imp[:3], 1.5 * np.array([0.7, 0.6, 1.1]), atol=1e-5)
