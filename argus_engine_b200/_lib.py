@@ -99,5 +99,6 @@ def load_library() -> C.CDLL:
     lib.argus_b200_score_reduce.argtypes = [vp, C.POINTER(ScoreReduceArgs)]
     lib.argus_b200_score_reduce_per_layer.argtypes = [vp, C.POINTER(ScoreReduceArgs)]
     lib.argus_b200_check_status.argtypes = [vp, vp]
+    lib.argus_b200_flash_attention_prefill.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i32, i32, i32]
     _lib = lib
     return lib

@@ -125,6 +125,29 @@ class B200Backend:
             self._h, self._stream(), q.data_ptr(), arr, n, out.data_ptr(), num_heads_q, num_heads_kv, head_dim, dt,
             self._extras(extras)))
 
+    # ── Backend::flash_attention_prefill ──
+    def flash_attention_prefill(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                                n_heads_q: int, n_heads_kv: int, seq_len: int, cache_seq_len: int, head_dim: int,
+                                kv_capacity: int, batch_size: int, is_head_major: bool) -> bool:
+        """Argument list of the reference trait method (engine/src/backend.rs:1011-1027). Returns True when the
+        GPU kernel handled the call, False when it declines (the reference's ``Ok(false)``); errors raise.
+        dtype mode follows the tensors: F32 Q + F16 K/V + F32 out (the engine's), all-BF16, or all-F16."""
+        if q.dtype == torch.float32 and k_cache.dtype == torch.float16 and out.dtype == torch.float32:
+            mode = 0
+        elif q.dtype == k_cache.dtype == out.dtype == torch.bfloat16:
+            mode = 1
+        elif q.dtype == k_cache.dtype == out.dtype == torch.float16:
+            mode = 2
+        else:
+            return False
+        rc = self._lib.argus_b200_flash_attention_prefill(
+            self._h, self._stream(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), n_heads_q,
+            n_heads_kv, seq_len, cache_seq_len, head_dim, kv_capacity, batch_size, int(bool(is_head_major)), mode)
+        if rc == -2:
+            return False
+        self._check(rc)
+        return True
+
     # ── CudaQuantAttnBackend (crates/argus-extension-api/src/lib.rs:3087-3104) ──
     def has_quant_attn_kernel(self, bits: int) -> bool:
         return bool(self._lib.argus_b200_kivi_has_quant_attn_kernel(self._h, bits))

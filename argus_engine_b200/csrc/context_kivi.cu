@@ -319,6 +319,60 @@ int argus_b200_score_reduce_per_layer(argus_b200_ctx* ctx, const argus_b200_scor
     return reduce_common(ctx, a, true);
 }
 
+int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void* stream, const void* q, const void* k_cache,
+                                       const void* v_cache, void* out, int n_heads_q, int n_heads_kv, int seq_len,
+                                       int cache_seq_len, int head_dim, int64_t kv_capacity, int batch_size,
+                                       int is_head_major, int dtype_mode) {
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    Context* c = C_(ctx);
+    c->err[0] = 0;
+    if (!q || !k_cache || !v_cache || !out || n_heads_q <= 0 || n_heads_kv <= 0 || n_heads_q % n_heads_kv != 0 ||
+        seq_len <= 0 || cache_seq_len < seq_len || kv_capacity < cache_seq_len || batch_size <= 0 || dtype_mode < 0 ||
+        dtype_mode > 2) {
+        c->set_error("flash_attention_prefill: bad arguments (S=%d T=%d cap=%lld B=%d)", seq_len, cache_seq_len,
+                     (long long)kv_capacity, batch_size);
+        return ARGUS_B200_E_INVALID;
+    }
+    if (head_dim != 128) {
+        c->set_error("flash_attention_prefill: head_dim %d is declined (128 only)", head_dim);
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+         reinterpret_cast<uintptr_t>(out)) & 15) {
+        c->set_error("flash_attention_prefill: pointers must be 16-byte aligned");
+        return ARGUS_B200_E_INVALID;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const void* q16 = q;
+    if (dtype_mode == ARGUS_B200_PREFILL_F32Q_F16KV) {
+        const long long n = (long long)batch_size * seq_len * n_heads_q * head_dim;
+        size_t cur = 0;
+        float* buf = c->scratch(&cur, (size_t)n * 2);
+        if (!buf) {
+            c->set_error("flash_attention_prefill: %lld bytes of scratch needed for the F16 copy of Q", n * 2);
+            return ARGUS_B200_E_WORKSPACE;
+        }
+        cudaError_t e = argus::launch_cast_f32_to_f16(static_cast<const float*>(q), buf, n, st);
+        if (e != cudaSuccess) return c->cuda_fail(e, "q cast launch");
+        c->launches += 1;
+        q16 = buf;
+    }
+    const int64_t pos_stride = is_head_major ? head_dim : (int64_t)n_heads_kv * head_dim;
+    const int64_t head_stride = is_head_major ? kv_capacity * head_dim : head_dim;
+    const int64_t batch_stride = kv_capacity * n_heads_kv * head_dim;
+    cudaError_t e = argus::launch_prefill_tc(q16, k_cache, v_cache, out, dtype_mode == ARGUS_B200_PREFILL_BF16,
+                                             dtype_mode == ARGUS_B200_PREFILL_F32Q_F16KV, batch_size, seq_len,
+                                             cache_seq_len, n_heads_q, n_heads_kv, cache_seq_len, pos_stride, head_stride,
+                                             batch_stride, c->status, st);
+    if (e == cudaErrorNotSupported) {
+        c->set_error("flash_attention_prefill: the driver does not export cuTensorMapEncodeTiled");
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    if (e != cudaSuccess) return c->cuda_fail(e, "prefill launch");
+    c->launches += 1;
+    return ARGUS_B200_OK;
+}
+
 int argus_b200_check_status(argus_b200_ctx* ctx, void* stream) {
     if (!ctx) return ARGUS_B200_E_INVALID;
     Context* c = C_(ctx);

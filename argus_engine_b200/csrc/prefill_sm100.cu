@@ -1,0 +1,487 @@
+// Causal GQA flash-attention prefill on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), sm_100a.
+//
+// Stands behind Backend::flash_attention_prefill (engine/src/backend.rs:1011-1027; CUDA implementation
+// engine/src/backend/cuda_pc.rs:830-926 with flash_attn_prefill_f16kv_dk128, engine/src/backend/cuda_pc/
+// kernels.cu:691-816). Same contract: Q/O [B][S][Hq][D], K/V HeadMajor [B][Hkv][cap][D], query row r sees
+// keys <= cache_seq_len - seq_len + r, rows without a visible key produce zeros. The reference runs one
+// thread per query row with scalar FMAs; here one CTA owns a 128-row query tile of one head:
+//
+//   warp 0      TMA producer: Q once, then K and V tiles of 128 keys (two stages each), 128B-swizzled boxes
+//   warp 1      one elected thread issues tcgen05.mma: S = Q·K^T (M128 N128 K16 x8) into one of two TMEM
+//               buffers, then O += P·V (V is the MN-major B operand) into a third TMEM region
+//   warps 2..5  softmax: each thread owns one query row = one TMEM lane. tcgen05.ld of the S row, running
+//               max in the log2 domain with a lazy rescale (O is only rescaled when the max grew by more
+//               than 2^8, as the exact algebra allows), exp2, P as 16-bit into 128B-swizzled shared
+//               memory for the second MMA, and finally O/l to global memory.
+//
+// S_{j+1} is issued before P_j is awaited, so the tensor pipe computes the next logits while the softmax
+// warps work on the current ones. Every mbarrier wait is bounded; a wait that runs out raises the status
+// word, makes every role leave its loop, and the CTA still frees its TMEM.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace argus {
+
+struct PrefillParams {
+    void* out;          // [B][S][Hq][D] 16-bit (same type as Q) or F32
+    int B, S, T, hq, hkv, group;
+    int n_qtiles;
+    float scale_log2;
+    int* status;
+};
+
+namespace pf {
+
+constexpr int BM = 128, BN = 128, D = 128;
+constexpr int TILE_B = BM * D * 2;          // 32 KB: one Q/K/V/P tile of 16-bit elements
+constexpr int HALF_B = TILE_B / 2;          // one 64-column (128-byte wide) swizzled block of a tile
+constexpr int KV_STAGES = 2;
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + TILE_B;
+constexpr int OFF_V = OFF_K + KV_STAGES * TILE_B;
+constexpr int OFF_P = OFF_V + KV_STAGES * TILE_B;
+constexpr int OFF_BAR = OFF_P + 2 * TILE_B;   // 224 KB
+constexpr int N_BAR = 1 + 4 * KV_STAGES + 8 + 1;
+constexpr int SMEM_B = OFF_BAR + N_BAR * 8 + 16 + 1024;   // + TMEM base slot + alignment slack
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TM_S0 = 0, TM_S1 = 128, TM_O = 256;
+constexpr float LAZY = 8.0f;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: returns false when the phase did not complete within the iteration limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int it = 0; it < (1 << 24); ++it) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,"
+        "%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format: version 1 at bit 46, layout type SWIZZLE_128B = 2 at bit 61).
+// Offsets are in 16-byte units.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: F32 accumulate, A/B format (0 = F16, 1 = BF16), B major, N, M.
+__host__ __device__ constexpr uint32_t instr_desc(int fmt, int b_mn_major, int M, int N) {
+    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float a, float b) {
+    if constexpr (BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    } else {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+}
+
+}  // namespace pf
+
+template <bool BF16, bool OUT_F32>
+__global__ void __launch_bounds__(192, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ PrefillParams p) {
+    using namespace pf;
+    extern __shared__ uint8_t smem_raw[];
+    // 128B-swizzled tiles need 1024-byte alignment
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (smem0 - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // barrier map
+    const uint32_t bar = smem0 + OFF_BAR;
+    const uint32_t b_qfull = bar;
+    auto b_kfull = [&](int s) { return bar + 8 * (1 + s); };
+    auto b_kempty = [&](int s) { return bar + 8 * (1 + KV_STAGES + s); };
+    auto b_vfull = [&](int s) { return bar + 8 * (1 + 2 * KV_STAGES + s); };
+    auto b_vempty = [&](int s) { return bar + 8 * (1 + 3 * KV_STAGES + s); };
+    const uint32_t bar2 = bar + 8 * (1 + 4 * KV_STAGES);
+    auto b_sfull = [&](int s) { return bar2 + 8 * s; };
+    auto b_sempty = [&](int s) { return bar2 + 8 * (2 + s); };
+    auto b_pfull = [&](int s) { return bar2 + 8 * (4 + s); };
+    auto b_pempty = [&](int s) { return bar2 + 8 * (6 + s); };
+    const uint32_t b_ofull = bar2 + 8 * 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + N_BAR * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_BAR + N_BAR * 8 + 8);
+
+    // work item: long query tiles first (they see the most keys); heads of one KV group are adjacent CTAs
+    const int qt = p.n_qtiles - 1 - (int)(blockIdx.x / (p.hq * p.B));
+    const int hb = blockIdx.x % (p.hq * p.B);
+    const int h = hb % p.hq, b = hb / p.hq;
+    const int kvh = h / p.group;
+    const int r0 = qt * BM;
+    const int q_start = p.T - p.S;                         // global position of query row 0
+    const int kv_end = min(p.T, q_start + r0 + BM);        // keys [0, kv_end) can be visible to this tile
+    const int n_tiles = (kv_end + BN - 1) / BN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(b_qfull, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(b_kfull(s), 1);
+            mbar_init(b_kempty(s), 1);
+            mbar_init(b_vfull(s), 1);
+            mbar_init(b_vempty(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(b_sfull(s), 1);
+            mbar_init(b_sempty(s), 128);
+            mbar_init(b_pfull(s), 128);
+            mbar_init(b_pempty(s), 1);
+        }
+        mbar_init(b_ofull, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem0 + OFF_BAR + N_BAR * 8),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    auto fail = [&]() {
+        *abort_flag = 1;
+        if (p.status != nullptr) atomicExch(p.status, 2);
+    };
+
+    if (warp == 0) {
+        // ───────── TMA producer ─────────
+        if (lane == 0) {
+            mbar_expect_tx(b_qfull, TILE_B);
+            tma_load_4d(smem0 + OFF_Q, &tm_q, b_qfull, 0, r0, h, b);
+            tma_load_4d(smem0 + OFF_Q + HALF_B, &tm_q, b_qfull, 64, r0, h, b);
+            for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
+                const int s = j % KV_STAGES;
+                const uint32_t ph = (j / KV_STAGES) & 1;
+                if (j >= KV_STAGES && !mbar_wait(b_kempty(s), ph ^ 1)) { fail(); break; }
+                mbar_expect_tx(b_kfull(s), TILE_B);
+                tma_load_4d(smem0 + OFF_K + s * TILE_B, &tm_k, b_kfull(s), 0, j * BN, kvh, b);
+                tma_load_4d(smem0 + OFF_K + s * TILE_B + HALF_B, &tm_k, b_kfull(s), 64, j * BN, kvh, b);
+                if (j >= KV_STAGES && !mbar_wait(b_vempty(s), ph ^ 1)) { fail(); break; }
+                mbar_expect_tx(b_vfull(s), TILE_B);
+                tma_load_4d(smem0 + OFF_V + s * TILE_B, &tm_v, b_vfull(s), 0, j * BN, kvh, b);
+                tma_load_4d(smem0 + OFF_V + s * TILE_B + HALF_B, &tm_v, b_vfull(s), 64, j * BN, kvh, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ───────── MMA issuer ─────────
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc(BF16 ? 1 : 0, 0, BM, BN);   // K tile is K-major
+            // A and B of one kind::f16 MMA must have the same format: an F16 P against a BF16 V faulted on B200.
+            constexpr uint32_t idesc_o = instr_desc(BF16 ? 1 : 0, 1, BM, D);    // V tile is MN-major
+            bool ok = mbar_wait(b_qfull, 0);
+            if (!ok) fail();
+            auto issue_pv = [&](int i) -> bool {
+                const int s = i % KV_STAGES, pb = i & 1;
+                if (!mbar_wait(b_pfull(pb), (i >> 1) & 1)) return false;
+                if (!mbar_wait(b_vfull(s), (i / KV_STAGES) & 1)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k) {
+                    // A = P: K-major, 16 keys = 32 bytes inside the 128-byte swizzle row, second 64-key block +16 KB
+                    const uint32_t pa = smem0 + OFF_P + pb * TILE_B + (k >> 2) * HALF_B + (k & 3) * 32;
+                    // B = V: MN-major. d runs along the 128-byte rows (two 64-d blocks, LBO = 16 KB apart),
+                    // 8 keys per 1024-byte group (SBO); one k-step = 16 keys = 2048 bytes.
+                    const uint32_t va = smem0 + OFF_V + s * TILE_B + k * 2048;
+                    tc_mma(tmem + TM_O, smem_desc(pa, 16, 1024), smem_desc(va, HALF_B, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tc_commit(b_pempty(pb));
+                tc_commit(b_vempty(s));
+                return true;
+            };
+            for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
+                const int s = j % KV_STAGES, sb = j & 1;
+                ok = mbar_wait(b_kfull(s), (j / KV_STAGES) & 1);
+                if (ok && j >= 2) ok = mbar_wait(b_sempty(sb), ((j >> 1) & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t qa = smem0 + OFF_Q + (k >> 2) * HALF_B + (k & 3) * 32;
+                    const uint32_t ka = smem0 + OFF_K + s * TILE_B + (k >> 2) * HALF_B + (k & 3) * 32;
+                    tc_mma(tmem + (sb ? TM_S1 : TM_S0), smem_desc(qa, 16, 1024), smem_desc(ka, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+                }
+                tc_commit(b_sfull(sb));
+                tc_commit(b_kempty(s));
+                if (j > 0) ok = issue_pv(j - 1);
+            }
+            if (ok && !*abort_flag && n_tiles > 0) ok = issue_pv(n_tiles - 1);
+            if (ok) tc_commit(b_ofull);
+            else fail();
+        }
+    } else {
+        // ───────── softmax / correction / epilogue: one query row per thread ─────────
+        const int quarter = warp & 3;                       // TMEM lanes this warp may touch
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const int qi = q_start + r0 + row;                  // global position of this query row
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int sb = j & 1;
+            if (*abort_flag || !mbar_wait(b_sfull(sb), (j >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sv[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_addr + (sb ? TM_S1 : TM_S0) + c * 32, sv[c]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(b_sempty(sb));
+            const bool diag = (j * BN + BN - 1 > q_start + r0);   // some key of this tile may be masked
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __uint_as_float(sv[c][i]);
+                    if (diag && (j * BN + c * 32 + i > qi)) x = -INFINITY;
+                    sv[c][i] = __float_as_uint(x);
+                    mx = fmaxf(mx, x);
+                }
+            const float m_tile = mx * p.scale_log2;
+            float alpha = 1.f;
+            if (m_tile > m_ref + LAZY) {                    // also the first tile (m_ref = -inf)
+                alpha = fast_exp2(m_ref - m_tile);
+                m_ref = m_tile;
+            }
+            // O rescale (rare after the first tiles): needs PV_{j-1} complete
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                if (!mbar_wait(b_pempty((j - 1) & 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem + lane_addr + TM_O + c * 32, ov);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+                    tmem_st32(tmem + lane_addr + TM_O + c * 32, ov);
+                }
+                tmem_wait_st();
+            }
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            float psum = 0.f;
+            // P buffer j&1 was last read by PV_{j-2}
+            if (j >= 2 && !mbar_wait(b_pempty(sb), ((j >> 1) & 1) ^ 1)) { ok = false; break; }
+            uint8_t* prow = smem + OFF_P + sb * TILE_B + row * 128;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) {            // 8 keys = one 16-byte chunk
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][q8 * 8 + 2 * e]), p.scale_log2, neg_m));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][q8 * 8 + 2 * e + 1]), p.scale_log2, neg_m));
+                        psum += p0 + p1;
+                        w[e] = pack16<BF16>(p0, p1);
+                    }
+                    const int chunk = c * 4 + q8;            // 0..15 over 128 keys
+                    uint8_t* dst = prow + (chunk >> 3) * HALF_B + (((chunk & 7) ^ (row & 7)) << 4);
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            l = l * alpha + psum;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(b_pfull(sb));
+        }
+        // epilogue
+        if (ok && n_tiles > 0 && !*abort_flag) ok = mbar_wait(b_ofull, 0);
+        if (!ok) fail();
+        tc_fence_after();
+        const bool row_ok = (r0 + row) < p.S;
+        const float inv_l = (ok && l > 0.f) ? 1.0f / l : 0.f;
+        const int64_t obase = (((int64_t)b * p.S + r0 + row) * p.hq + h) * D;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t ov[32];
+            if (ok && n_tiles > 0) {
+                tmem_ld32(tmem + lane_addr + TM_O + c * 32, ov);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) ov[i] = 0;
+            }
+            if (row_ok) {
+                if constexpr (OUT_F32) {
+                    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + obase + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        dst[i] = make_float4(__uint_as_float(ov[4 * i]) * inv_l, __uint_as_float(ov[4 * i + 1]) * inv_l,
+                                             __uint_as_float(ov[4 * i + 2]) * inv_l, __uint_as_float(ov[4 * i + 3]) * inv_l);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + obase + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            w[e] = pack16<BF16>(__uint_as_float(ov[8 * i + 2 * e]) * inv_l,
+                                                __uint_as_float(ov[8 * i + 2 * e + 1]) * inv_l);
+                        dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+// F32 -> F16 copy of Q for the engine's F32-Q entry.
+__global__ void __launch_bounds__(256) cast_f32_to_f16_kernel(const float* __restrict__ src, __half* __restrict__ dst,
+                                                              long long n) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        const float4 v = *reinterpret_cast<const float4*>(src + i);
+        *reinterpret_cast<__half2*>(dst + i) = __floats2half2_rn(v.x, v.y);
+        *reinterpret_cast<__half2*>(dst + i + 2) = __floats2half2_rn(v.z, v.w);
+    } else {
+        for (long long k = i; k < n; ++k) dst[k] = __float2half_rn(src[k]);
+    }
+}
+
+// ── host side ──
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// 4-D view {D, rows, heads, batch} of a 16-bit tensor with a {64, 128, 1, 1} box, 128-byte swizzle, zero fill.
+static bool make_map(CUtensorMap* m, bool bf16, const void* base, uint64_t rows, uint64_t heads, uint64_t batch,
+                     uint64_t row_stride_e, uint64_t head_stride_e, uint64_t batch_stride_e) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return false;
+    cuuint64_t dims[4] = {128, rows, heads, batch};
+    cuuint64_t strides[3] = {row_stride_e * 2, head_stride_e * 2, batch_stride_e * 2};
+    cuuint32_t box[4] = {64, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base),
+               dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// q16/k/v: 16-bit tensors (BF16 or F16). K/V element (b, kvh, t, c) at b*kv_batch_stride + kvh*kv_head_stride +
+// t*kv_pos_stride + c (elements). Returns cudaErrorNotSupported when the driver entry point is missing.
+cudaError_t launch_prefill_tc(const void* q16, const void* k, const void* v, void* out, bool bf16, bool out_f32, int B,
+                              int S, int T, int hq, int hkv, int64_t cap_rows, int64_t kv_pos_stride,
+                              int64_t kv_head_stride, int64_t kv_batch_stride, int* status, cudaStream_t st) {
+    CUtensorMap mq, mk, mv;
+    if (!make_map(&mq, bf16, q16, (uint64_t)S, (uint64_t)hq, (uint64_t)B, (uint64_t)hq * 128, 128, (uint64_t)S * hq * 128) ||
+        !make_map(&mk, bf16, k, (uint64_t)cap_rows, (uint64_t)hkv, (uint64_t)B, (uint64_t)kv_pos_stride,
+                  (uint64_t)kv_head_stride, (uint64_t)kv_batch_stride) ||
+        !make_map(&mv, bf16, v, (uint64_t)cap_rows, (uint64_t)hkv, (uint64_t)B, (uint64_t)kv_pos_stride,
+                  (uint64_t)kv_head_stride, (uint64_t)kv_batch_stride))
+        return cudaErrorNotSupported;
+    PrefillParams p;
+    p.out = out;
+    p.B = B;
+    p.S = S;
+    p.T = T;
+    p.hq = hq;
+    p.hkv = hkv;
+    p.group = hq / hkv;
+    p.n_qtiles = (S + pf::BM - 1) / pf::BM;
+    p.scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
+    p.status = status;
+    const int grid = p.n_qtiles * hq * B;
+    auto launch = [&](auto kern) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::SMEM_B);
+        if (e != cudaSuccess) return e;
+        kern<<<grid, 192, pf::SMEM_B, st>>>(mq, mk, mv, p);
+        return cudaGetLastError();
+    };
+    if (bf16) return out_f32 ? launch(prefill_tc_kernel<true, true>) : launch(prefill_tc_kernel<true, false>);
+    return out_f32 ? launch(prefill_tc_kernel<false, true>) : launch(prefill_tc_kernel<false, false>);
+}
+
+cudaError_t launch_cast_f32_to_f16(const float* src, void* dst, long long n, cudaStream_t st) {
+    if (n <= 0) return cudaSuccess;
+    const long long threads = (n + 3) / 4;
+    cast_f32_to_f16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(src, static_cast<__half*>(dst), n);
+    return cudaGetLastError();
+}
+
+}  // namespace argus

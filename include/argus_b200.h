@@ -224,6 +224,25 @@ ARGUS_B200_API int argus_b200_score_reduce(argus_b200_ctx* ctx, const argus_b200
 /* reduce_per_layer — kernel_score_fused_reduce_per_layer (score_reduce.cu:66-91). */
 ARGUS_B200_API int argus_b200_score_reduce_per_layer(argus_b200_ctx* ctx, const argus_b200_score_reduce_args* args);
 
+/* ───────────── Prefill: Backend::flash_attention_prefill (engine/src/backend.rs:1011-1027) ───────────── */
+
+#define ARGUS_B200_PREFILL_F32Q_F16KV 0 /* the engine's entry: Q/O F32, K/V F16 (cuda_pc.rs:830-926) */
+#define ARGUS_B200_PREFILL_BF16 1       /* Q, K, V, O all BF16 */
+#define ARGUS_B200_PREFILL_F16 2        /* Q, K, V, O all F16 */
+
+/* Causal GQA flash-attention prefill — replaces CudaBackend::flash_attention_prefill
+ * (engine/src/backend/cuda_pc.rs:830-926) and flash_attn_prefill_f16kv_dk128
+ * (engine/src/backend/cuda_pc/kernels.cu:691-816). Q/O [batch][seq_len][Hq][D]; K/V
+ * [batch][Hkv][kv_capacity][D] when is_head_major, else [batch][kv_capacity][Hkv][D]. Query row r sees keys
+ * 0..=cache_seq_len-seq_len+r; scale = 1/sqrt(D). Returns ARGUS_B200_E_UNSUPPORTED for head_dim != 128
+ * (the reference's `Ok(false)`: the caller keeps its own route). In the F32-Q mode Q is first rounded to
+ * F16 into context scratch (batch*seq_len*Hq*D*2 bytes). */
+ARGUS_B200_API int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void* stream, const void* q,
+                                                      const void* k_cache, const void* v_cache, void* out,
+                                                      int n_heads_q, int n_heads_kv, int seq_len,
+                                                      int cache_seq_len, int head_dim, int64_t kv_capacity,
+                                                      int batch_size, int is_head_major, int dtype_mode);
+
 /* Blocks until `stream` is idle and returns the status word the kernels set when one of their bounded
  * waits ran out (0 = clean). The word is cleared by the call. */
 ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
