@@ -41,15 +41,13 @@ constexpr int BM = 128, BN = 128, D = 128;
 constexpr int TILE_B = BM * D * 2;          // 32 KB: one Q/K/V/P tile of 16-bit elements
 constexpr int HALF_B = TILE_B / 2;          // one 64-column (128-byte wide) swizzled block of a tile
 constexpr int KV_STAGES = 2;
-constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + TILE_B;
+constexpr int OFF_Q = 0;                       // two query tiles
+constexpr int OFF_K = OFF_Q + 2 * TILE_B;
 constexpr int OFF_V = OFF_K + KV_STAGES * TILE_B;
-constexpr int OFF_P = OFF_V + KV_STAGES * TILE_B;
-constexpr int OFF_BAR = OFF_P + 2 * TILE_B;   // 224 KB
-constexpr int N_BAR = 1 + 4 * KV_STAGES + 8 + 1;
+constexpr int OFF_BAR = OFF_V + KV_STAGES * TILE_B;   // 192 KB
+constexpr int N_BAR = 1 + 4 * KV_STAGES + 6;
 constexpr int SMEM_B = OFF_BAR + N_BAR * 8 + 16 + 1024;   // + TMEM base slot + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TM_S0 = 0, TM_S1 = 128, TM_O = 256;
 constexpr float LAZY = 8.0f;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
@@ -139,18 +137,39 @@ __device__ __forceinline__ uint32_t pack16(float a, float b) {
 
 }  // namespace pf
 
-template <bool BF16, bool OUT_F32>
-__global__ void __launch_bounds__(192, 1)
+// tcgen05.mma with the A operand in tensor memory (16-bit elements, two per 32-bit column, K-major).
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// One CTA = two 128-row query tiles (X = 0, 1) of one head, FlashAttention-4 style:
+//   warp 0        TMA producer (Q0, Q1 once; K_j, V_j stages)
+//   warp 1        MMA issuer: S_X = Q_X·K_j^T into TMEM, O_X += P_X·V_j with P_X read from TMEM
+//   warps 2..3    idle (they only exist so that the register budget can move between whole warpgroups)
+//   warps 4..7    softmax of tile 0, warps 8..11 softmax of tile 1 (one query row per thread)
+// TMEM: S_0 [0,128) S_1 [128,256) O_0 [256,384) O_1 [384,512). P_X overwrites S_X in place as 16-bit
+// pairs (columns [0,64) of the region; with PSPLIT the rounding residual goes to [64,128) and P·V runs
+// twice, which keeps ~16 bits of P when the cache type is BF16). The tensor pipe executes one thread's
+// MMAs in issue order, so S_X(j+1) may be issued right behind P_X(j)·V_j although it reuses the region.
+// While one tile's softmax runs, the tensor pipe works on the other tile.
+template <bool BF16, bool OUT_F32, bool PSPLIT>
+__global__ void __launch_bounds__(384, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ PrefillParams p) {
     using namespace pf;
     extern __shared__ uint8_t smem_raw[];
-    // 128B-swizzled tiles need 1024-byte alignment
-    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;   // 128B-swizzled tiles need 1024-byte alignment
     uint8_t* smem = smem_raw + (smem0 - smem_u32(smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // barrier map
     const uint32_t bar = smem0 + OFF_BAR;
     const uint32_t b_qfull = bar;
     auto b_kfull = [&](int s) { return bar + 8 * (1 + s); };
@@ -158,11 +177,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     auto b_vfull = [&](int s) { return bar + 8 * (1 + 2 * KV_STAGES + s); };
     auto b_vempty = [&](int s) { return bar + 8 * (1 + 3 * KV_STAGES + s); };
     const uint32_t bar2 = bar + 8 * (1 + 4 * KV_STAGES);
-    auto b_sfull = [&](int s) { return bar2 + 8 * s; };
-    auto b_sempty = [&](int s) { return bar2 + 8 * (2 + s); };
-    auto b_pfull = [&](int s) { return bar2 + 8 * (4 + s); };
-    auto b_pempty = [&](int s) { return bar2 + 8 * (6 + s); };
-    const uint32_t b_ofull = bar2 + 8 * 8;
+    auto b_sfull = [&](int x) { return bar2 + 8 * x; };
+    auto b_pfull = [&](int x) { return bar2 + 8 * (2 + x); };
+    auto b_ofull = [&](int x) { return bar2 + 8 * (4 + x); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + N_BAR * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_BAR + N_BAR * 8 + 8);
 
@@ -171,10 +188,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int hb = blockIdx.x % (p.hq * p.B);
     const int h = hb % p.hq, b = hb / p.hq;
     const int kvh = h / p.group;
-    const int r0 = qt * BM;
-    const int q_start = p.T - p.S;                         // global position of query row 0
-    const int kv_end = min(p.T, q_start + r0 + BM);        // keys [0, kv_end) can be visible to this tile
-    const int n_tiles = (kv_end + BN - 1) / BN;
+    const int r0 = qt * (2 * BM);
+    const int q_start = p.T - p.S;                                   // global position of query row 0
+    // keys [0, kv_end_x) can be visible to tile x; a tile that starts past the last query row does nothing
+    int n_x[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int kv_end = (r0 + x * BM < p.S) ? min(p.T, q_start + r0 + x * BM + BM) : 0;
+        n_x[x] = (kv_end + BN - 1) / BN;
+    }
+    const int n_tiles = max(n_x[0], n_x[1]);
 
     if (threadIdx.x == 0) {
         mbar_init(b_qfull, 1);
@@ -184,13 +207,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(b_vfull(s), 1);
             mbar_init(b_vempty(s), 1);
         }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(b_sfull(s), 1);
-            mbar_init(b_sempty(s), 128);
-            mbar_init(b_pfull(s), 128);
-            mbar_init(b_pempty(s), 1);
+        for (int x = 0; x < 2; ++x) {
+            mbar_init(b_sfull(x), 1);
+            mbar_init(b_pfull(x), 128);
+            mbar_init(b_ofull(x), 1);
         }
-        mbar_init(b_ofull, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -210,12 +231,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (p.status != nullptr) atomicExch(p.status, 2);
     };
 
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 128;");
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+    }
     if (warp == 0) {
         // ───────── TMA producer ─────────
         if (lane == 0) {
-            mbar_expect_tx(b_qfull, TILE_B);
-            tma_load_4d(smem0 + OFF_Q, &tm_q, b_qfull, 0, r0, h, b);
-            tma_load_4d(smem0 + OFF_Q + HALF_B, &tm_q, b_qfull, 64, r0, h, b);
+            mbar_expect_tx(b_qfull, 2 * TILE_B);
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                tma_load_4d(smem0 + OFF_Q + x * TILE_B, &tm_q, b_qfull, 0, r0 + x * BM, h, b);
+                tma_load_4d(smem0 + OFF_Q + x * TILE_B + HALF_B, &tm_q, b_qfull, 64, r0 + x * BM, h, b);
+            }
             for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
                 const int s = j % KV_STAGES;
                 const uint32_t ph = (j / KV_STAGES) & 1;
@@ -233,137 +262,187 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // ───────── MMA issuer ─────────
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc(BF16 ? 1 : 0, 0, BM, BN);   // K tile is K-major
-            // A and B of one kind::f16 MMA must have the same format: an F16 P against a BF16 V faulted on B200.
             constexpr uint32_t idesc_o = instr_desc(BF16 ? 1 : 0, 1, BM, D);    // V tile is MN-major
             bool ok = mbar_wait(b_qfull, 0);
-            if (!ok) fail();
-            auto issue_pv = [&](int i) -> bool {
-                const int s = i % KV_STAGES, pb = i & 1;
-                if (!mbar_wait(b_pfull(pb), (i >> 1) & 1)) return false;
-                if (!mbar_wait(b_vfull(s), (i / KV_STAGES) & 1)) return false;
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < BN / 16; ++k) {
-                    // A = P: K-major, 16 keys = 32 bytes inside the 128-byte swizzle row, second 64-key block +16 KB
-                    const uint32_t pa = smem0 + OFF_P + pb * TILE_B + (k >> 2) * HALF_B + (k & 3) * 32;
-                    // B = V: MN-major. d runs along the 128-byte rows (two 64-d blocks, LBO = 16 KB apart),
-                    // 8 keys per 1024-byte group (SBO); one k-step = 16 keys = 2048 bytes.
-                    const uint32_t va = smem0 + OFF_V + s * TILE_B + k * 2048;
-                    tc_mma(tmem + TM_O, smem_desc(pa, 16, 1024), smem_desc(va, HALF_B, 1024), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
-                }
-                tc_commit(b_pempty(pb));
-                tc_commit(b_vempty(s));
-                return true;
-            };
-            for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
-                const int s = j % KV_STAGES, sb = j & 1;
-                ok = mbar_wait(b_kfull(s), (j / KV_STAGES) & 1);
-                if (ok && j >= 2) ok = mbar_wait(b_sempty(sb), ((j >> 1) & 1) ^ 1);
-                if (!ok) break;
-                tc_fence_after();
+            auto issue_s = [&](int x, int j) {
+                const int s = j % KV_STAGES;
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t qa = smem0 + OFF_Q + (k >> 2) * HALF_B + (k & 3) * 32;
+                    const uint32_t qa = smem0 + OFF_Q + x * TILE_B + (k >> 2) * HALF_B + (k & 3) * 32;
                     const uint32_t ka = smem0 + OFF_K + s * TILE_B + (k >> 2) * HALF_B + (k & 3) * 32;
-                    tc_mma(tmem + (sb ? TM_S1 : TM_S0), smem_desc(qa, 16, 1024), smem_desc(ka, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+                    tc_mma(tmem + x * 128, smem_desc(qa, 16, 1024), smem_desc(ka, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
                 }
-                tc_commit(b_sfull(sb));
-                tc_commit(b_kempty(s));
-                if (j > 0) ok = issue_pv(j - 1);
+                tc_commit(b_sfull(x));
+            };
+            auto issue_pv = [&](int x, int j) {
+                const int s = j % KV_STAGES;
+#pragma unroll
+                for (int pass = 0; pass < (PSPLIT ? 2 : 1); ++pass)
+#pragma unroll
+                    for (int k = 0; k < BN / 16; ++k) {
+                        // A = P from TMEM: 16 keys = 8 columns per k-step. B = V: MN-major, d along the 128-byte
+                        // rows (two 64-d blocks LBO = 16 KB apart), 8 keys per 1024-byte group (SBO), 16 keys = 2 KB.
+                        const uint32_t va = smem0 + OFF_V + s * TILE_B + k * 2048;
+                        tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + pass * 64 + k * 8, smem_desc(va, HALF_B, 1024),
+                                  idesc_o, (j > 0 || k > 0 || pass > 0) ? 1u : 0u);
+                    }
+            };
+            if (ok && n_tiles > 0) {
+                ok = mbar_wait(b_kfull(0), 0);
+                if (ok) {
+                    tc_fence_after();
+                    if (n_x[0] > 0) issue_s(0, 0);
+                    if (n_x[1] > 0) issue_s(1, 0);
+                    tc_commit(b_kempty(0));
+                }
             }
-            if (ok && !*abort_flag && n_tiles > 0) ok = issue_pv(n_tiles - 1);
-            if (ok) tc_commit(b_ofull);
-            else fail();
+            for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
+                const int s = j % KV_STAGES;
+                const bool more = (j + 1 < n_tiles);
+                bool v_ready = false, k_ready = false;
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    if (j < n_x[x]) {
+                        ok = mbar_wait(b_pfull(x), j & 1);
+                        if (ok && !v_ready) { ok = mbar_wait(b_vfull(s), (j / KV_STAGES) & 1); v_ready = true; }
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_pv(x, j);
+                        if (j + 1 >= n_x[x]) tc_commit(b_ofull(x));
+                    }
+                    if (j + 1 < n_x[x]) {
+                        if (!k_ready) { ok = mbar_wait(b_kfull((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1); k_ready = true; }
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_s(x, j + 1);
+                    }
+                }
+                if (!ok) break;
+                tc_commit(b_vempty(s));
+                if (more) tc_commit(b_kempty((j + 1) % KV_STAGES));
+            }
+            if (!ok) fail();
         }
-    } else {
+    } else if (warp >= 4) {
         // ───────── softmax / correction / epilogue: one query row per thread ─────────
+        const int x = (warp - 4) >> 2;                      // which query tile
         const int quarter = warp & 3;                       // TMEM lanes this warp may touch
         const int row = quarter * 32 + lane;
-        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int qi = q_start + r0 + row;                  // global position of this query row
+        const uint32_t t_s = tmem + ((uint32_t)(quarter * 32) << 16) + x * 128;
+        const uint32_t t_o = tmem + ((uint32_t)(quarter * 32) << 16) + 256 + x * 128;
+        const int rq = r0 + x * BM + row;                   // query row inside the sequence
+        const int qi = q_start + rq;                        // its global position
+        const int n_mine = n_x[x];
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int sb = j & 1;
-            if (*abort_flag || !mbar_wait(b_sfull(sb), (j >> 1) & 1)) { ok = false; break; }
+        for (int j = 0; j < n_mine; ++j) {
+            if (*abort_flag || !mbar_wait(b_sfull(x), j & 1)) { ok = false; break; }
             tc_fence_after();
-            uint32_t sv[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_addr + (sb ? TM_S1 : TM_S0) + c * 32, sv[c]);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(b_sempty(sb));
-            const bool diag = (j * BN + BN - 1 > q_start + r0);   // some key of this tile may be masked
+            // pass 1: row maximum (the S row is read twice from tensor memory rather than held in 128 registers)
+            const bool diag = (j * BN + BN - 1 > q_start + r0 + x * BM);   // some key of this tile may be masked
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int hf = 0; hf < 2; ++hf) {
+                uint32_t sv[2][32];
+                tmem_ld32(t_s + hf * 64, sv[0]);
+                tmem_ld32(t_s + hf * 64 + 32, sv[1]);
+                tmem_wait_ld();
+                if (diag) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __uint_as_float(sv[c][i]);
-                    if (diag && (j * BN + c * 32 + i > qi)) x = -INFINITY;
-                    sv[c][i] = __float_as_uint(x);
-                    mx = fmaxf(mx, x);
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (j * BN + hf * 64 + c * 32 + i <= qi) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            mx = max3(mx, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
                 }
+            }
             const float m_tile = mx * p.scale_log2;
             float alpha = 1.f;
             if (m_tile > m_ref + LAZY) {                    // also the first tile (m_ref = -inf)
                 alpha = fast_exp2(m_ref - m_tile);
                 m_ref = m_tile;
             }
-            // O rescale (rare after the first tiles): needs PV_{j-1} complete
+            // O rescale (rare after the first tiles). s_full(j) was committed behind P·V of tile j-1, so O is quiescent.
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                if (!mbar_wait(b_pempty((j - 1) & 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
-                tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t ov[32];
-                    tmem_ld32(tmem + lane_addr + TM_O + c * 32, ov);
+                    tmem_ld32(t_o + c * 32, ov);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-                    tmem_st32(tmem + lane_addr + TM_O + c * 32, ov);
+                    tmem_st32(t_o + c * 32, ov);
                 }
-                tmem_wait_st();
             }
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-            float psum = 0.f;
-            // P buffer j&1 was last read by PV_{j-2}
-            if (j >= 2 && !mbar_wait(b_pempty(sb), ((j >> 1) & 1) ^ 1)) { ok = false; break; }
-            uint8_t* prow = smem + OFF_P + sb * TILE_B + row * 128;
+            float psum0 = 0.f, psum1 = 0.f;
+            // pass 2: p = exp2(s*scale - m), packed to 16 bits. P overwrites S in place: the first half's results
+            // are stored only after the second half of S has been read.
+            uint32_t hi[2][32], lo[PSPLIT ? 2 : 1][PSPLIT ? 32 : 1];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {            // 8 keys = one 16-byte chunk
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][q8 * 8 + 2 * e]), p.scale_log2, neg_m));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][q8 * 8 + 2 * e + 1]), p.scale_log2, neg_m));
-                        psum += p0 + p1;
-                        w[e] = pack16<BF16>(p0, p1);
-                    }
-                    const int chunk = c * 4 + q8;            // 0..15 over 128 keys
-                    uint8_t* dst = prow + (chunk >> 3) * HALF_B + (((chunk & 7) ^ (row & 7)) << 4);
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int hf = 0; hf < 2; ++hf) {
+                uint32_t sv[2][32];
+                tmem_ld32(t_s + hf * 64, sv[0]);
+                tmem_ld32(t_s + hf * 64 + 32, sv[1]);
+                tmem_wait_ld();
+                if (hf == 1) {
+                    tmem_st32(t_s, hi[0]);
+                    if constexpr (PSPLIT) tmem_st32(t_s + 64, lo[0]);
                 }
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        float s0 = __uint_as_float(sv[c][2 * e]), s1 = __uint_as_float(sv[c][2 * e + 1]);
+                        if (diag) {
+                            const int kc = j * BN + hf * 64 + c * 32 + 2 * e;
+                            if (kc > qi) s0 = -INFINITY;
+                            if (kc + 1 > qi) s1 = -INFINITY;
+                        }
+                        const float p0 = fast_exp2(fmaf(s0, p.scale_log2, neg_m));
+                        const float p1 = fast_exp2(fmaf(s1, p.scale_log2, neg_m));
+                        psum0 += p0;
+                        psum1 += p1;
+                        const uint32_t w = pack16<BF16>(p0, p1);
+                        hi[hf][c * 16 + e] = w;
+                        if constexpr (PSPLIT) {
+                            float h0, h1;
+                            if constexpr (BF16) {
+                                h0 = __uint_as_float(w << 16);
+                                h1 = __uint_as_float(w & 0xffff0000u);
+                            } else {
+                                const float2 hf2 = unpack_half2(w);
+                                h0 = hf2.x;
+                                h1 = hf2.y;
+                            }
+                            lo[hf][c * 16 + e] = pack16<BF16>(p0 - h0, p1 - h1);
+                        }
+                    }
             }
-            l = l * alpha + psum;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tmem_st32(t_s + 32, hi[1]);
+            if constexpr (PSPLIT) tmem_st32(t_s + 96, lo[1]);
+            l = l * alpha + (psum0 + psum1);
+            tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(b_pfull(sb));
+            mbar_arrive(b_pfull(x));
         }
         // epilogue
-        if (ok && n_tiles > 0 && !*abort_flag) ok = mbar_wait(b_ofull, 0);
+        if (ok && n_mine > 0 && !*abort_flag) ok = mbar_wait(b_ofull(x), 0);
         if (!ok) fail();
         tc_fence_after();
-        const bool row_ok = (r0 + row) < p.S;
+        const bool row_ok = rq < p.S;
         const float inv_l = (ok && l > 0.f) ? 1.0f / l : 0.f;
-        const int64_t obase = (((int64_t)b * p.S + r0 + row) * p.hq + h) * D;
+        const int64_t obase = (((int64_t)b * p.S + rq) * p.hq + h) * D;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             uint32_t ov[32];
-            if (ok && n_tiles > 0) {
-                tmem_ld32(tmem + lane_addr + TM_O + c * 32, ov);
+            if (ok && n_mine > 0) {
+                tmem_ld32(t_o + c * 32, ov);
                 tmem_wait_ld();
             } else {
 #pragma unroll
@@ -447,7 +526,7 @@ static bool make_map(CUtensorMap* m, bool bf16, const void* base, uint64_t rows,
 // t*kv_pos_stride + c (elements). Returns cudaErrorNotSupported when the driver entry point is missing.
 cudaError_t launch_prefill_tc(const void* q16, const void* k, const void* v, void* out, bool bf16, bool out_f32, int B,
                               int S, int T, int hq, int hkv, int64_t cap_rows, int64_t kv_pos_stride,
-                              int64_t kv_head_stride, int64_t kv_batch_stride, int* status, cudaStream_t st) {
+                              int64_t kv_head_stride, int64_t kv_batch_stride, bool p_split, int* status, cudaStream_t st) {
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, bf16, q16, (uint64_t)S, (uint64_t)hq, (uint64_t)B, (uint64_t)hq * 128, 128, (uint64_t)S * hq * 128) ||
         !make_map(&mk, bf16, k, (uint64_t)cap_rows, (uint64_t)hkv, (uint64_t)B, (uint64_t)kv_pos_stride,
@@ -463,18 +542,23 @@ cudaError_t launch_prefill_tc(const void* q16, const void* k, const void* v, voi
     p.hq = hq;
     p.hkv = hkv;
     p.group = hq / hkv;
-    p.n_qtiles = (S + pf::BM - 1) / pf::BM;
+    p.n_qtiles = (S + 2 * pf::BM - 1) / (2 * pf::BM);
     p.scale_log2 = (1.0f / sqrtf(128.0f)) * 1.4426950408889634f;
     p.status = status;
     const int grid = p.n_qtiles * hq * B;
     auto launch = [&](auto kern) -> cudaError_t {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pf::SMEM_B);
         if (e != cudaSuccess) return e;
-        kern<<<grid, 192, pf::SMEM_B, st>>>(mq, mk, mv, p);
+        kern<<<grid, 384, pf::SMEM_B, st>>>(mq, mk, mv, p);
         return cudaGetLastError();
     };
-    if (bf16) return out_f32 ? launch(prefill_tc_kernel<true, true>) : launch(prefill_tc_kernel<true, false>);
-    return out_f32 ? launch(prefill_tc_kernel<false, true>) : launch(prefill_tc_kernel<false, false>);
+    // BF16 keeps 8 significant bits of P per MMA operand; the split form adds the rounding residual as a second
+    // operand so that outputs stay within the 2e-3 absolute tolerance. F16 (11 bits) does not need it.
+    if (bf16) {
+        if (p_split) return out_f32 ? launch(prefill_tc_kernel<true, true, true>) : launch(prefill_tc_kernel<true, false, true>);
+        return out_f32 ? launch(prefill_tc_kernel<true, true, false>) : launch(prefill_tc_kernel<true, false, false>);
+    }
+    return out_f32 ? launch(prefill_tc_kernel<false, true, false>) : launch(prefill_tc_kernel<false, false, false>);
 }
 
 cudaError_t launch_cast_f32_to_f16(const float* src, void* dst, long long n, cudaStream_t st) {
