@@ -247,6 +247,31 @@ ARGUS_B200_API int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void*
  * waits ran out (0 = clean). The word is cleared by the call. */
 ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
 
+/* ───────────── Decode without any allocation ─────────────
+ * No counterpart in the reference (its CUDA backend allocates freely: managed KV buffers, a lazily grown
+ * score scratch, a per-call score buffer in the KIVI plugin). This entry point is for hosts of this library
+ * that cannot call cudaMalloc - code running under a stream capture or in a serving loop where an allocation
+ * would synchronise the device, and embedders whose device memory comes once from their own pool.
+ *
+ * Same computation as argus_b200_attention_gen for one sequence (F16 K/V, D in {64,128}, Hq/Hkv <= 8) with an
+ * optional natural-log lse[Hq] output and no score outputs. No context: the split-KV scratch lives in a fixed
+ * array of argus_b200_static_scratch_bytes() = 4 MiB inside the library image, one per device that loads the
+ * library, held until the process exits. A call whose split plan needs more (about 4 KB per (split, KV head)
+ * at D=128; in practice Hkv up to 256 and any sequence length) returns ARGUS_B200_E_WORKSPACE.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and the SM count
+ * with that device current: make that first call before any stream capture begins. All calls on a device
+ * share the array and it keeps the last call's contents; the words that must start at zero are cleared on
+ * `stream` at the start of every call. Calls whose kernels may overlap on the GPU race on the array: issue
+ * them on one stream, or otherwise order them. Calls cudaMemsetAsync and one kernel launch, nothing that
+ * allocates. Error text: argus_b200_static_last_error() (per host thread). */
+ARGUS_B200_API int argus_b200_attention_gen_static(void* stream, const float* q, const void* k_cache,
+                                                   const void* v_cache, float* out, float* lse, int num_heads_q,
+                                                   int num_heads_kv, int head_dim, int64_t cache_seq_len,
+                                                   int kv_dtype, int64_t head_stride, int64_t pos_stride);
+ARGUS_B200_API size_t argus_b200_static_scratch_bytes(void);
+ARGUS_B200_API const char* argus_b200_static_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif
