@@ -214,6 +214,13 @@ class B200Backend:
                               score_stride, max_seq_len, layer_flat)
         return int(self._lib.argus_b200_score_reduce_per_layer(self._h, C.byref(a)))
 
+    def lse_merge(self, parts: torch.Tensor, num_heads_q: int, head_dim: int, out: torch.Tensor,
+                  lse_out: Optional[torch.Tensor] = None) -> None:
+        """parts [n_parts, Hq*D + Hq] f32 (per rank: outputs then lse) -> out [Hq, D]."""
+        self._check(self._lib.argus_b200_lse_merge(self._h, self._stream(), parts.data_ptr(), parts.shape[0],
+                                                   parts.stride(0), num_heads_q, head_dim, out.data_ptr(),
+                                                   _ptr(lse_out)))
+
     def check_status(self) -> int:
         """Synchronises the current stream; non-zero if a kernel's bounded wait ran out since the last check."""
         return int(self._lib.argus_b200_check_status(self._h, self._stream()))

@@ -374,6 +374,21 @@ int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void* stream, const 
     return ARGUS_B200_OK;
 }
 
+int argus_b200_lse_merge(argus_b200_ctx* ctx, void* stream, const float* parts, int n_parts, int64_t part_stride,
+                         int num_heads_q, int head_dim, float* out, float* lse_out) {
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    if (!parts || !out || n_parts <= 0 || num_heads_q <= 0 || head_dim <= 0 ||
+        part_stride < (int64_t)num_heads_q * head_dim + num_heads_q) {
+        C_(ctx)->set_error("lse_merge: bad arguments (n_parts=%d part_stride=%lld)", n_parts, (long long)part_stride);
+        return ARGUS_B200_E_INVALID;
+    }
+    cudaError_t e = argus::launch_lse_merge(parts, n_parts, (long long)part_stride, num_heads_q, head_dim, out, lse_out,
+                                            static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return C_(ctx)->cuda_fail(e, "lse_merge launch");
+    C_(ctx)->launches += 1;
+    return ARGUS_B200_OK;
+}
+
 int argus_b200_check_status(argus_b200_ctx* ctx, void* stream) {
     if (!ctx) return ARGUS_B200_E_INVALID;
     Context* c = C_(ctx);

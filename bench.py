@@ -173,6 +173,126 @@ def workload_config(name, case):
             "l2": "inputs (310 MB) exceed the 126 MB L2; two KV copies are alternated between steps"}
 
 
+def _time_events(fn, iters, warmup=3):
+    """Median and mean device time (ms) of fn() over `iters` calls, CUDA events on the current stream."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    return ts[len(ts) // 2], sum(ts) / len(ts)
+
+
+def other_configs(be, peaks, which):
+    """The remaining benchmark configurations on one GPU (shorter runs; same timing hygiene). Returned as a
+    dict that rides along in the JSON line; the headline stays the batched F16 decode."""
+    import torch
+
+    from argus_engine_b200 import DecodeExtras
+    from argus_engine_b200 import workloads as wl
+
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()  # noqa: E731
+    res = {}
+    if "c1" in which:
+        # configs[0]: launch-latency dominated, so the figure is microseconds per layer-step. 40 KV copies
+        # (168 MB > L2) replayed from one CUDA graph, i.e. device time without host launch gaps.
+        case = wl.config1()
+        q = dev(case.q)
+        out = torch.zeros(1, 32, 64, device="cuda")
+        ks = [dev(case.k[0]) for _ in range(40)]
+        vs = [dev(case.v[0]) for _ in range(40)]
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            for i in range(3):
+                be.attention_gen(q[0], ks[i], vs[i], out[0], 32, 8, 64, 2048)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                for i in range(40):
+                    be.attention_gen(q[0], ks[i], vs[i], out[0], 32, 8, 64, 2048)
+            med, _ = _time_events(g.replay, 20)
+        nbytes = decode_bytes(case)
+        res["c1_decode_f16_T2048"] = {"us_per_layer_step": med * 1e3 / 40, "achieved_gbs": nbytes / (med / 40) / 1e6,
+                                      "algorithmic_bytes": nbytes, "timing": "CUDA-graph replay of 40 calls on 40 KV copies"}
+        del ks, vs
+    if "c3" in which:
+        case = wl.config3()
+        B, T = len(case.q_tokens), case.q_tokens[0] + case.res_tokens[0]
+        seqs = [(dev(case.qk[i]), dev(case.qv[i]), dev(case.res_k[i]), dev(case.res_v[i]), case.q_tokens[i],
+                 case.res_tokens[i]) for i in range(B)]
+        q = dev(case.q)
+        out = torch.zeros(B, 32, 128, device="cuda")
+        ex = DecodeExtras(head_scores=torch.zeros(B, 8, T, device="cuda"), score_stride=T)
+        fn = lambda: be.kivi_attention_batched(q, seqs, out, 32, 8, 128, 128, 4, 1 / np.sqrt(128), res_f16=True,  # noqa: E731
+                                               extras=ex)
+        med, _ = _time_events(fn, 20)
+        nbytes = wl.kivi_bytes(case, True)
+        res["c3_kivi_q4_h2o"] = {"us_per_layer_step": med * 1e3, "achieved_gbs": nbytes / med / 1e6,
+                                 "frac_of_hbm_peak": nbytes / med / 1e6 / peaks["hbm_gbs"], "algorithmic_bytes": nbytes,
+                                 "l2": "338 MB of packed KV per step exceed the 126 MB L2"}
+        del seqs
+    if "c4" in which:
+        B, S = 4, 4096
+        gen = torch.Generator(device="cuda").manual_seed(3)
+        q = torch.randn(B, S, 32, 128, device="cuda", generator=gen).to(torch.bfloat16)
+        k = torch.randn(B, 8, S, 128, device="cuda", generator=gen).to(torch.bfloat16)
+        v = torch.randn(B, 8, S, 128, device="cuda", generator=gen).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        fn = lambda: be.flash_attention_prefill(q, k, v, out, 32, 8, S, S, 128, S, B, True)  # noqa: E731
+        med, _ = _time_events(fn, 20)
+        fl = wl.prefill_flops(B, S, S, 32, 128)
+        res["c4_prefill_bf16"] = {"ms": med, "tflops": fl / med / 1e9, "frac_of_bf16_peak": fl / med / 1e9 / peaks["bf16_tflops"],
+                                  "frac_of_bf16_sustained": fl / med / 1e9 / peaks["bf16_tflops_sustained"],
+                                  "flops": fl, "p_operand": "split (hi + residual) so that BF16 outputs hold 2e-3"}
+    return res
+
+
+def sharded_c5(be, dist, world, rank, peaks, iters=20):
+    """configs[4]: 1M-token decode sharded by KV sequence over `world` GPUs. Per step: split-KV kernel over the
+    local T/N slice -> one all-gather of (o, lse) -> merge. Device time, max over ranks."""
+    import torch
+
+    from argus_engine_b200.sharded import make_gpu_decoder, shard_range
+
+    T, hq, hkv, d = 1 << 20, 64, 8, 128
+    lo, hi = shard_range(T, world, rank)
+    gen = torch.Generator(device="cuda").manual_seed(4 + rank)
+    k = torch.randn(hkv, hi - lo, d, device="cuda", generator=gen, dtype=torch.float32).to(torch.float16)
+    v = torch.randn(hkv, hi - lo, d, device="cuda", generator=gen, dtype=torch.float32).to(torch.float16)
+    q = torch.randn(hq, d, device="cuda", generator=torch.Generator(device="cuda").manual_seed(4))
+    dec = make_gpu_decoder(be, k, v, hi - lo, hq, hkv, d)
+    out = torch.zeros(hq, d, device="cuda")
+    for _ in range(3):
+        dec.step(q, out)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        dec.step(q, out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    nbytes = T * hkv * d * 2 * 2 + 2 * hq * d * 4
+    del k, v
+    return {"workload": "c5: 1M-token decode, Hq=64 Hkv=8 D=128, KV sharded by sequence", "n_gpus": world,
+            "us_per_layer_step": ms * 1e3, "value_tbs": nbytes / (ms * 1e-3) / 1e12,
+            "frac_of_aggregate_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world),
+            "gather_bytes_per_rank": (hq * d + hq) * 4, "scaling": "strong", "l2": "shard >= 537 MB > L2"}
+
+
 def run_b200(args):
     import torch
 
@@ -291,6 +411,13 @@ def run_b200(args):
                "sample": f"the whole step (16 sequences, {step_bytes / 1e6:.1f} MB algorithmic), mean of {reps} runs",
                "ms_per_step": dt * 1e3}
 
+    del kv_sets, hk_pin, hv_pin
+    torch.cuda.empty_cache()
+    extra = {}
+    if world == 1 and args.others:
+        extra = other_configs(be, peaks, args.others.split(","))
+    shard = sharded_c5(be, dist, world, rank, peaks) if args.sharded else None
+
     if rank == 0:
         achieved = step_bytes / (ms * 1e-3) / 1e9
         line = {
@@ -308,6 +435,8 @@ def run_b200(args):
             "gpu_launches": int(launches),
             "clocks": sampler.summary(),
             "parity_max_abs_vs_oracle": parity,
+            "other_configs": extra,
+            "sharded": shard,
         }
         print(json.dumps(line), flush=True)
     be.close()
@@ -321,6 +450,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--others", default="c1,c3,c4", help="comma list of further configs to time at N=1 ('' = none)")
+    ap.add_argument("--no-sharded", dest="sharded", action="store_false", help="skip the sharded 1M-token decode")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps == 2000:

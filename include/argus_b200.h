@@ -243,6 +243,17 @@ ARGUS_B200_API int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void*
                                                       int cache_seq_len, int head_dim, int64_t kv_capacity,
                                                       int batch_size, int is_head_major, int dtype_mode);
 
+/* ───────────── Sequence-sharded decode: merge of per-rank (o, lse) partials ─────────────
+ * The reference is single-device; its only split/merge is the CPU chunk merge of
+ * engine/src/backend/cpu/neon.rs:1028-1125, whose algebra this follows. Each rank runs
+ * argus_b200_attention_gen over its slice of the KV sequence with `out` and `extras.lse` pointing into one
+ * buffer of part_stride = Hq*D + Hq floats ([Hq][D] outputs, then [Hq] lse); the buffers of all ranks are
+ * gathered (one NCCL all-gather) into `parts` [n_parts][part_stride] in this rank's own memory, and this call
+ * writes out[Hq][D] (and optionally the merged lse[Hq]). Empty shards (lse = -inf) are skipped. */
+ARGUS_B200_API int argus_b200_lse_merge(argus_b200_ctx* ctx, void* stream, const float* parts, int n_parts,
+                                        int64_t part_stride, int num_heads_q, int head_dim, float* out,
+                                        float* lse_out);
+
 /* Blocks until `stream` is idle and returns the status word the kernels set when one of their bounded
  * waits ran out (0 = clean). The word is cleared by the call. */
 ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
