@@ -4,18 +4,10 @@
 // engine/src/backend/cuda_pc.rs:830-926 with flash_attn_prefill_f16kv_dk128, engine/src/backend/cuda_pc/
 // kernels.cu:691-816). Same contract: Q/O [B][S][Hq][D], K/V HeadMajor [B][Hkv][cap][D], query row r sees
 // keys <= cache_seq_len - seq_len + r, rows without a visible key produce zeros. The reference runs one
-// thread per query row with scalar FMAs; here one CTA owns a 128-row query tile of one head:
-//
-//   warp 0      TMA producer: Q once, then K and V tiles of 128 keys (two stages each), 128B-swizzled boxes
-//   warp 1      one elected thread issues tcgen05.mma: S = Q·K^T (M128 N128 K16 x8) into one of two TMEM
-//               buffers, then O += P·V (V is the MN-major B operand) into a third TMEM region
-//   warps 2..5  softmax: each thread owns one query row = one TMEM lane. tcgen05.ld of the S row, running
-//               max in the log2 domain with a lazy rescale (O is only rescaled when the max grew by more
-//               than 2^8, as the exact algebra allows), exp2, P as 16-bit into 128B-swizzled shared
-//               memory for the second MMA, and finally O/l to global memory.
-//
-// S_{j+1} is issued before P_j is awaited, so the tensor pipe computes the next logits while the softmax
-// warps work on the current ones. Every mbarrier wait is bounded; a wait that runs out raises the status
+// thread per query row with scalar FMAs; here one CTA owns two 128-row query tiles of one head, TMA feeds
+// 128B-swizzled Q/K/V tiles, one thread issues tcgen05.mma for S = Q·K^T and O += P·V with the accumulators
+// (and P) in tensor memory, and eight softmax warps own one query row per thread. The kernel comment below
+// gives the roles and the TMEM map. Every mbarrier wait is bounded; a wait that runs out raises the status
 // word, makes every role leave its loop, and the CTA still frees its TMEM.
 #include <cuda.h>
 #include <cuda_bf16.h>
