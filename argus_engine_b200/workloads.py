@@ -64,16 +64,12 @@ def config2(batch: int = 16, lo: int = 1024, hi: int = 8192) -> DecodeCase:
 
 
 @dataclass
-class KiviCase:
-    """KIVI-packed sequences as the engine's container holds them (built by feeding the tokens through the
-    restated ring/flush logic). Per sequence: packed K/V bytes, F32 residual ring [Hkv,res_cap,D] and counts."""
-    q: np.ndarray                 # [B,Hq,D] f32
-    qk: List[np.ndarray]
-    qv: List[np.ndarray]
-    res_k: List[np.ndarray]
-    res_v: List[np.ndarray]
-    q_tokens: List[int]
-    res_tokens: List[int]
+class KiviSource:
+    """Un-quantised source tensors of a KIVI configuration: per sequence K and V [T,Hkv,D] float32 in token
+    order (what the engine hands to the container token by token) and q [B,Hq,D]."""
+    q: np.ndarray
+    k: List[np.ndarray]
+    v: List[np.ndarray]
     hq: int
     hkv: int
     d: int
@@ -81,16 +77,12 @@ class KiviCase:
     bits: int
 
 
-def kivi_case(seed: int, lens, hq: int, hkv: int, d: int, res_cap: int = 128, bits: int = 4,
-              outlier_frac: float = 0.01, outlier_scale: float = 8.0, res_f16: bool = False) -> KiviCase:
+def kivi_source(seed: int, lens, hq: int, hkv: int, d: int, res_cap: int = 128, bits: int = 4,
+                outlier_frac: float = 0.01, outlier_scale: float = 8.0) -> KiviSource:
     """Draw order per sequence: K [T,Hkv,D], V [T,Hkv,D], the outlier (kv_head, channel) set; q after all
-    sequences. `outlier_frac` of the Hkv*D K channels are multiplied by `outlier_scale` for every token.
-    The tokens go through the oracle's container, whose flush order defines the packed layout.
-    With res_f16 the residual rows are rounded to F16 (and kept as such in res_k/res_v)."""
-    from oracle import oracle as orc   # container logic is test infrastructure; workloads are inputs only
-
+    sequences. `outlier_frac` of the Hkv*D K channels are multiplied by `outlier_scale` for every token."""
     rng = _rng(seed)
-    out = KiviCase(None, [], [], [], [], [], [], hq, hkv, d, res_cap, bits)
+    ks, vs = [], []
     for t in lens:
         k = rng.standard_normal((t, hkv, d), dtype=np.float32)
         v = rng.standard_normal((t, hkv, d), dtype=np.float32)
@@ -98,83 +90,28 @@ def kivi_case(seed: int, lens, hq: int, hkv: int, d: int, res_cap: int = 128, bi
         if n_out > 0:
             idx = rng.choice(hkv * d, n_out, replace=False)
             k.reshape(t, hkv * d)[:, idx] *= outlier_scale
-        c = orc.KiviCache(hkv, d, res_cap, bits)
-        c.update(k, v)
-        qk, qv, rk, rv = c.export()
-        if res_f16:
-            rk, rv = rk.astype(np.float16), rv.astype(np.float16)
-        out.qk.append(qk)
-        out.qv.append(qv)
-        out.res_k.append(rk)
-        out.res_v.append(rv)
-        out.q_tokens.append(c.q_tokens)
-        out.res_tokens.append(c.res_tokens)
-    out.q = rng.standard_normal((len(lens), hq, d), dtype=np.float32)
-    return out
+        ks.append(k)
+        vs.append(v)
+    q = rng.standard_normal((len(lens), hq, d), dtype=np.float32)
+    return KiviSource(q, ks, vs, hq, hkv, d, res_cap, bits)
 
 
-def config3(batch: int = 8, T: int = 32768, res_f16: bool = True) -> KiviCase:
+def config3_source(batch: int = 8, T: int = 32768) -> KiviSource:
     """KIVI Q4 decode with H2O scores: B=8, Hq=32, Hkv=8, D=128, T=32768 (32640 packed + 128 residual), seed 2."""
-    return kivi_case(2, [T] * batch, 32, 8, 128, 128, 4, res_f16=res_f16)
+    return kivi_source(2, [T] * batch, 32, 8, 128, 128, 4)
 
 
-def kivi_bytes(case: KiviCase, with_head_scores: bool = True) -> int:
-    """Algorithmic bytes of one KIVI decode step: packed blocks + residual rows read once, q read, out
-    written, and the [Hkv,T] F32 group-mean score vector written."""
+def kivi_step_bytes(q_tokens, res_tokens, hq: int, hkv: int, d: int, bits: int, res_itemsize: int,
+                    with_head_scores: bool = True) -> int:
+    """Algorithmic bytes of one KIVI decode step: packed K and V blocks and residual rows read once, q read,
+    out written, and the [Hkv,T] F32 group-mean score vector written."""
+    bb = {2: 12, 4: 20, 8: 36}[bits]
     total = 0
-    for i in range(len(case.q_tokens)):
-        total += case.qk[i].nbytes + case.qv[i].nbytes
-        total += 2 * case.hkv * case.res_tokens[i] * case.d * case.res_k[i].itemsize
+    for qt, rt in zip(q_tokens, res_tokens):
+        total += 2 * qt * hkv * (d // 32) * bb
+        total += 2 * hkv * rt * d * res_itemsize
         if with_head_scores:
-            total += case.hkv * (case.q_tokens[i] + case.res_tokens[i]) * 4
-    return total + 2 * len(case.q_tokens) * case.hq * case.d * 4
+            total += hkv * (qt + rt) * 4
+    return total + 2 * len(q_tokens) * hq * d * 4
 
 
-@dataclass
-class PrefillCase:
-    """Q [B,S,Hq,D], K/V HeadMajor [B,Hkv,cap,D] as float32 arrays already rounded to the 16-bit input type
-    (`dtype` "bf16" or "f16"); the GPU gets the same values in 16 bits, the oracle the float32 copies."""
-    q: np.ndarray
-    k: np.ndarray
-    v: np.ndarray
-    S: int
-    T: int
-    cap: int
-    hq: int
-    hkv: int
-    d: int
-    dtype: str
-
-
-def _round_bf16(x: np.ndarray) -> np.ndarray:
-    """Round-to-nearest-even float32 -> bfloat16 -> float32."""
-    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
-    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
-    return r.astype(np.uint32).view(np.float32).reshape(x.shape)
-
-
-def prefill_case(seed: int, B: int, S: int, T: int, hq: int, hkv: int, d: int = 128, cap: int = 0,
-                 dtype: str = "bf16") -> PrefillCase:
-    """Draw order: Q [B,S,Hq,D], K [B,T,Hkv,D], V [B,T,Hkv,D] (token-major draws, then placed HeadMajor)."""
-    rng = _rng(seed)
-    cap = cap or T
-    q = rng.standard_normal((B, S, hq, d), dtype=np.float32)
-    k = rng.standard_normal((B, T, hkv, d), dtype=np.float32)
-    v = rng.standard_normal((B, T, hkv, d), dtype=np.float32)
-    rnd = _round_bf16 if dtype == "bf16" else (lambda a: a.astype(np.float16).astype(np.float32))
-    kh = np.zeros((B, hkv, cap, d), dtype=np.float32)
-    vh = np.zeros((B, hkv, cap, d), dtype=np.float32)
-    kh[:, :, :T] = rnd(k).transpose(0, 2, 1, 3)
-    vh[:, :, :T] = rnd(v).transpose(0, 2, 1, 3)
-    return PrefillCase(rnd(q), kh, vh, S, T, cap, hq, hkv, d, dtype)
-
-
-def config4(B: int = 4, S: int = 4096) -> PrefillCase:
-    """Causal GQA prefill: B=4, S=4096, Hq=32, Hkv=8, D=128, BF16, seed 3."""
-    return prefill_case(3, B, S, S, 32, 8, 128, dtype="bf16")
-
-
-def prefill_flops(B: int, S: int, T: int, hq: int, d: int) -> float:
-    """Causal-useful FLOPs: 4*D per (query row, visible key) pair; row r sees T-S+r+1 keys."""
-    pairs = S * (T - S) + S * (S + 1) / 2.0
-    return 4.0 * B * hq * d * pairs

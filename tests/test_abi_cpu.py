@@ -1,0 +1,57 @@
+"""CPU-only checks of the C-ABI boundary: the library loads without a GPU, exports every symbol that
+include/argus_b200.h declares, and the ctypes mirrors of the reference's #[repr(C)] structs have the sizes
+the header asserts. No compute call is made here."""
+import ctypes as C
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "argus_b200.h")).read()
+    return sorted(set(re.findall(r"ARGUS_B200_API[^;(]*?\b(argus_b200_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from argus_engine_b200 import load_library
+
+    lib = load_library()
+    names = _declared()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in the header but not exported"
+    assert lib.argus_b200_version() >= 1 and lib.argus_b200_sm_arch() == 100
+
+
+def test_struct_mirrors_match_reference_layouts():
+    from argus_engine_b200 import _lib
+
+    assert C.sizeof(_lib.QuantAttnArgs) == 128 and _lib.QuantAttnArgs.scale.offset == 120
+    assert C.sizeof(_lib.QuantGatherArgs) == 64
+    assert C.sizeof(_lib.QuantDequantFlushArgs) == 72 and _lib.QuantDequantFlushArgs.bits.offset == 64
+    assert C.sizeof(_lib.QuantScatterResidualArgs) == 64
+    assert C.sizeof(_lib.ScoreReduceArgs) == 96 and _lib.ScoreReduceArgs.n_layers.offset == 40
+    assert C.sizeof(_lib.DecodeExtrasC) == 48 and C.sizeof(_lib.Seq) == 40 and C.sizeof(_lib.KiviSeq) == 48
+
+
+def test_no_gpu_means_loud_failure_not_fallback():
+    import pytest
+    import torch
+
+    from argus_engine_b200 import B200Backend
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(RuntimeError):
+        B200Backend(0)
+
+
+def test_product_never_imports_the_oracle():
+    """Nothing in the shipped package imports, loads or runs anything under oracle/."""
+    pkg = os.path.join(ROOT, "argus_engine_b200")
+    for fn in os.listdir(pkg):
+        if fn.endswith(".py"):
+            text = open(os.path.join(pkg, fn)).read()
+            assert not re.search(r"^\s*(from|import)\s+oracle", text, re.M), fn
+            assert "libargus_oracle" not in text, fn

@@ -10,6 +10,7 @@ import torch
 
 from argus_engine_b200 import workloads as wl
 from oracle import oracle as orc
+from tests._kivi import pack_with_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -121,7 +122,7 @@ def _oracle_kivi(case, i, scale=None, scores=False):
 def test_attention_gen_quant_vs_oracle(be, bits, d, g, T):
     """The reference-shaped entry (CudaQuantAttnArgs): packed + residual, host score read-back."""
     hkv = 2
-    case = wl.kivi_case(1000 + bits + T, [T], hkv * g, hkv, d, 128, bits)
+    case = pack_with_oracle(wl.kivi_source(1000 + bits + T, [T], hkv * g, hkv, d, 128, bits))
     want, want_p = _oracle_kivi(case, 0, scores=True)
     out = torch.full((case.hq, d), float("nan"), device="cuda")
     stride = T + 5
@@ -186,7 +187,7 @@ def test_batched_c3_shape_reduced(be, res_f16):
     from argus_engine_b200 import DecodeExtras
 
     lens = [4224, 2176, 777]
-    case = wl.kivi_case(2, lens, 32, 8, 128, 128, 4, res_f16=res_f16)
+    case = pack_with_oracle(wl.kivi_source(2, lens, 32, 8, 128, 128, 4), res_f16=res_f16)
     B, stride = len(lens), 4352
     seqs = [(_dev(case.qk[i]), _dev(case.qv[i]), _dev(case.res_k[i]), _dev(case.res_v[i]), case.q_tokens[i],
              case.res_tokens[i]) for i in range(B)]
@@ -238,3 +239,29 @@ def test_score_reduce_vs_oracle(be, case_id):
     assert np.array_equal(lflat.cpu().numpy(), w_lf)
     if case_id == 0:
         np.testing.assert_allclose(w_imp[:3], 1.5 * np.array([0.7, 0.6, 1.1]), atol=1e-5)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_device_cache_matches_oracle_container(be, bits):
+    """The device-resident container (ring write + device flush) ends up with exactly the bytes of the
+    restated engine container, for prompt-sized and token-by-token updates, and decodes to the same result."""
+    from argus_engine_b200.kivi_cache import KiviDeviceCache
+
+    hkv, d, rc, T = 2, 64, 64, 64 * 3 + 21
+    src = wl.kivi_source(77 + bits, [T], 8, hkv, d, rc, bits)
+    want = pack_with_oracle(src)
+    cache = KiviDeviceCache(be, hkv, d, 1024, rc, bits)
+    k, v = _dev(src.k[0]), _dev(src.v[0])
+    cache.update(k[:150], v[:150])            # a prefill-sized write crossing two flushes
+    for t in range(150, T):                   # then token by token
+        cache.update(k[t:t + 1], v[t:t + 1])
+    torch.cuda.synchronize()
+    assert (cache.q_tokens, cache.res_pos) == (want.q_tokens[0], want.res_tokens[0])
+    assert np.array_equal(cache.qk.cpu().numpy()[:want.qk[0].size], want.qk[0])
+    assert np.array_equal(cache.qv.cpu().numpy()[:want.qv[0].size], want.qv[0])
+    assert np.array_equal(cache.res_k.cpu().numpy()[:, :cache.res_pos], want.res_k[0][:, :cache.res_pos])
+    out = torch.zeros(1, 8, d, device="cuda")
+    be.kivi_attention_batched(_dev(src.q), [cache.seq()], out, 8, hkv, d, rc, bits, 1 / np.sqrt(d))
+    torch.cuda.synchronize()
+    ref, _ = _oracle_kivi(want, 0)
+    np.testing.assert_allclose(out[0].cpu().numpy(), ref, atol=OUT_ATOL, rtol=OUT_RTOL)
