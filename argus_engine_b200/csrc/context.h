@@ -52,7 +52,7 @@ cudaError_t launch_score_reduce_per_layer(const float* scores, float* layer_flat
 // prefill_sm100.cu
 cudaError_t launch_prefill_tc(const void* q16, const void* k, const void* v, void* out, bool bf16, bool out_f32, int B,
                               int S, int T, int hq, int hkv, int64_t cap_rows, int64_t kv_pos_stride,
-                              int64_t kv_head_stride, int64_t kv_batch_stride, bool p_split, int* status, cudaStream_t st);
+                              int64_t kv_head_stride, int64_t kv_batch_stride, int p_mode, int* status, cudaStream_t st);
 cudaError_t launch_cast_f32_to_f16(const float* src, void* dst, long long n, cudaStream_t st);
 // lse_merge.cu
 cudaError_t launch_lse_merge(const float* parts, int n_parts, long long part_stride, int hq, int d, float* out,

@@ -364,7 +364,7 @@ int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void* stream, const 
     cudaError_t e = argus::launch_prefill_tc(q16, k_cache, v_cache, out, dtype_mode == ARGUS_B200_PREFILL_BF16,
                                              dtype_mode == ARGUS_B200_PREFILL_F32Q_F16KV, batch_size, seq_len,
                                              cache_seq_len, n_heads_q, n_heads_kv, cache_seq_len, pos_stride, head_stride,
-                                             batch_stride, getenv("ARGUS_B200_PREFILL_BF16_SINGLE_P") == nullptr, c->status, st);
+                                             batch_stride, getenv("ARGUS_B200_PREFILL_BF16_P") ? atoi(getenv("ARGUS_B200_PREFILL_BF16_P")) : 2, c->status, st);
     if (e == cudaErrorNotSupported) {
         c->set_error("flash_attention_prefill: the driver does not export cuTensorMapEncodeTiled");
         return ARGUS_B200_E_UNSUPPORTED;

@@ -17,6 +17,8 @@
 // softmax does not care and P·V uses the same order. The residual window is a separate split handled in
 // plain F32 FMA. Everything after the main loop (warp merge, split merge, score finalize) is shared with
 // the F16 kernel.
+#include <stdlib.h>
+
 #include "decode_epilogue.cuh"
 #include "decode_params.h"
 #include "ptx.cuh"
@@ -101,8 +103,8 @@ struct DecodeKiviCfg {
     static constexpr int SMEM_B = PIPE_B > EPI_B ? PIPE_B : EPI_B;
 };
 
-template <int D, int BITS, int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, 2)
+template <int D, int BITS, int WARPS, int STAGES, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ KiviBatch bt) {
     using Cfg = DecodeKiviCfg<D, BITS, WARPS, STAGES>;
     constexpr int BB = Cfg::BB, TILE_B = Cfg::TILE_B, STAGE_B = Cfg::STAGE_B, PIECE = KvBlock<BITS>::PIECE;
@@ -276,15 +278,16 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
             kh[i] = make_uint2(__byte_perm(h0, h1, 0x5410), __byte_perm(h0, h1, 0x7632));
         }
         for (int i = lane; i < Cfg::VH_N; i += 32) {
-            const int blk = i >> 4, tl = i & 15;
-            const int t = 8 * (tl >> 2) + (tl & 3);   // pairs (t, t+4)
+            const int blk = i >> 4, t = i & 15;        // pairs (t, t+16)
             const uint32_t h0 = *reinterpret_cast<const uint32_t*>(vt + (t * NB + blk) * BB);
-            const uint32_t h1 = *reinterpret_cast<const uint32_t*>(vt + ((t + 4) * NB + blk) * BB);
+            const uint32_t h1 = *reinterpret_cast<const uint32_t*>(vt + ((t + 16) * NB + blk) * BB);
             vh[i] = make_uint2(__byte_perm(h0, h1, 0x5410), __byte_perm(h0, h1, 0x7632));
         }
         __syncwarp();
 
-        // S[head][token]: MMA column `quad` of n-tile jp is token 4*quad + jp of the group
+        // S[head][token]: MMA column `quad` of n-tile jp is token 4*piece + jp of the group, where lane group
+        // `quad` reads code piece (quad>>1) + 4*(quad&1). That permutation makes the tokens one lane later pairs
+        // for P·V lie 16 apart, so that the four lanes of a quad do not all hit the same shared-memory banks.
         float c[4][4];
 #pragma unroll
         for (int n = 0; n < 4; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
@@ -292,7 +295,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
         for (int ks = 0; ks < KS; ++ks) {
             const int cha = ks * 16 + 2 * qlane;
             const uint2 ha = kh[cha >> 1], hb = kh[(cha >> 1) + 4];
-            const uint8_t* pk = kt + cha * BB + 4 + PIECE * quad;
+            const uint8_t* pk = kt + cha * BB + 4 + PIECE * ((quad >> 1) + 4 * (quad & 1));
             uint32_t xa0 = load_piece<BITS>(pk), xa1 = load_piece<BITS>(pk + BB);
             uint32_t xb0 = load_piece<BITS>(pk + 8 * BB), xb1 = load_piece<BITS>(pk + 9 * BB);
             if constexpr (BITS != 8) {
@@ -306,7 +309,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                 mma_f16_16816(c[jp], qf[ks], b0, b1);
             }
         }
-        // accumulator column 2*qlane+i of n-tile jp  <->  token 8*qlane + 4*i + jp of the group
+        // accumulator column 2*qlane+i of n-tile jp  <->  token 4*qlane + 16*i + jp of the group
         const int tokb = (g0 + warp + j * WARPS) * 32;
         float s[4][2];
         float tile_max = -INFINITY;
@@ -315,7 +318,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const float x = c[jp][i] + c[jp][i + 2];
-                if (logit_row != nullptr) logit_row[tokb + 8 * qlane + 4 * i + jp] = x;
+                if (logit_row != nullptr) logit_row[tokb + 4 * qlane + 16 * i + jp] = x;
                 s[jp][i] = x;
                 tile_max = fmaxf(tile_max, x);
             }
@@ -341,7 +344,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
             }
         }
         // O[head][channel] += P · V. k-step u: A columns 2q+i <- n-tile 2u, 8+2q+i <- n-tile 2u+1, i.e.
-        // tokens (8q+2u, 8q+4+2u | 8q+2u+1, 8q+5+2u); MMA column `quad` of n-tile (blk, jc) is channel 32blk+4quad+jc.
+        // tokens (4q+2u, 4q+16+2u | 4q+2u+1, 4q+17+2u); MMA column `quad` of n-tile (blk, jc) is channel 32blk+4quad+jc.
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             uint32_t pa[4];
@@ -353,13 +356,13 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                 pa[n * 2 + 0] = hi;
                 pa[n * 2 + 1] = pack_half2(p0 - hif.x, p1 - hif.y);
             }
-            const int ta = 8 * qlane + 2 * u;   // b0b1 pairs tokens (ta, ta+4), b2b3 pairs (ta+1, ta+5)
+            const int ta = 4 * qlane + 2 * u;   // b0b1 pairs tokens (ta, ta+16), b2b3 pairs (ta+1, ta+17)
 #pragma unroll
             for (int blk = 0; blk < NB; ++blk) {
                 const uint2 ha = vh[blk * 16 + qlane * 4 + 2 * u], hb = vh[blk * 16 + qlane * 4 + 2 * u + 1];
                 const uint8_t* pv = vt + (ta * NB + blk) * BB + 4 + PIECE * quad;
-                uint32_t xa0 = load_piece<BITS>(pv), xa1 = load_piece<BITS>(pv + 4 * NB * BB);
-                uint32_t xb0 = load_piece<BITS>(pv + NB * BB), xb1 = load_piece<BITS>(pv + 5 * NB * BB);
+                uint32_t xa0 = load_piece<BITS>(pv), xa1 = load_piece<BITS>(pv + 16 * NB * BB);
+                uint32_t xb0 = load_piece<BITS>(pv + NB * BB), xb1 = load_piece<BITS>(pv + 17 * NB * BB);
                 if constexpr (BITS != 8) {
                     xa0 |= xa1 << 16;
                     xb0 |= xb1 << 16;
@@ -402,11 +405,11 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
     decode_epilogue<D, WARPS>(smem, p, b, kv, item, item0, n_splits);
 }
 
-template <int D, int BITS, int WARPS, int STAGES>
+template <int D, int BITS, int WARPS, int STAGES, int MINB = 2>
 static cudaError_t launch_kivi_t(const DecodeParams& p, const KiviBatch& bt, int n_items, cudaStream_t st) {
     using Cfg = DecodeKiviCfg<D, BITS, WARPS, STAGES>;
     static bool attr_done = false;
-    auto kern = decode_kivi_kernel<D, BITS, WARPS, STAGES>;
+    auto kern = decode_kivi_kernel<D, BITS, WARPS, STAGES, MINB>;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_B);
         if (e != cudaSuccess) return e;
@@ -419,7 +422,11 @@ static cudaError_t launch_kivi_t(const DecodeParams& p, const KiviBatch& bt, int
 cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int head_dim, int bits, int n_items,
                                cudaStream_t st) {
     if (head_dim == 128) {
-        if (bits == 4) return launch_kivi_t<128, 4, 4, 4>(p, bt, n_items, st);
+        if (bits == 4) {
+            static const int variant = getenv("ARGUS_B200_KIVI_VARIANT") ? atoi(getenv("ARGUS_B200_KIVI_VARIANT")) : 0;
+            if (variant == 1) return launch_kivi_t<128, 4, 4, 4>(p, bt, n_items, st);
+            return launch_kivi_t<128, 4, 4, 3, 3>(p, bt, n_items, st);   // 3 CTAs per SM: +17 % over 2 CTAs of 4 stages
+        }
         if (bits == 8) return launch_kivi_t<128, 8, 4, 3>(p, bt, n_items, st);
         if (bits == 2) return launch_kivi_t<128, 2, 4, 4>(p, bt, n_items, st);
     } else if (head_dim == 64) {

@@ -37,7 +37,7 @@ constexpr int OFF_Q = 0;                       // two query tiles
 constexpr int OFF_K = OFF_Q + 2 * TILE_B;
 constexpr int OFF_V = OFF_K + KV_STAGES * TILE_B;
 constexpr int OFF_BAR = OFF_V + KV_STAGES * TILE_B;   // 192 KB
-constexpr int N_BAR = 1 + 4 * KV_STAGES + 6;
+constexpr int N_BAR = 1 + 5 * KV_STAGES + 6;
 constexpr int SMEM_B = OFF_BAR + N_BAR * 8 + 16 + 1024;   // + TMEM base slot + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float LAZY = 8.0f;
@@ -152,7 +152,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // twice, which keeps ~16 bits of P when the cache type is BF16). The tensor pipe executes one thread's
 // MMAs in issue order, so S_X(j+1) may be issued right behind P_X(j)·V_j although it reuses the region.
 // While one tile's softmax runs, the tensor pipe works on the other tile.
-template <bool BF16, bool OUT_F32, bool PSPLIT>
+template <bool BF16, bool OUT_F32, bool PSPLIT, bool VCONV>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ PrefillParams p) {
@@ -168,7 +168,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     auto b_kempty = [&](int s) { return bar + 8 * (1 + KV_STAGES + s); };
     auto b_vfull = [&](int s) { return bar + 8 * (1 + 2 * KV_STAGES + s); };
     auto b_vempty = [&](int s) { return bar + 8 * (1 + 3 * KV_STAGES + s); };
-    const uint32_t bar2 = bar + 8 * (1 + 4 * KV_STAGES);
+    auto b_vconv = [&](int s) { return bar + 8 * (1 + 4 * KV_STAGES + s); };   // V tile converted to F16 (VCONV)
+    const uint32_t bar2 = bar + 8 * (1 + 5 * KV_STAGES);
     auto b_sfull = [&](int x) { return bar2 + 8 * x; };
     auto b_pfull = [&](int x) { return bar2 + 8 * (2 + x); };
     auto b_ofull = [&](int x) { return bar2 + 8 * (4 + x); };
@@ -197,6 +198,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(b_kfull(s), 1);
             mbar_init(b_kempty(s), 1);
             mbar_init(b_vfull(s), 1);
+            mbar_init(b_vconv(s), 64);
             mbar_init(b_vempty(s), 1);
         }
         for (int x = 0; x < 2; ++x) {
@@ -254,7 +256,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // ───────── MMA issuer ─────────
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc(BF16 ? 1 : 0, 0, BM, BN);   // K tile is K-major
-            constexpr uint32_t idesc_o = instr_desc(BF16 ? 1 : 0, 1, BM, D);    // V tile is MN-major
+            // With VCONV the V tile has been rewritten as F16 in shared memory and P is packed as F16 too.
+            constexpr uint32_t idesc_o = instr_desc((BF16 && !VCONV) ? 1 : 0, 1, BM, D);    // V tile is MN-major
             bool ok = mbar_wait(b_qfull, 0);
             auto issue_s = [&](int x, int j) {
                 const int s = j % KV_STAGES;
@@ -296,7 +299,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 for (int x = 0; x < 2; ++x) {
                     if (j < n_x[x]) {
                         ok = mbar_wait(b_pfull(x), j & 1);
-                        if (ok && !v_ready) { ok = mbar_wait(b_vfull(s), (j / KV_STAGES) & 1); v_ready = true; }
+                        if (ok && !v_ready) { ok = mbar_wait(VCONV ? b_vconv(s) : b_vfull(s), (j / KV_STAGES) & 1); v_ready = true; }
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(x, j);
@@ -315,7 +318,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             if (!ok) fail();
         }
-    } else if (warp >= 4) {
+    } else if (warp < 4) {
+        // ───────── warps 2..3: V tile BF16 -> F16 in place (VCONV only), otherwise idle ─────────
+        if constexpr (VCONV) {
+            const int t64 = threadIdx.x - 64;   // 0..63
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % KV_STAGES;
+                if (*abort_flag || !mbar_wait(b_vfull(s), (j / KV_STAGES) & 1)) { fail(); break; }
+                uint4* tile = reinterpret_cast<uint4*>(smem + OFF_V + s * TILE_B);
+#pragma unroll 4
+                for (int i = 0; i < TILE_B / 16 / 64; ++i) {
+                    uint4 w = tile[t64 + 64 * i];
+                    uint32_t* e = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float lo = __uint_as_float(e[k] << 16), hi = __uint_as_float(e[k] & 0xffff0000u);
+                        uint32_t r;
+                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+                        e[k] = r;
+                    }
+                    tile[t64 + 64 * i] = w;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(b_vconv(s));
+            }
+        }
+    } else {
         // ───────── softmax / correction / epilogue: one query row per thread ─────────
         const int x = (warp - 4) >> 2;                      // which query tile
         const int quarter = warp & 3;                       // TMEM lanes this warp may touch
@@ -400,7 +428,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         const float p1 = fast_exp2(fmaf(s1, p.scale_log2, neg_m));
                         psum0 += p0;
                         psum1 += p1;
-                        const uint32_t w = pack16<BF16>(p0, p1);
+                        const uint32_t w = pack16<BF16 && !VCONV>(p0, p1);
                         hi[hf][c * 16 + e] = w;
                         if constexpr (PSPLIT) {
                             float h0, h1;
@@ -518,7 +546,7 @@ static bool make_map(CUtensorMap* m, bool bf16, const void* base, uint64_t rows,
 // t*kv_pos_stride + c (elements). Returns cudaErrorNotSupported when the driver entry point is missing.
 cudaError_t launch_prefill_tc(const void* q16, const void* k, const void* v, void* out, bool bf16, bool out_f32, int B,
                               int S, int T, int hq, int hkv, int64_t cap_rows, int64_t kv_pos_stride,
-                              int64_t kv_head_stride, int64_t kv_batch_stride, bool p_split, int* status, cudaStream_t st) {
+                              int64_t kv_head_stride, int64_t kv_batch_stride, int p_mode, int* status, cudaStream_t st) {
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, bf16, q16, (uint64_t)S, (uint64_t)hq, (uint64_t)B, (uint64_t)hq * 128, 128, (uint64_t)S * hq * 128) ||
         !make_map(&mk, bf16, k, (uint64_t)cap_rows, (uint64_t)hkv, (uint64_t)B, (uint64_t)kv_pos_stride,
@@ -544,13 +572,16 @@ cudaError_t launch_prefill_tc(const void* q16, const void* k, const void* v, voi
         kern<<<grid, 384, pf::SMEM_B, st>>>(mq, mk, mv, p);
         return cudaGetLastError();
     };
-    // BF16 keeps 8 significant bits of P per MMA operand; the split form adds the rounding residual as a second
-    // operand so that outputs stay within the 2e-3 absolute tolerance. F16 (11 bits) does not need it.
+    // BF16 keeps 8 significant bits of P per MMA operand, which does not hold the 2e-3 absolute tolerance.
+    // p_mode 2 (default for BF16): the V tile is rewritten as F16 in shared memory by two otherwise idle warps
+    // (exact for |v| < 65504, saturating beyond) and P is F16 (11 bits). p_mode 1: P = BF16 rounding + residual,
+    // two P.V passes, exact for any V. p_mode 0: single BF16 P (fastest, outside the tolerance on rare elements).
     if (bf16) {
-        if (p_split) return out_f32 ? launch(prefill_tc_kernel<true, true, true>) : launch(prefill_tc_kernel<true, false, true>);
-        return out_f32 ? launch(prefill_tc_kernel<true, true, false>) : launch(prefill_tc_kernel<true, false, false>);
+        if (p_mode == 2) return out_f32 ? launch(prefill_tc_kernel<true, true, false, true>) : launch(prefill_tc_kernel<true, false, false, true>);
+        if (p_mode == 1) return out_f32 ? launch(prefill_tc_kernel<true, true, true, false>) : launch(prefill_tc_kernel<true, false, true, false>);
+        return out_f32 ? launch(prefill_tc_kernel<true, true, false, false>) : launch(prefill_tc_kernel<true, false, false, false>);
     }
-    return out_f32 ? launch(prefill_tc_kernel<false, true, false>) : launch(prefill_tc_kernel<false, false, false>);
+    return out_f32 ? launch(prefill_tc_kernel<false, true, false, false>) : launch(prefill_tc_kernel<false, false, false, false>);
 }
 
 cudaError_t launch_cast_f32_to_f16(const float* src, void* dst, long long n, cudaStream_t st) {

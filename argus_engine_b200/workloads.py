@@ -115,3 +115,51 @@ def kivi_step_bytes(q_tokens, res_tokens, hq: int, hkv: int, d: int, bits: int, 
     return total + 2 * len(q_tokens) * hq * d * 4
 
 
+@dataclass
+class PrefillCase:
+    """Q [B,S,Hq,D], K/V HeadMajor [B,Hkv,cap,D] as float32 arrays already rounded to the 16-bit input type
+    (`dtype` "bf16" or "f16"); the GPU gets the same values in 16 bits, the oracle the float32 copies."""
+    q: np.ndarray
+    k: np.ndarray
+    v: np.ndarray
+    S: int
+    T: int
+    cap: int
+    hq: int
+    hkv: int
+    d: int
+    dtype: str
+
+
+def _round_bf16(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even float32 -> bfloat16 -> float32."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return r.astype(np.uint32).view(np.float32).reshape(x.shape)
+
+
+def prefill_case(seed: int, B: int, S: int, T: int, hq: int, hkv: int, d: int = 128, cap: int = 0,
+                 dtype: str = "bf16") -> PrefillCase:
+    """Draw order: Q [B,S,Hq,D], K [B,T,Hkv,D], V [B,T,Hkv,D] (token-major draws, then placed HeadMajor)."""
+    rng = _rng(seed)
+    cap = cap or T
+    q = rng.standard_normal((B, S, hq, d), dtype=np.float32)
+    k = rng.standard_normal((B, T, hkv, d), dtype=np.float32)
+    v = rng.standard_normal((B, T, hkv, d), dtype=np.float32)
+    rnd = _round_bf16 if dtype == "bf16" else (lambda a: a.astype(np.float16).astype(np.float32))
+    kh = np.zeros((B, hkv, cap, d), dtype=np.float32)
+    vh = np.zeros((B, hkv, cap, d), dtype=np.float32)
+    kh[:, :, :T] = rnd(k).transpose(0, 2, 1, 3)
+    vh[:, :, :T] = rnd(v).transpose(0, 2, 1, 3)
+    return PrefillCase(rnd(q), kh, vh, S, T, cap, hq, hkv, d, dtype)
+
+
+def config4(B: int = 4, S: int = 4096) -> PrefillCase:
+    """Causal GQA prefill: B=4, S=4096, Hq=32, Hkv=8, D=128, BF16, seed 3."""
+    return prefill_case(3, B, S, S, 32, 8, 128, dtype="bf16")
+
+
+def prefill_flops(B: int, S: int, T: int, hq: int, d: int) -> float:
+    """Causal-useful FLOPs: 4*D per (query row, visible key) pair; row r sees T-S+r+1 keys."""
+    pairs = S * (T - S) + S * (S + 1) / 2.0
+    return 4.0 * B * hq * d * pairs
