@@ -32,12 +32,12 @@ namespace pf {
 constexpr int BM = 128, BN = 128, D = 128;
 constexpr int TILE_B = BM * D * 2;          // 32 KB: one Q/K/V/P tile of 16-bit elements
 constexpr int HALF_B = TILE_B / 2;          // one 64-column (128-byte wide) swizzled block of a tile
-constexpr int KV_STAGES = 2;
+constexpr int K_STAGES = 3, V_STAGES = 2;      // K is needed one tile ahead of V (S_{j+1} is issued before P_j·V_j)
 constexpr int OFF_Q = 0;                       // two query tiles
 constexpr int OFF_K = OFF_Q + 2 * TILE_B;
-constexpr int OFF_V = OFF_K + KV_STAGES * TILE_B;
-constexpr int OFF_BAR = OFF_V + KV_STAGES * TILE_B;   // 192 KB
-constexpr int N_BAR = 1 + 5 * KV_STAGES + 6;
+constexpr int OFF_V = OFF_K + K_STAGES * TILE_B;
+constexpr int OFF_BAR = OFF_V + V_STAGES * TILE_B;   // 224 KB
+constexpr int N_BAR = 1 + 2 * K_STAGES + 3 * V_STAGES + 6;
 constexpr int SMEM_B = OFF_BAR + N_BAR * 8 + 16 + 1024;   // + TMEM base slot + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float LAZY = 8.0f;
@@ -136,6 +136,25 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
         : "memory");
 }
+// Packed F32 pairs (sm_100): one issue slot for two FMAs / adds.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -165,11 +184,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t bar = smem0 + OFF_BAR;
     const uint32_t b_qfull = bar;
     auto b_kfull = [&](int s) { return bar + 8 * (1 + s); };
-    auto b_kempty = [&](int s) { return bar + 8 * (1 + KV_STAGES + s); };
-    auto b_vfull = [&](int s) { return bar + 8 * (1 + 2 * KV_STAGES + s); };
-    auto b_vempty = [&](int s) { return bar + 8 * (1 + 3 * KV_STAGES + s); };
-    auto b_vconv = [&](int s) { return bar + 8 * (1 + 4 * KV_STAGES + s); };   // V tile converted to F16 (VCONV)
-    const uint32_t bar2 = bar + 8 * (1 + 5 * KV_STAGES);
+    auto b_kempty = [&](int s) { return bar + 8 * (1 + K_STAGES + s); };
+    auto b_vfull = [&](int s) { return bar + 8 * (1 + 2 * K_STAGES + s); };
+    auto b_vempty = [&](int s) { return bar + 8 * (1 + 2 * K_STAGES + V_STAGES + s); };
+    auto b_vconv = [&](int s) { return bar + 8 * (1 + 2 * K_STAGES + 2 * V_STAGES + s); };   // V tile converted to F16 (VCONV)
+    const uint32_t bar2 = bar + 8 * (1 + 2 * K_STAGES + 3 * V_STAGES);
     auto b_sfull = [&](int x) { return bar2 + 8 * x; };
     auto b_pfull = [&](int x) { return bar2 + 8 * (2 + x); };
     auto b_ofull = [&](int x) { return bar2 + 8 * (4 + x); };
@@ -194,9 +213,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     if (threadIdx.x == 0) {
         mbar_init(b_qfull, 1);
-        for (int s = 0; s < KV_STAGES; ++s) {
+        for (int s = 0; s < K_STAGES; ++s) {
             mbar_init(b_kfull(s), 1);
             mbar_init(b_kempty(s), 1);
+        }
+        for (int s = 0; s < V_STAGES; ++s) {
             mbar_init(b_vfull(s), 1);
             mbar_init(b_vconv(s), 64);
             mbar_init(b_vempty(s), 1);
@@ -240,16 +261,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tma_load_4d(smem0 + OFF_Q + x * TILE_B + HALF_B, &tm_q, b_qfull, 64, r0 + x * BM, h, b);
             }
             for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
-                const int s = j % KV_STAGES;
-                const uint32_t ph = (j / KV_STAGES) & 1;
-                if (j >= KV_STAGES && !mbar_wait(b_kempty(s), ph ^ 1)) { fail(); break; }
+                const int s = j % K_STAGES, sv = j % V_STAGES;
+                if (j >= K_STAGES && !mbar_wait(b_kempty(s), ((j / K_STAGES) & 1) ^ 1)) { fail(); break; }
                 mbar_expect_tx(b_kfull(s), TILE_B);
                 tma_load_4d(smem0 + OFF_K + s * TILE_B, &tm_k, b_kfull(s), 0, j * BN, kvh, b);
                 tma_load_4d(smem0 + OFF_K + s * TILE_B + HALF_B, &tm_k, b_kfull(s), 64, j * BN, kvh, b);
-                if (j >= KV_STAGES && !mbar_wait(b_vempty(s), ph ^ 1)) { fail(); break; }
-                mbar_expect_tx(b_vfull(s), TILE_B);
-                tma_load_4d(smem0 + OFF_V + s * TILE_B, &tm_v, b_vfull(s), 0, j * BN, kvh, b);
-                tma_load_4d(smem0 + OFF_V + s * TILE_B + HALF_B, &tm_v, b_vfull(s), 64, j * BN, kvh, b);
+                if (j >= V_STAGES && !mbar_wait(b_vempty(sv), ((j / V_STAGES) & 1) ^ 1)) { fail(); break; }
+                mbar_expect_tx(b_vfull(sv), TILE_B);
+                tma_load_4d(smem0 + OFF_V + sv * TILE_B, &tm_v, b_vfull(sv), 0, j * BN, kvh, b);
+                tma_load_4d(smem0 + OFF_V + sv * TILE_B + HALF_B, &tm_v, b_vfull(sv), 64, j * BN, kvh, b);
             }
         }
     } else if (warp == 1) {
@@ -260,7 +280,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             constexpr uint32_t idesc_o = instr_desc((BF16 && !VCONV) ? 1 : 0, 1, BM, D);    // V tile is MN-major
             bool ok = mbar_wait(b_qfull, 0);
             auto issue_s = [&](int x, int j) {
-                const int s = j % KV_STAGES;
+                const int s = j % K_STAGES;
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const uint32_t qa = smem0 + OFF_Q + x * TILE_B + (k >> 2) * HALF_B + (k & 3) * 32;
@@ -270,7 +290,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_commit(b_sfull(x));
             };
             auto issue_pv = [&](int x, int j) {
-                const int s = j % KV_STAGES;
+                const int s = j % V_STAGES;
 #pragma unroll
                 for (int pass = 0; pass < (PSPLIT ? 2 : 1); ++pass)
 #pragma unroll
@@ -292,21 +312,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
             for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
-                const int s = j % KV_STAGES;
+                const int s = j % V_STAGES;
                 const bool more = (j + 1 < n_tiles);
                 bool v_ready = false, k_ready = false;
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     if (j < n_x[x]) {
                         ok = mbar_wait(b_pfull(x), j & 1);
-                        if (ok && !v_ready) { ok = mbar_wait(VCONV ? b_vconv(s) : b_vfull(s), (j / KV_STAGES) & 1); v_ready = true; }
+                        if (ok && !v_ready) { ok = mbar_wait(VCONV ? b_vconv(s) : b_vfull(s), (j / V_STAGES) & 1); v_ready = true; }
                         if (!ok) break;
                         tc_fence_after();
                         issue_pv(x, j);
                         if (j + 1 >= n_x[x]) tc_commit(b_ofull(x));
                     }
                     if (j + 1 < n_x[x]) {
-                        if (!k_ready) { ok = mbar_wait(b_kfull((j + 1) % KV_STAGES), ((j + 1) / KV_STAGES) & 1); k_ready = true; }
+                        if (!k_ready) { ok = mbar_wait(b_kfull((j + 1) % K_STAGES), ((j + 1) / K_STAGES) & 1); k_ready = true; }
                         if (!ok) break;
                         tc_fence_after();
                         issue_s(x, j + 1);
@@ -314,7 +334,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 if (!ok) break;
                 tc_commit(b_vempty(s));
-                if (more) tc_commit(b_kempty((j + 1) % KV_STAGES));
+                if (more) tc_commit(b_kempty((j + 1) % K_STAGES));
             }
             if (!ok) fail();
         }
@@ -323,8 +343,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if constexpr (VCONV) {
             const int t64 = threadIdx.x - 64;   // 0..63
             for (int j = 0; j < n_tiles; ++j) {
-                const int s = j % KV_STAGES;
-                if (*abort_flag || !mbar_wait(b_vfull(s), (j / KV_STAGES) & 1)) { fail(); break; }
+                const int s = j % V_STAGES;
+                if (*abort_flag || !mbar_wait(b_vfull(s), (j / V_STAGES) & 1)) { fail(); break; }
                 uint4* tile = reinterpret_cast<uint4*>(smem + OFF_V + s * TILE_B);
 #pragma unroll 4
                 for (int i = 0; i < TILE_B / 16 / 64; ++i) {
@@ -400,7 +420,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-            float psum0 = 0.f, psum1 = 0.f;
+            uint64_t psum2 = pack_f32x2(0.f, 0.f);
+            const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
             // pass 2: p = exp2(s*scale - m), packed to 16 bits. P overwrites S in place: the first half's results
             // are stored only after the second half of S has been read.
             uint32_t hi[2][32], lo[PSPLIT ? 2 : 1][PSPLIT ? 32 : 1];
@@ -424,10 +445,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             if (kc > qi) s0 = -INFINITY;
                             if (kc + 1 > qi) s1 = -INFINITY;
                         }
-                        const float p0 = fast_exp2(fmaf(s0, p.scale_log2, neg_m));
-                        const float p1 = fast_exp2(fmaf(s1, p.scale_log2, neg_m));
-                        psum0 += p0;
-                        psum1 += p1;
+                        float x0, x1;
+                        unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), scale2, negm2), x0, x1);
+                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                        psum2 = add_f32x2(psum2, pack_f32x2(p0, p1));
                         const uint32_t w = pack16<BF16 && !VCONV>(p0, p1);
                         hi[hf][c * 16 + e] = w;
                         if constexpr (PSPLIT) {
@@ -446,6 +467,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             tmem_st32(t_s + 32, hi[1]);
             if constexpr (PSPLIT) tmem_st32(t_s + 96, lo[1]);
+            float psum0, psum1;
+            unpack_f32x2(psum2, psum0, psum1);
             l = l * alpha + (psum0 + psum1);
             tmem_wait_st();
             tc_fence_before();
