@@ -101,6 +101,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -381,25 +388,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // pass 1: row maximum (the S row is read twice from tensor memory rather than held in 128 registers)
             const bool diag = (j * BN + BN - 1 > q_start + r0 + x * BM);   // some key of this tile may be masked
             float mx = -INFINITY;
+            {
+                // four independent max chains
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                uint32_t sv[2][32];
-                tmem_ld32(t_s + hf * 64, sv[0]);
-                tmem_ld32(t_s + hf * 64 + 32, sv[1]);
-                tmem_wait_ld();
-                if (diag) {
+                for (int hf = 0; hf < 2; ++hf) {
+                    uint32_t sv[2][32];
+                    tmem_ld32(t_s + hf * 64, sv[0]);
+                    tmem_ld32(t_s + hf * 64 + 32, sv[1]);
+                    tmem_wait_ld();
+                    if (diag) {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c)
+                        for (int c = 0; c < 2; ++c)
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (j * BN + hf * 64 + c * 32 + i <= qi) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
-                } else {
+                            for (int i = 0; i < 32; ++i)
+                                if (j * BN + hf * 64 + c * 32 + i <= qi)
+                                    m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[c][i]));
+                    } else {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c)
+                        for (int c = 0; c < 2; ++c)
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            mx = max3(mx, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+                            for (int i = 0; i < 32; i += 2)
+                                m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+                    }
                 }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
             const float m_tile = mx * p.scale_log2;
             float alpha = 1.f;
@@ -420,8 +433,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-            uint64_t psum2 = pack_f32x2(0.f, 0.f);
+            uint64_t psum2 = pack_f32x2(0.f, 0.f), psum2b = pack_f32x2(0.f, 0.f);
             const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
+            if constexpr (!PSPLIT) {
+                // pass 2, pipelined by 32-key chunks: chunk c+1 is in flight while chunk c is turned into P.
+                // P chunk c (16 packed columns at 16c) lands inside S chunk c/2, which has been read by then.
+                uint32_t sbuf[2][32];
+                tmem_ld32(t_s, sbuf[0]);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    if (c + 1 < 4) tmem_ld32(t_s + (c + 1) * 32, sbuf[(c + 1) & 1]);
+                    uint32_t hi16[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        float s0 = __uint_as_float(sbuf[c & 1][2 * e]), s1 = __uint_as_float(sbuf[c & 1][2 * e + 1]);
+                        if (diag) {
+                            const int kc = j * BN + c * 32 + 2 * e;
+                            if (kc > qi) s0 = -INFINITY;
+                            if (kc + 1 > qi) s1 = -INFINITY;
+                        }
+                        float x0, x1;
+                        unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), scale2, negm2), x0, x1);
+                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                        if (e & 1) psum2b = add_f32x2(psum2b, pack_f32x2(p0, p1));
+                        else psum2 = add_f32x2(psum2, pack_f32x2(p0, p1));
+                        hi16[e] = pack16<BF16 && !VCONV>(p0, p1);
+                    }
+                    if (c + 1 < 4) tmem_wait_ld();
+                    tmem_st16(t_s + c * 16, hi16);
+                }
+            } else {
             // pass 2: p = exp2(s*scale - m), packed to 16 bits. P overwrites S in place: the first half's results
             // are stored only after the second half of S has been read.
             uint32_t hi[2][32], lo[PSPLIT ? 2 : 1][PSPLIT ? 32 : 1];
@@ -467,6 +509,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             tmem_st32(t_s + 32, hi[1]);
             if constexpr (PSPLIT) tmem_st32(t_s + 96, lo[1]);
+            }
+            psum2 = add_f32x2(psum2, psum2b);
             float psum0, psum1;
             unpack_f32x2(psum2, psum0, psum1);
             l = l * alpha + (psum0 + psum1);
