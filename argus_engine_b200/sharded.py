@@ -45,6 +45,21 @@ class ShardedDecoder:
         self.part = torch.zeros(self.part_len, dtype=torch.float32, device=device)
         self.parts = torch.zeros(self.world, self.part_len, dtype=torch.float32, device=device)
 
+    def capture(self, q: torch.Tensor, out: torch.Tensor):
+        """Record one step (kernel, gather, merge) on static tensors into a CUDA graph and return it; replaying it
+        removes the host launch cost, which at 8 GPUs is larger than the device time of a step. Returns None when
+        the capture is not possible (the caller keeps calling step())."""
+        try:
+            self.step(q, out)                      # warm-up outside the capture (lazy initialisation, NCCL setup)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.step(q, out)
+            return g
+        except Exception:
+            torch.cuda.synchronize()
+            return None
+
     def step(self, q: torch.Tensor, out: torch.Tensor) -> None:
         self.partial_fn(q, self.part)
         if self.world > 1:
