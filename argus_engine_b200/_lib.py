@@ -101,6 +101,9 @@ def load_library() -> C.CDLL:
     lib.argus_b200_check_status.argtypes = [vp, vp]
     lib.argus_b200_flash_attention_prefill.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i32, i32, i32]
     lib.argus_b200_lse_merge.argtypes = [vp, vp, vp, i32, i64, i32, i32, vp, vp]
+    lib.argus_b200_exchange_merge.argtypes = [vp, vp, vp, C.POINTER(vp), C.POINTER(vp), i32, i32, i32, vp, i64, i64, i32, i32,
+                                              vp, vp, i32]
+    lib.argus_b200_step_increment.argtypes = [vp, vp, vp]
     lib.argus_b200_attention_gen_static.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64]
     lib.argus_b200_static_scratch_bytes.restype = C.c_size_t
     lib.argus_b200_static_last_error.restype = C.c_char_p

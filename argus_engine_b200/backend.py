@@ -221,6 +221,22 @@ class B200Backend:
                                                    parts.stride(0), num_heads_q, head_dim, out.data_ptr(),
                                                    _ptr(lse_out)))
 
+    def exchange_merge(self, local_part: torch.Tensor, peer_parts, peer_flags, rank: int, num_heads_q: int, head_dim: int,
+                       out: torch.Tensor, step: int = 0, step_dev: Optional[torch.Tensor] = None,
+                       parts_parity_stride: int = 0, flags_parity_stride: int = 0,
+                       lse_out: Optional[torch.Tensor] = None, phases: int = 3) -> None:
+        """Fused peer exchange + merge. peer_parts / peer_flags: device pointers (ints), one per rank, valid on this
+        GPU. Give the step number as `step` (host) or `step_dev` (int32 device tensor, see step_increment)."""
+        n = len(peer_parts)
+        pp = (C.c_void_p * n)(*peer_parts)
+        pf = (C.c_void_p * n)(*peer_flags)
+        self._check(self._lib.argus_b200_exchange_merge(
+            self._h, self._stream(), local_part.data_ptr(), pp, pf, n, rank, step, _ptr(step_dev), parts_parity_stride,
+            flags_parity_stride, num_heads_q, head_dim, out.data_ptr(), _ptr(lse_out), phases))
+
+    def step_increment(self, step_dev: torch.Tensor) -> None:
+        self._check(self._lib.argus_b200_step_increment(self._h, self._stream(), step_dev.data_ptr()))
+
     def check_status(self) -> int:
         """Synchronises the current stream; non-zero if a kernel's bounded wait ran out since the last check."""
         return int(self._lib.argus_b200_check_status(self._h, self._stream()))

@@ -94,7 +94,7 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
         return ARGUS_B200_E_INVALID;
     }
     const int g = hq / hkv;
-    if (kv_dtype != ARGUS_B200_KV_F16 || (d != 64 && d != 128) || g > kMaxGroup) {
+    if ((kv_dtype != ARGUS_B200_KV_F16 && kv_dtype != ARGUS_B200_KV_F32) || (d != 64 && d != 128) || g > kMaxGroup) {
         ctx->set_error("attention_gen: unsupported (kv_dtype=%d head_dim=%d group=%d)", kv_dtype, d, g);
         return ARGUS_B200_E_UNSUPPORTED;
     }
@@ -115,7 +115,8 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
         }
         if (s.seq_len > 0) {
             if (!s.k || !s.v || (reinterpret_cast<uintptr_t>(s.k) & 15) || (reinterpret_cast<uintptr_t>(s.v) & 15) ||
-                (s.head_stride & 7) || (s.pos_stride & 7) || s.pos_stride < d) {
+                (s.head_stride & (kv_dtype == ARGUS_B200_KV_F16 ? 7 : 3)) || (s.pos_stride & (kv_dtype == ARGUS_B200_KV_F16 ? 7 : 3)) ||
+                s.pos_stride < d) {
                 ctx->set_error("attention_gen: sequence %d: K/V must be 16-byte aligned with strides that are multiples of 8 elements", i);
                 return ARGUS_B200_E_INVALID;
             }
@@ -149,6 +150,30 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
 
     // scratch carve-up
     size_t cur = 0;
+    if (kv_dtype == ARGUS_B200_KV_F32) {
+        // F32 cache: the kernel runs on a packed F16 HeadMajor copy made in scratch
+        for (int i = 0; i < n_seqs; ++i) {
+            if (lens[i] == 0) continue;
+            const size_t bytes = (size_t)hkv * lens[i] * d * sizeof(__half);
+            float* kc = ctx->scratch(&cur, bytes);
+            float* vc = ctx->scratch(&cur, bytes);
+            if (!kc || !vc) {
+                ctx->set_error("attention_gen: the F16 copy of an F32 cache needs more scratch than %zu bytes", ctx->ws_bytes);
+                return ARGUS_B200_E_WORKSPACE;
+            }
+            cudaError_t ce = launch_kv_f32_to_f16(static_cast<const float*>(bt.k[i]), kc, hkv, lens[i], d, bt.head_stride[i],
+                                                  bt.pos_stride[i], st);
+            if (ce == cudaSuccess)
+                ce = launch_kv_f32_to_f16(static_cast<const float*>(bt.v[i]), vc, hkv, lens[i], d, bt.head_stride[i],
+                                          bt.pos_stride[i], st);
+            if (ce != cudaSuccess) return ctx->cuda_fail(ce, "kv cast launch");
+            ctx->launches += 2;
+            bt.k[i] = kc;
+            bt.v[i] = vc;
+            bt.head_stride[i] = lens[i] * d;
+            bt.pos_stride[i] = d;
+        }
+    }
     int* tickets = ctx->tickets;  // persistent, zero between calls
     if ((size_t)n_seqs * hkv > ctx->n_tickets) {
         ctx->set_error("attention_gen: %d ticket slots needed, %zu available", n_seqs * hkv, ctx->n_tickets);

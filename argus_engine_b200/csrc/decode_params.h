@@ -69,4 +69,19 @@ struct FinalizeParams {
     int32_t seq_len[kMaxBatch];
 };
 
+// Peer exchange + merge of a sequence-sharded decode (exchange_merge.cu).
+constexpr int kMaxRanks = 16;
+struct ExchangeParams {
+    float* peer_parts[kMaxRanks];   // receive buffer [n_ranks][Hq*D+Hq] of every rank (own entry = local memory)
+    int* peer_flags[kMaxRanks];     // flag array [n_ranks][Hq] of every rank
+    const float* local_part;        // this rank's partial: [Hq][D] outputs, then [Hq] lse
+    float* out;                     // [Hq][D]
+    float* lse_out;                 // [Hq], nullable
+    int* status;
+    const int* step_dev;            // nullable: step number in device memory (CUDA-graph replay)
+    long long parts_parity_stride;  // floats between the even-step and the odd-step receive buffers
+    long long flags_parity_stride;  // ints between the even-step and the odd-step flag arrays
+    int n_ranks, rank, step, hq, d, phases;
+};
+
 }  // namespace argus

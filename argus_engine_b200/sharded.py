@@ -44,6 +44,7 @@ class ShardedDecoder:
         self.part_len = num_heads_q * head_dim + num_heads_q
         self.part = torch.zeros(self.part_len, dtype=torch.float32, device=device)
         self.parts = torch.zeros(self.world, self.part_len, dtype=torch.float32, device=device)
+        self.exchange_fn = None   # set by make_gpu_decoder(..., fused=True): replaces gather + merge
 
     def capture(self, q: torch.Tensor, out: torch.Tensor):
         """Record one step (kernel, gather, merge) on static tensors into a CUDA graph and return it; replaying it
@@ -62,6 +63,9 @@ class ShardedDecoder:
 
     def step(self, q: torch.Tensor, out: torch.Tensor) -> None:
         self.partial_fn(q, self.part)
+        if self.exchange_fn is not None:
+            self.exchange_fn(self.part, out)
+            return
         if self.world > 1:
             dist.all_gather_into_tensor(self.parts.view(-1), self.part, group=self.group)
         else:
@@ -69,9 +73,35 @@ class ShardedDecoder:
         self.merge_fn(self.parts, out)
 
 
+class PeerBuffers:
+    """Receive buffers and flags of the fused exchange, in memory every rank of the node can address
+    (torch symmetric memory over NVLink). Layout per rank, in 4-byte words: two sets (even / odd steps) of
+    parts [N][Hq*D+Hq] floats, then two sets of flags [N][Hq] ints, all zero-initialised."""
+
+    def __init__(self, num_heads_q: int, head_dim: int, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        part_len = num_heads_q * head_dim + num_heads_q
+        self.parts_stride = self.world * part_len
+        self.flags_stride = self.world * num_heads_q
+        n_words = 2 * self.parts_stride + 2 * self.flags_stride
+        self.buf = symm_mem.empty(n_words, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        self.peer_parts = bases
+        self.peer_flags = [b + 4 * 2 * self.parts_stride for b in bases]
+
+
 def make_gpu_decoder(be, k_shard: torch.Tensor, v_shard: torch.Tensor, shard_len: int, num_heads_q: int,
-                     num_heads_kv: int, head_dim: int, group=None) -> ShardedDecoder:
-    """ShardedDecoder over the CUDA kernels of `be` (a B200Backend) for an F16 HeadMajor shard."""
+                     num_heads_kv: int, head_dim: int, group=None, fused: bool = False) -> ShardedDecoder:
+    """ShardedDecoder over the CUDA kernels of `be` (a B200Backend) for an F16 HeadMajor shard. With `fused` the
+    all-gather and the merge become one kernel that stores the partial into every rank's receive buffer over
+    NVLink peer pointers and merges when all flags have arrived (argus_b200_exchange_merge)."""
     from .backend import DecodeExtras
 
     hq, d = num_heads_q, head_dim
@@ -83,4 +113,16 @@ def make_gpu_decoder(be, k_shard: torch.Tensor, v_shard: torch.Tensor, shard_len
     def merge_fn(parts, out):
         be.lse_merge(parts, hq, d, out)
 
-    return ShardedDecoder(hq, d, partial_fn, merge_fn, k_shard.device, group)
+    dec = ShardedDecoder(hq, d, partial_fn, merge_fn, k_shard.device, group)
+    if fused and dec.world > 1:
+        peers = PeerBuffers(hq, d, group)
+        step_dev = torch.zeros(1, dtype=torch.int32, device=k_shard.device)
+
+        def exchange_fn(part, out):
+            be.step_increment(step_dev)   # the step number lives on the device so that a CUDA graph can replay this
+            be.exchange_merge(part, peers.peer_parts, peers.peer_flags, peers.rank, hq, d, out, step_dev=step_dev,
+                              parts_parity_stride=peers.parts_stride, flags_parity_stride=peers.flags_stride)
+
+        dec.exchange_fn = exchange_fn
+        dec._peers = peers   # keep the symmetric allocation alive
+    return dec

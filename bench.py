@@ -276,7 +276,12 @@ def sharded_c5(be, dist, world, rank, peaks, iters=20):
     k = torch.randn(hkv, hi - lo, d, device="cuda", generator=gen, dtype=torch.float32).to(torch.float16)
     v = torch.randn(hkv, hi - lo, d, device="cuda", generator=gen, dtype=torch.float32).to(torch.float16)
     q = torch.randn(hq, d, device="cuda", generator=torch.Generator(device="cuda").manual_seed(4))
-    dec = make_gpu_decoder(be, k, v, hi - lo, hq, hkv, d)
+    fused = world > 1 and os.environ.get("ARGUS_B200_SHARDED_NCCL") is None
+    try:
+        dec = make_gpu_decoder(be, k, v, hi - lo, hq, hkv, d, fused=fused)
+    except Exception:   # symmetric memory unavailable: NCCL all-gather + merge kernel
+        fused = False
+        dec = make_gpu_decoder(be, k, v, hi - lo, hq, hkv, d)
     out = torch.zeros(hq, d, device="cuda")
     for _ in range(3):
         dec.step(q, out)
@@ -304,7 +309,8 @@ def sharded_c5(be, dist, world, rank, peaks, iters=20):
             "us_per_layer_step": ms * 1e3, "value_tbs": nbytes / (ms * 1e-3) / 1e12,
             "frac_of_aggregate_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world),
             "gather_bytes_per_rank": (hq * d + hq) * 4, "scaling": "strong", "l2": "shard >= 537 MB > L2",
-            "launch": "CUDA graph replay of kernel + all-gather + merge" if graph is not None else "eager"}
+            "exchange": "fused peer-store exchange + merge kernel" if fused else "NCCL all-gather + merge kernel",
+            "launch": "CUDA graph replay of the step" if graph is not None else "eager"}
 
 
 def run_b200(args):

@@ -97,8 +97,9 @@ typedef struct argus_b200_decode_extras {
 /* Single-query GQA decode attention = Backend::attention_gen (engine/src/backend.rs:284-295; CUDA
  * implementation engine/src/backend/cuda_pc.rs:1693-1885 + attention_gen_f16kv_naive,
  * engine/src/backend/cuda_pc/kernels.cu:471-540). q [Hq][D] F32, out [Hq][D] F32,
- * scale = 1/sqrt(D) computed inside, no mask. kv_dtype: ARGUS_B200_KV_F16 (F32 is declined with
- * E_UNSUPPORTED in this version). D in {64,128}; Hq/Hkv <= 8 per KV head group. */
+ * scale = 1/sqrt(D) computed inside, no mask. kv_dtype: ARGUS_B200_KV_F16, or ARGUS_B200_KV_F32 (the cache is
+ * first rounded to a packed F16 copy in context scratch, 2*Hkv*T*D*2 bytes; strides then need only be
+ * multiples of 4 elements). D in {64,128}; Hq/Hkv <= 8 per KV head group. */
 ARGUS_B200_API int argus_b200_attention_gen(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_cache,
                              const void* v_cache, float* out, int num_heads_q, int num_heads_kv,
                              int head_dim, int64_t cache_seq_len, int kv_dtype, int64_t head_stride,
@@ -253,6 +254,24 @@ ARGUS_B200_API int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void*
 ARGUS_B200_API int argus_b200_lse_merge(argus_b200_ctx* ctx, void* stream, const float* parts, int n_parts,
                                         int64_t part_stride, int num_heads_q, int head_dim, float* out,
                                         float* lse_out);
+
+/* The same merge with the exchange fused in: instead of an all-gather, CTA h of every rank stores row h of its
+ * partial into slot `rank` of EVERY rank's receive buffer through NVLink peer pointers, raises a per-(rank, head)
+ * flag there to `step`, waits (bounded) for the flags of all ranks in its own flag array and merges. No
+ * counterpart in the reference (single device). peer_parts[s] / peer_flags[s] are device pointers valid on this
+ * GPU to rank s's receive buffer [n_ranks][Hq*D+Hq] floats and flag array [n_ranks][Hq] ints (zero-initialised
+ * once; e.g. a torch symmetric-memory allocation). The step number must grow by one per call on all ranks alike
+ * (starting at 1): pass it as `step`, or keep it in device memory (`step_dev`, bumped on the stream by
+ * argus_b200_step_increment) so that the call can be replayed from a CUDA graph. Odd steps use the buffers
+ * `*_parity_stride` elements behind the even ones, so that a fast rank's next push cannot overwrite what a slow
+ * rank still merges. phases: 3 normally; 1 (push only) and 2 (wait + merge only) exist for single-GPU tests.
+ * n_ranks <= 16. A wait that runs out zeroes the output and sets the status word. */
+ARGUS_B200_API int argus_b200_exchange_merge(argus_b200_ctx* ctx, void* stream, const float* local_part,
+                                             float* const* peer_parts, int* const* peer_flags, int n_ranks, int rank,
+                                             int step, const int* step_dev, int64_t parts_parity_stride,
+                                             int64_t flags_parity_stride, int num_heads_q, int head_dim, float* out,
+                                             float* lse_out, int phases);
+ARGUS_B200_API int argus_b200_step_increment(argus_b200_ctx* ctx, void* stream, int* step_dev);
 
 /* Blocks until `stream` is idle and returns the status word the kernels set when one of their bounded
  * waits ran out (0 = clean). The word is cleared by the call. */

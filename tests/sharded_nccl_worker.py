@@ -21,12 +21,16 @@ lo, hi = shard_range(T, world, rank)
 be = B200Backend(local)
 k = torch.from_numpy(np.ascontiguousarray(case.k[0][:, lo:hi])).cuda()
 v = torch.from_numpy(np.ascontiguousarray(case.v[0][:, lo:hi])).cuda()
-dec = make_gpu_decoder(be, k, v, hi - lo, hq, hkv, d)
-out = torch.zeros(hq, d, device="cuda")
-dec.step(torch.from_numpy(case.q[0]).cuda(), out)
-torch.cuda.synchronize()
 want, _ = orc.attention_gen(case.q[0], case.k[0].view(np.uint16), case.v[0].view(np.uint16), hq, hkv, d, T)
-np.testing.assert_allclose(out.cpu().numpy(), want, atol=2e-3, rtol=1e-2)
+qd = torch.from_numpy(case.q[0]).cuda()
+for fused in (False, True):      # NCCL all-gather + merge, then the fused peer exchange + merge (plain peer stores)
+    dec = make_gpu_decoder(be, k, v, hi - lo, hq, hkv, d, fused=fused)
+    for _ in range(3):           # several steps: the fused path alternates its two buffer sets
+        out = torch.full((hq, d), float("nan"), device="cuda")
+        dec.step(qd, out)
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(out.cpu().numpy(), want, atol=2e-3, rtol=1e-2)
+    assert be.check_status() == 0
 dist.barrier()
 if rank == 0:
     print("SHARDED_OK")

@@ -141,6 +141,23 @@ def test_many_splits_and_determinism(be):
     assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("seq_major", [False, True])
+def test_f32_kv_cache(be, seq_major):
+    """F32 K/V (engine/src/backend.rs:305-313): served through an F16 copy; the oracle reads the F32 values."""
+    T, hq, hkv, d = 1500, 16, 4, 128
+    rng = np.random.default_rng(8)
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+    k = rng.standard_normal((hkv, T, d), dtype=np.float32)
+    v = rng.standard_normal((hkv, T, d), dtype=np.float32)
+    want, _ = orc.attention_gen(q, k, v, hq, hkv, d, T)
+    if seq_major:
+        k, v = (np.ascontiguousarray(a.transpose(1, 0, 2)) for a in (k, v))
+    out = torch.zeros(hq, d, device="cuda")
+    be.attention_gen(_dev(q), _dev(k), _dev(v), out, hq, hkv, d, T)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(out.cpu().numpy(), want, atol=OUT_ATOL, rtol=OUT_RTOL)
+
+
 def test_argument_errors(be):
     from argus_engine_b200 import ArgusB200Error
 

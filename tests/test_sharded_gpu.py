@@ -42,6 +42,38 @@ def test_virtual_ranks_match_unsharded_oracle(T, N):
     be.close()
 
 
+def test_fused_exchange_phases_on_one_gpu():
+    """The fused exchange + merge kernel with all ranks' buffers on one GPU: the ranks push one after the other
+    (phase 1), then each rank merges (phase 2) - no kernel ever waits for a later launch. Two consecutive steps
+    use the two buffer sets; results equal the plain merge kernel."""
+    from argus_engine_b200 import B200Backend
+
+    be = B200Backend(0)
+    N, hq, d = 4, 16, 128
+    plen = hq * d + hq
+    bufs = [torch.zeros(2 * N * plen + 2 * N * hq, device="cuda") for _ in range(N)]   # one "rank" each
+    peer_parts = [b.data_ptr() for b in bufs]
+    peer_flags = [b.data_ptr() + 4 * 2 * N * plen for b in bufs]
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    for step in (1, 2):
+        parts = torch.randn(N, plen, device="cuda", generator=gen)
+        parts[1, hq * d:] = float("-inf")        # an empty shard
+        want = torch.zeros(hq, d, device="cuda")
+        be.lse_merge(parts, hq, d, want)
+        out = [torch.full((hq, d), float("nan"), device="cuda") for _ in range(N)]
+        for r in range(N):
+            be.exchange_merge(parts[r], peer_parts, peer_flags, r, hq, d, out[r], step=step, parts_parity_stride=N * plen,
+                              flags_parity_stride=N * hq, phases=1)
+        for r in range(N):
+            be.exchange_merge(parts[r], peer_parts, peer_flags, r, hq, d, out[r], step=step, parts_parity_stride=N * plen,
+                              flags_parity_stride=N * hq, phases=2)
+        torch.cuda.synchronize()
+        assert be.check_status() == 0
+        for r in range(N):
+            assert torch.allclose(out[r], want, atol=1e-6, rtol=1e-6)
+    be.close()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_process_nccl():
     s = socket.socket()
