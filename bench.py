@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl b200|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--others c1,c3,c4] [--no-sharded] [--impl b200|reference]
 
 One "step" is one pass of the hot path over one batch of synthetic input (one layer-step). The default
 workload is the batched GQA decode of the Llama-3-8B layer shape (B=16, Hq=32, Hkv=8, D=128, per-sequence
