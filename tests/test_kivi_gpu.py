@@ -180,11 +180,35 @@ def test_exactly_representable_q2_blocks(be):
     np.testing.assert_allclose(out.cpu().numpy(), want, atol=1e-3)
 
 
+@pytest.mark.parametrize("kernel", ["tc", "mma"])
+@pytest.mark.parametrize("g", [1, 4, 8])
+@pytest.mark.parametrize("T", [128 * 2 + 1, 128 * 7 + 100, 128 * 70 + 5, 128 * 301])
+def test_q4_d128_both_kernels(be, monkeypatch, kernel, g, T):
+    """Q4 at head_dim 128 has two kernels: the tcgen05 form (default; tiles of 4 groups, ragged last tile, several
+    splits at the longer lengths) and the mma.sync form (ARGUS_B200_KIVI_TC=0). Both against the oracle, with scores."""
+    monkeypatch.setenv("ARGUS_B200_KIVI_TC", "1" if kernel == "tc" else "0")
+    hkv, d = 2, 128
+    case = pack_with_oracle(wl.kivi_source(77 + T + g, [T], hkv * g, hkv, d, 128, 4))
+    want, want_p = _oracle_kivi(case, 0, scores=True)
+    out = torch.full((case.hq, d), float("nan"), device="cuda")
+    sc = torch.full((case.hq, T), -1.0)
+    rc = be.attention_gen_quant(_dev(case.q[0]), _dev(case.qk[0]), _dev(case.qv[0]), _dev(case.res_k[0]),
+                                _dev(case.res_v[0]), out, case.hq, hkv, d, case.q_tokens[0], case.res_tokens[0], 128,
+                                1.0 / np.sqrt(d), 4, scores_out=sc)
+    assert rc == 0
+    np.testing.assert_allclose(out.cpu().numpy(), want, atol=OUT_ATOL, rtol=OUT_RTOL)
+    np.testing.assert_allclose(sc.numpy(), want_p, atol=P_ATOL, rtol=P_RTOL)
+    assert be.check_status() == 0
+
+
+@pytest.mark.parametrize("kernel", ["tc", "mma"])
 @pytest.mark.parametrize("res_f16", [False, True])
-def test_batched_c3_shape_reduced(be, res_f16):
+def test_batched_c3_shape_reduced(be, monkeypatch, res_f16, kernel):
     """configs[2] scaled down (B=3, T in {4224, 2048+128, 777}): Q4, 1% of K channels x8, fused H2O
     group-mean vector [B,Hkv,T] and flat sums; F32 ring (engine) and F16 residual (benchmark wording)."""
     from argus_engine_b200 import DecodeExtras
+
+    monkeypatch.setenv("ARGUS_B200_KIVI_TC", "1" if kernel == "tc" else "0")
 
     lens = [4224, 2176, 777]
     case = pack_with_oracle(wl.kivi_source(2, lens, 32, 8, 128, 128, 4), res_f16=res_f16)
