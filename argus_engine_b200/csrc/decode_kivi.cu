@@ -79,6 +79,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
             : "r"(bar), "r"(parity)
             : "memory");
         if (ok) return true;
+        __nanosleep(32);   // a spinning warp takes issue slots from the warps that have work
     }
     return false;
 }

@@ -77,6 +77,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
                      : "r"(bar), "r"(parity)
                      : "memory");
         if (ok) return true;
+        __nanosleep(32);   // a spinning warp takes issue slots from the warps it is waiting for
     }
     return false;
 }
@@ -189,6 +190,13 @@ __device__ __forceinline__ uint32_t f2key(float x) {
 }
 __device__ __forceinline__ float key2f(uint32_t k) {
     return __uint_as_float(k ^ ((k >> 31) ? 0x80000000u : 0xFFFFFFFFu));
+}
+
+// One arrival per warp: 512 arrivals on one mbarrier word serialise (they are shared-memory atomics on one address),
+// so the lanes meet at __syncwarp (which orders their earlier shared-memory accesses) and lane 0 arrives for them.
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
 }
 
 // barrier ids: 0 = __syncthreads; 1 = the 128 softmax threads
@@ -339,18 +347,18 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
 #pragma unroll
         for (int s = 0; s < PK_STAGES; ++s) {
             mbar_init(bar0 + 8 * (B_PK_FULL + s), 1);
-            mbar_init(bar0 + 8 * (B_PK_EMPTY + s), N_DEQ);
+            mbar_init(bar0 + 8 * (B_PK_EMPTY + s), DEQ_WARPS);
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar0 + 8 * (B_KD_FULL + i), N_DEQ);
+            mbar_init(bar0 + 8 * (B_KD_FULL + i), DEQ_WARPS);
             mbar_init(bar0 + 8 * (B_KD_EMPTY + i), 1);
             mbar_init(bar0 + 8 * (B_S_FULL + i), 1);
-            mbar_init(bar0 + 8 * (B_P_FULL + i), 128);
+            mbar_init(bar0 + 8 * (B_P_FULL + i), 4);
         }
 #pragma unroll
         for (int i = 0; i < VD_BUFS; ++i) {
-            mbar_init(bar0 + 8 * (B_VD_FULL + i), N_DEQ);
+            mbar_init(bar0 + 8 * (B_VD_FULL + i), DEQ_WARPS);
             mbar_init(bar0 + 8 * (B_VD_EMPTY + i), 1);
         }
         *abort_flag = 0;
@@ -512,19 +520,19 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
             if (vgi < ng) dequant_block_q4(pk_v + v_src, vvec);
             else vvec[0] = vvec[1] = vvec[2] = vvec[3] = make_uint4(0u, 0u, 0u, 0u);
             // the codes are in registers (the values above depend on every load): the packed stage may be refilled
-            mbar_arrive(bar0 + 8 * (B_PK_EMPTY + s));
+            warp_arrive(bar0 + 8 * (B_PK_EMPTY + s), lane);
             if (T >= 2) (void)wait_or_abort(bar0 + 8 * (B_KD_EMPTY + bf), ((T >> 1) - 1) & 1, abort_flag);
             uint8_t* kd = smem + OFF_KD + bf * KD_B + k_dst;
 #pragma unroll
             for (int w = 0; w < 4; ++w) *reinterpret_cast<uint4*>(kd + w * 128) = kvec[w];
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(bar0 + 8 * (B_KD_FULL + bf));
+            warp_arrive(bar0 + 8 * (B_KD_FULL + bf), lane);
             if (T >= VD_BUFS) (void)wait_or_abort(bar0 + 8 * (B_VD_EMPTY + vb), ((T / VD_BUFS) - 1) & 1, abort_flag);
             uint8_t* vd = smem + OFF_VD + vb * KD_B + v_dst;
 #pragma unroll
             for (int w = 0; w < 4; ++w) *reinterpret_cast<uint4*>(vd + w * 128) = vvec[w];
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(bar0 + 8 * (B_VD_FULL + vb));
+            warp_arrive(bar0 + 8 * (B_VD_FULL + vb), lane);
         }
     } else {
         // ───────── softmax: thread = TMEM lane L = token position of S^T, channel position of O^T ─────────
@@ -610,7 +618,7 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
                                                        pack_half2(pr[4], pr[5]), pack_half2(pr[6], pr[7]));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
-            mbar_arrive(bar0 + 8 * (B_P_FULL + bf));
+            warp_arrive(bar0 + 8 * (B_P_FULL + bf), lane);
         }
         if (n_tiles > 0) {
             // the last P·V; a real bounded wait even after a give-up, so that nothing is in flight at dealloc
