@@ -104,6 +104,9 @@ def load_library() -> C.CDLL:
     lib.argus_b200_exchange_merge.argtypes = [vp, vp, vp, C.POINTER(vp), C.POINTER(vp), i32, i32, i32, vp, i64, i64, i32, i32,
                                               vp, vp, i32]
     lib.argus_b200_step_increment.argtypes = [vp, vp, vp]
+    lib.argus_b200_kv_scatter.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64]
+    lib.argus_b200_kv_compact.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, i64, i64, i32]
+    lib.argus_b200_kv_weighted_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, vp, vp, vp, vp, i32, i32]
     lib.argus_b200_attention_gen_static.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64]
     lib.argus_b200_static_scratch_bytes.restype = C.c_size_t
     lib.argus_b200_static_last_error.restype = C.c_char_p

@@ -237,6 +237,44 @@ class B200Backend:
     def step_increment(self, step_dev: torch.Tensor) -> None:
         self._check(self._lib.argus_b200_step_increment(self._h, self._stream(), step_dev.data_ptr()))
 
+    # ── KV write and eviction executors (HeadMajor [Hkv, cap, D] caches, F16 or F32) ──
+    @staticmethod
+    def _kv_layout(k_cache: torch.Tensor):
+        if k_cache.dim() != 3 or k_cache.stride(2) != 1 or k_cache.dtype not in (torch.float16, torch.float32):
+            raise ValueError("expected a [Hkv, cap, D] F16/F32 cache with contiguous rows")
+        return 1 if k_cache.dtype == torch.float16 else 0, k_cache.stride(0), k_cache.stride(1)
+
+    def kv_scatter(self, k_src: torch.Tensor, v_src: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   write_pos: int) -> None:
+        """kv_scatter_f32_to_f16[_batch] / f32_to_f32_batch: rows k_src/v_src [S, Hkv, D] F32 -> cache positions
+        write_pos .. write_pos+S-1."""
+        dt, hs, ps = self._kv_layout(k_cache)
+        S, hkv, d = k_src.shape
+        self._check(self._lib.argus_b200_kv_scatter(self._h, self._stream(), k_src.data_ptr(), v_src.data_ptr(),
+                                                    k_cache.data_ptr(), v_cache.data_ptr(), dt, hkv, d, k_cache.shape[1],
+                                                    hs, ps, write_pos, S))
+
+    def kv_compact(self, k_cache: torch.Tensor, v_cache: torch.Tensor, keep: torch.Tensor, write_start: int,
+                   head: int = -1) -> None:
+        """KVCache::compact_keep_positions (head = -1) / _for_head: position write_start+i <- position keep[i], in place.
+        keep: ascending int32 device tensor."""
+        dt, hs, ps = self._kv_layout(k_cache)
+        if keep.dtype != torch.int32 or not keep.is_cuda:
+            raise ValueError("keep must be an int32 device tensor")
+        self._check(self._lib.argus_b200_kv_compact(self._h, self._stream(), k_cache.data_ptr(), v_cache.data_ptr(), dt,
+                                                    k_cache.shape[0], k_cache.shape[2], hs, ps, keep.data_ptr(),
+                                                    keep.numel(), write_start, head))
+
+    def kv_weighted_merge(self, k_cache: torch.Tensor, v_cache: torch.Tensor, into_pos: torch.Tensor,
+                          into_weight: torch.Tensor, from_start: torch.Tensor, from_pos: torch.Tensor,
+                          from_weight: torch.Tensor, axis: int = 0) -> None:
+        """apply_weighted_merges (F32/F16 arms): CSR lists on the device, axis 0 both / 1 K only / 2 V only."""
+        dt, hs, ps = self._kv_layout(k_cache)
+        self._check(self._lib.argus_b200_kv_weighted_merge(
+            self._h, self._stream(), k_cache.data_ptr(), v_cache.data_ptr(), dt, k_cache.shape[0], k_cache.shape[2], hs,
+            ps, into_pos.data_ptr(), into_weight.data_ptr(), from_start.data_ptr(), from_pos.data_ptr(),
+            from_weight.data_ptr(), into_pos.numel(), axis))
+
     def check_status(self) -> int:
         """Synchronises the current stream; non-zero if a kernel's bounded wait ran out since the last check."""
         return int(self._lib.argus_b200_check_status(self._h, self._stream()))

@@ -60,6 +60,17 @@ cudaError_t launch_step_increment(int* step, cudaStream_t st);
 // kv_cast.cu
 cudaError_t launch_kv_f32_to_f16(const float* src, void* dst, int hkv, long long T, int d, long long head_stride,
                                  long long pos_stride, cudaStream_t st);
+// kv_ops.cu
+cudaError_t launch_kv_scatter(const float* k_src, const float* v_src, void* k_dst, void* v_dst, bool dst_f16, int hkv,
+                              int d, long long head_stride, long long pos_stride, long long write_pos, long long seq_len,
+                              cudaStream_t st);
+cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, long long i0, long long n_rows,
+                                   long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
+                                   long long pos_stride_bytes, int to_scratch, int* status, cudaStream_t st);
+cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d, long long head_stride,
+                                     long long pos_stride, const int* into_pos, const float* into_w, const int* from_start,
+                                     const int* from_pos, const float* from_w, int n_merges, int do_k, int do_v,
+                                     cudaStream_t st);
 // lse_merge.cu
 cudaError_t launch_lse_merge(const float* parts, int n_parts, long long part_stride, int hq, int d, float* out,
                              float* lse_out, cudaStream_t st);

@@ -1,0 +1,109 @@
+// C-ABI entry points of the KV write and eviction executors (kv_ops.cu).
+#include <stdint.h>
+#include <string.h>
+
+#include <algorithm>
+
+#include "context.h"
+
+using namespace argus;
+
+namespace {
+
+int elt_bytes(int dtype) { return dtype == ARGUS_B200_KV_F16 ? 2 : dtype == ARGUS_B200_KV_F32 ? 4 : -1; }
+
+// Rows are moved as 16-byte vectors: base pointers, the row pitch and the head pitch must allow that.
+bool rows_are_vector_aligned(const void* k, const void* v, int64_t head_stride, int64_t pos_stride, int d, int eb) {
+    return ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 && (head_stride * eb) % 16 == 0 &&
+           (pos_stride * eb) % 16 == 0 && ((int64_t)d * eb) % 16 == 0;
+}
+
+}  // namespace
+
+extern "C" int argus_b200_kv_scatter(argus_b200_ctx* c, void* stream, const float* k_src, const float* v_src, void* k_dst,
+                                     void* v_dst, int dst_dtype, int num_heads_kv, int head_dim, int64_t capacity,
+                                     int64_t head_stride, int64_t pos_stride, int64_t write_pos, int64_t seq_len) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    const int eb = elt_bytes(dst_dtype);
+    if (!k_src || !v_src || !k_dst || !v_dst || eb < 0 || num_heads_kv <= 0 || head_dim <= 0 || seq_len < 0 ||
+        write_pos < 0 || write_pos + seq_len > capacity) {
+        ctx->set_error("kv_scatter: null pointer, bad dtype, or rows [%lld, %lld) outside capacity %lld",
+                       (long long)write_pos, (long long)(write_pos + seq_len), (long long)capacity);
+        return ARGUS_B200_E_INVALID;
+    }
+    if (head_dim % 4 != 0 || ((reinterpret_cast<uintptr_t>(k_src) | reinterpret_cast<uintptr_t>(v_src)) & 15) ||
+        ((reinterpret_cast<uintptr_t>(k_dst) | reinterpret_cast<uintptr_t>(v_dst)) & 15) || (head_stride * eb) % 16 ||
+        (pos_stride * eb) % 16) {
+        ctx->set_error("kv_scatter: head_dim %% 4, 16-byte aligned pointers and row pitches are required");
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    cudaError_t e = launch_kv_scatter(k_src, v_src, k_dst, v_dst, dst_dtype == ARGUS_B200_KV_F16, num_heads_kv, head_dim,
+                                      head_stride, pos_stride, write_pos, seq_len, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_scatter launch");
+    ctx->launches += seq_len > 0 ? 1 : 0;
+    return ARGUS_B200_OK;
+}
+
+extern "C" int argus_b200_kv_compact(argus_b200_ctx* c, void* stream, void* k, void* v, int kv_dtype, int num_heads_kv,
+                                     int head_dim, int64_t head_stride, int64_t pos_stride, const int32_t* keep_dev,
+                                     int64_t n_keep, int64_t write_start, int head) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    const int eb = elt_bytes(kv_dtype);
+    if (!k || !v || eb < 0 || num_heads_kv <= 0 || head_dim <= 0 || n_keep < 0 || write_start < 0 || head < -1 ||
+        head >= num_heads_kv || (n_keep > 0 && !keep_dev)) {
+        ctx->set_error("kv_compact: null pointer, bad dtype or head index %d (of %d)", head, num_heads_kv);
+        return ARGUS_B200_E_INVALID;
+    }
+    if (n_keep == 0) return ARGUS_B200_OK;   // compact_keep_positions returns early on an empty list
+    if (!rows_are_vector_aligned(k, v, head_stride, pos_stride, head_dim, eb)) {
+        ctx->set_error("kv_compact: rows must be 16-byte aligned (pointers, head_dim, row and head pitch)");
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    const int head0 = head < 0 ? 0 : head, n_heads = head < 0 ? num_heads_kv : 1;
+    const int64_t row_bytes = (int64_t)head_dim * eb;
+    const int64_t rows_per_pass = (int64_t)(ctx->ws_bytes / (size_t)(row_bytes * n_heads));
+    if (rows_per_pass < 1) {
+        ctx->set_error("kv_compact: scratch of %zu bytes does not hold one row of every head", ctx->ws_bytes);
+        return ARGUS_B200_E_WORKSPACE;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int64_t i0 = 0; i0 < n_keep; i0 += rows_per_pass) {
+        const int64_t n = std::min(rows_per_pass, n_keep - i0);
+        for (int which = 0; which < 2; ++which) {
+            void* cache = which == 0 ? k : v;
+            for (int to_scratch = 1; to_scratch >= 0; --to_scratch) {
+                cudaError_t e = launch_kv_compact_pass(cache, ctx->ws, keep_dev, i0, n, write_start, head0, n_heads,
+                                                       (int)row_bytes, head_stride * eb, pos_stride * eb, to_scratch,
+                                                       ctx->status, st);
+                if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_compact launch");
+                ctx->launches += 1;
+            }
+        }
+    }
+    return ARGUS_B200_OK;
+}
+
+extern "C" int argus_b200_kv_weighted_merge(argus_b200_ctx* c, void* stream, void* k, void* v, int kv_dtype,
+                                            int num_heads_kv, int head_dim, int64_t head_stride, int64_t pos_stride,
+                                            const int32_t* into_pos, const float* into_weight, const int32_t* from_start,
+                                            const int32_t* from_pos, const float* from_weight, int n_merges, int axis) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    const int eb = elt_bytes(kv_dtype);
+    if (!k || !v || eb < 0 || num_heads_kv <= 0 || num_heads_kv > 65535 || head_dim <= 0 || n_merges < 0 || axis < 0 ||
+        axis > 2 || (n_merges > 0 && (!into_pos || !into_weight || !from_start || !from_pos || !from_weight))) {
+        ctx->set_error("kv_weighted_merge: null pointer, bad dtype or axis %d", axis);
+        return ARGUS_B200_E_INVALID;
+    }
+    cudaError_t e = launch_kv_weighted_merge(k, v, kv_dtype == ARGUS_B200_KV_F16, num_heads_kv, head_dim, head_stride,
+                                             pos_stride, into_pos, into_weight, from_start, from_pos, from_weight,
+                                             n_merges, axis != 2, axis != 1, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_weighted_merge launch");
+    ctx->launches += n_merges > 0 ? 1 : 0;
+    return ARGUS_B200_OK;
+}

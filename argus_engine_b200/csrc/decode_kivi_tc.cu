@@ -33,6 +33,7 @@ constexpr int D = 128, BB = 20, TILE_TOK = 128, GROUPS = 4;
 constexpr int GRP_B = D * BB;                    // 2560: packed K (== V) bytes of one group
 constexpr int PK_STAGE_B = 2 * GROUPS * GRP_B;   // 20480: packed K + V of one tile
 constexpr int PK_STAGES = 2;                    // a stage is released as soon as its codes are in registers
+constexpr int P_BUFS = 3;                       // p(T) is held until P·V(T) has completed
 constexpr int VD_BUFS = 3;                      // V_d(T) is held until P·V(T), two handoffs after K_d(T) is used
 constexpr int KD_B = TILE_TOK * D * 2;           // 32 KB dequantised K (or V) tile
 constexpr int Q_B = 16 * 2 * 128;                // q tile: 16 k-blocks x 2 n-blocks (value, residual) x 128 B
@@ -42,9 +43,9 @@ constexpr int OFF_KD = OFF_PK + PK_STAGES * PK_STAGE_B;
 constexpr int OFF_VD = OFF_KD + 2 * KD_B;
 constexpr int OFF_Q = OFF_VD + VD_BUFS * KD_B;
 constexpr int OFF_P = OFF_Q + Q_B;
-constexpr int OFF_RED = OFF_P + 2 * P_B;         // float [3][4 warps][8 heads] softmax exchange
+constexpr int OFF_RED = OFF_P + P_BUFS * P_B;         // float [3][4 warps][8 heads] softmax exchange
 constexpr int OFF_BAR = OFF_RED + 3 * 32 * 4;   // two tile-max buffers + one for the final sums
-constexpr int N_BAR = 2 * PK_STAGES + 4 + 2 * VD_BUFS + 4;
+constexpr int N_BAR = 2 * PK_STAGES + 4 + 2 * VD_BUFS + 2 + P_BUFS + 2;
 constexpr int SMEM_B = OFF_BAR + N_BAR * 8 + 64 + 128;
 constexpr int DEQ_WARPS = 16;
 constexpr int FIRST_DEQ_WARP = 8;
@@ -56,7 +57,7 @@ constexpr uint32_t O_COL = 32;
 // mbarrier indices
 constexpr int B_PK_FULL = 0, B_PK_EMPTY = PK_STAGES, B_KD_FULL = 2 * PK_STAGES, B_KD_EMPTY = B_KD_FULL + 2,
               B_VD_FULL = B_KD_FULL + 4, B_VD_EMPTY = B_VD_FULL + VD_BUFS, B_S_FULL = B_VD_EMPTY + VD_BUFS,
-              B_P_FULL = B_S_FULL + 2;
+              B_P_FULL = B_S_FULL + 2, B_DONE = B_P_FULL + P_BUFS;   // B_DONE + {0, 1}: all MMAs of an issuer have completed
 constexpr float LAZY = 8.0f;
 
 
@@ -183,6 +184,11 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     return false;
 }
 
+// The same for a whole warp, with one answer for all lanes (the lanes meet again at __syncwarp later on).
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag));
+}
+
 // float <-> unsigned key whose unsigned order is the float order (for redux.sync.max)
 __device__ __forceinline__ uint32_t f2key(float x) {
     const uint32_t u = __float_as_uint(x);
@@ -201,6 +207,15 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
 
 // barrier ids: 0 = __syncthreads; 1 = the 128 softmax threads
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// the same barrier, returning the OR of `flag` over the 128 threads (one answer for all of them)
+__device__ __forceinline__ bool softmax_bar_or(bool flag) {
+    uint32_t out;
+    asm volatile("{ .reg .pred p, q; setp.ne.b32 q, %1, 0; bar.red.or.pred p, 1, 128, q; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(out)
+                 : "r"((uint32_t)flag)
+                 : "memory");
+    return out != 0;
+}
 
 
 // Residual-window split (all warps): plain F32 FMA. Warp w owns heads 4*(w&1).. and the tokens r0 + (w>>1) + (N_WARPS/2)*i,
@@ -354,13 +369,16 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
             mbar_init(bar0 + 8 * (B_KD_FULL + i), DEQ_WARPS);
             mbar_init(bar0 + 8 * (B_KD_EMPTY + i), 1);
             mbar_init(bar0 + 8 * (B_S_FULL + i), 1);
-            mbar_init(bar0 + 8 * (B_P_FULL + i), 4);
         }
+#pragma unroll
+        for (int i = 0; i < P_BUFS; ++i) mbar_init(bar0 + 8 * (B_P_FULL + i), 4);
 #pragma unroll
         for (int i = 0; i < VD_BUFS; ++i) {
             mbar_init(bar0 + 8 * (B_VD_FULL + i), DEQ_WARPS);
             mbar_init(bar0 + 8 * (B_VD_EMPTY + i), 1);
         }
+        mbar_init(bar0 + 8 * B_DONE, 1);
+        mbar_init(bar0 + 8 * (B_DONE + 1), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -382,7 +400,7 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
         *reinterpret_cast<__half*>(at + 128) = lo;
     }
     // p tiles: n-block 0 is rewritten every tile, n-block 1 stays zero (the MMA needs N = 16)
-    for (int e = threadIdx.x; e < 2 * P_B / 16; e += THREADS) reinterpret_cast<uint4*>(smem + OFF_P)[e] = make_uint4(0u, 0u, 0u, 0u);
+    for (int e = threadIdx.x; e < P_BUFS * P_B / 16; e += THREADS) reinterpret_cast<uint4*>(smem + OFF_P)[e] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
     __syncthreads();
@@ -403,9 +421,10 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
             // Groups of one flush are contiguous for K and for V, so a tile is fetched in runs (one run of 4 groups
             // when a flush holds a multiple of 4 groups); the position advances without divisions.
             int f = g0 / gpf, gif = g0 - f * gpf;
-            for (int T = 0; T < n_tiles; ++T) {
+            int T = 0;   // tiles issued so far
+            for (; T < n_tiles; ++T) {
                 const int s = T % PK_STAGES;
-                if (T >= PK_STAGES) (void)wait_or_abort(bar0 + 8 * (B_PK_EMPTY + s), ((T / PK_STAGES) - 1) & 1, abort_flag);
+                if (T >= PK_STAGES && !wait_or_abort(bar0 + 8 * (B_PK_EMPTY + s), ((T / PK_STAGES) - 1) & 1, abort_flag)) break;
                 const int ng = min(GROUPS, n_groups - GROUPS * T);
                 const uint32_t full = bar0 + 8 * (B_PK_FULL + s);
                 const uint32_t dst = sbase + OFF_PK + s * PK_STAGE_B;
@@ -425,9 +444,9 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
                     }
                 }
             }
-            if (*abort_flag)   // let the copies still in flight land before shared memory is reused
-                for (int T = max(0, n_tiles - PK_STAGES); T < n_tiles; ++T)
-                    (void)mbar_wait(bar0 + 8 * (B_PK_FULL + T % PK_STAGES), (T / PK_STAGES) & 1);
+            if (*abort_flag)   // gave up: let the copies still in flight land before shared memory is reused
+                for (int Ti = max(0, T - PK_STAGES); Ti < T; ++Ti)
+                    (void)mbar_wait(bar0 + 8 * (B_PK_FULL + Ti % PK_STAGES), (Ti / PK_STAGES) & 1);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -446,9 +465,9 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
             }
             for (int T = 0; T < n_tiles; ++T) {
                 const uint32_t bf = T & 1;
-                (void)wait_or_abort(bar0 + 8 * (B_KD_FULL + bf), (T >> 1) & 1, abort_flag);
+                if (!wait_or_abort(bar0 + 8 * (B_KD_FULL + bf), (T >> 1) & 1, abort_flag)) break;
                 // softmax(T-2) has read this S buffer once p(T-2) is complete
-                if (T >= 2) (void)wait_or_abort(bar0 + 8 * (B_P_FULL + bf), ((T >> 1) - 1) & 1, abort_flag);
+                if (T >= 2 && !wait_or_abort(bar0 + 8 * (B_P_FULL + (T - 2) % P_BUFS), ((T - 2) / P_BUFS) & 1, abort_flag)) break;
                 tc_fence_after();
                 if (bf == 0) {
 #pragma unroll
@@ -460,6 +479,9 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
                 tc_commit(bar0 + 8 * (B_S_FULL + bf));
                 tc_commit(bar0 + 8 * (B_KD_EMPTY + bf));
             }
+            // nothing of this thread is in flight when tensor memory is released, whatever happened above
+            tc_commit(bar0 + 8 * B_DONE);
+            if (!mbar_wait(bar0 + 8 * B_DONE, 0)) *abort_flag = 1;
         }
         __syncwarp();
     } else if (warp == 2) {
@@ -467,29 +489,23 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
         if (lane == 0) {
             constexpr uint32_t idesc_o = idesc_f16(1, 1, 128, 16);   // A = V_d MN-major, B = p MN-major
             constexpr uint32_t hi = desc_hi(128);
-            uint64_t bd[2][8];
-#pragma unroll
-            for (uint32_t t = 0; t < 8; ++t) {
-                bd[0][t] = desc64(desc_lo(sbase + OFF_P + t * 512, 256), hi);
-                bd[1][t] = desc64(desc_lo(sbase + OFF_P + P_B + t * 512, 256), hi);
-            }
             for (int T = 0; T < n_tiles; ++T) {
-                const uint32_t bf = T & 1, vb = T % VD_BUFS;
-                uint64_t ad[8];   // built while there is nothing to issue
+                const uint32_t vb = T % VD_BUFS, pb = T % P_BUFS;
+                uint64_t ad[8], bd[8];   // built while there is nothing to issue
 #pragma unroll
-                for (uint32_t t = 0; t < 8; ++t) ad[t] = desc64(desc_lo(sbase + OFF_VD + vb * KD_B + t * 4096, 2048), hi);
-                (void)wait_or_abort(bar0 + 8 * (B_VD_FULL + vb), (T / VD_BUFS) & 1, abort_flag);
-                (void)wait_or_abort(bar0 + 8 * (B_P_FULL + bf), (T >> 1) & 1, abort_flag);
-                tc_fence_after();
-                if (bf == 0) {
-#pragma unroll
-                    for (uint32_t t = 0; t < 8; ++t) tc_mma64(tmem + O_COL, ad[t], bd[0][t], idesc_o, (T > 0 || t > 0) ? 1u : 0u);
-                } else {
-#pragma unroll
-                    for (uint32_t t = 0; t < 8; ++t) tc_mma64(tmem + O_COL, ad[t], bd[1][t], idesc_o, 1u);
+                for (uint32_t t = 0; t < 8; ++t) {
+                    ad[t] = desc64(desc_lo(sbase + OFF_VD + vb * KD_B + t * 4096, 2048), hi);
+                    bd[t] = desc64(desc_lo(sbase + OFF_P + pb * P_B + t * 512, 256), hi);
                 }
+                if (!wait_or_abort(bar0 + 8 * (B_VD_FULL + vb), (T / VD_BUFS) & 1, abort_flag)) break;
+                if (!wait_or_abort(bar0 + 8 * (B_P_FULL + pb), (T / P_BUFS) & 1, abort_flag)) break;
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t t = 0; t < 8; ++t) tc_mma64(tmem + O_COL, ad[t], bd[t], idesc_o, (T > 0 || t > 0) ? 1u : 0u);
                 tc_commit(bar0 + 8 * (B_VD_EMPTY + vb));
             }
+            tc_commit(bar0 + 8 * (B_DONE + 1));
+            if (!mbar_wait(bar0 + 8 * (B_DONE + 1), 0)) *abort_flag = 1;
         }
         __syncwarp();
     } else if (warp == 3) {
@@ -511,7 +527,7 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
         for (int T = 0; T < n_tiles; ++T) {
             const int s = T % PK_STAGES, bf = T & 1, vb = T % VD_BUFS;
             const int ng = min(GROUPS, n_groups - GROUPS * T);
-            (void)wait_or_abort(bar0 + 8 * (B_PK_FULL + s), (T / PK_STAGES) & 1, abort_flag);
+            if (!warp_wait(bar0 + 8 * (B_PK_FULL + s), (T / PK_STAGES) & 1, abort_flag)) break;
             const uint8_t* pk_k = smem + OFF_PK + s * PK_STAGE_B;
             const uint8_t* pk_v = pk_k + GROUPS * GRP_B;
             uint4 kvec[4], vvec[4];
@@ -521,13 +537,13 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
             else vvec[0] = vvec[1] = vvec[2] = vvec[3] = make_uint4(0u, 0u, 0u, 0u);
             // the codes are in registers (the values above depend on every load): the packed stage may be refilled
             warp_arrive(bar0 + 8 * (B_PK_EMPTY + s), lane);
-            if (T >= 2) (void)wait_or_abort(bar0 + 8 * (B_KD_EMPTY + bf), ((T >> 1) - 1) & 1, abort_flag);
+            if (T >= 2 && !warp_wait(bar0 + 8 * (B_KD_EMPTY + bf), ((T >> 1) - 1) & 1, abort_flag)) break;
             uint8_t* kd = smem + OFF_KD + bf * KD_B + k_dst;
 #pragma unroll
             for (int w = 0; w < 4; ++w) *reinterpret_cast<uint4*>(kd + w * 128) = kvec[w];
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             warp_arrive(bar0 + 8 * (B_KD_FULL + bf), lane);
-            if (T >= VD_BUFS) (void)wait_or_abort(bar0 + 8 * (B_VD_EMPTY + vb), ((T / VD_BUFS) - 1) & 1, abort_flag);
+            if (T >= VD_BUFS && !warp_wait(bar0 + 8 * (B_VD_EMPTY + vb), ((T / VD_BUFS) - 1) & 1, abort_flag)) break;
             uint8_t* vd = smem + OFF_VD + vb * KD_B + v_dst;
 #pragma unroll
             for (int w = 0; w < 4; ++w) *reinterpret_cast<uint4*>(vd + w * 128) = vvec[w];
@@ -540,6 +556,7 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
         const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
         const int tok_in_tile = (L & ~7) + perm8(L & 7);
         int* red = reinterpret_cast<int*>(smem + OFF_RED);
+        bool gave_up = false;
         // The reference point m_ref of exp2(s - m_ref) only has to be near the running maximum (it is raised when a
         // tile exceeds it by more than LAZY), so the tile maximum is taken on the bits of s + MAX_OFS as signed
         // integers: non-negative floats order like their bits, one redux.sync per head. Logits (log2 units) below
@@ -548,7 +565,7 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
         for (int T = 0; T < n_tiles; ++T) {
             const int bf = T & 1;
             const int ng = min(GROUPS, n_groups - GROUPS * T);
-            (void)wait_or_abort(bar0 + 8 * (B_S_FULL + bf), (T >> 1) & 1, abort_flag);
+            const bool s_ok = wait_or_abort(bar0 + 8 * (B_S_FULL + bf), (T >> 1) & 1, abort_flag);
             tc_fence_after();
             uint32_t r[16];
             tmem_ld16(tmem + lane_off + 16 * bf, r);
@@ -563,7 +580,11 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
                 const int k = __reduce_max_sync(0xffffffffu, __float_as_int(fmaxf(s[h], -MAX_OFS) + MAX_OFS));
                 if (lane == 0) rd[(warp & 3) * 8 + h] = k;
             }
-            softmax_bar();
+            // the tile-maximum exchange doubles as the give-up vote: the 128 threads leave the loop together
+            if (softmax_bar_or(!s_ok || *abort_flag != 0)) {
+                gave_up = true;
+                break;
+            }
             if (p.logits != nullptr && valid) {
                 const int64_t tok = (int64_t)(g0 + GROUPS * T) * 32 + tok_in_tile;
 #pragma unroll
@@ -612,17 +633,20 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
                 pr[h] = fast_exp2(s[h] - ((m_ref[h] == -INFINITY) ? 0.f : m_ref[h]));
                 l_run[h] += pr[h];
             }
+            // P·V(T-3) read this p buffer: it has to be complete before the buffer is rewritten. (It also keeps
+            // p_full from running two phases ahead of the P·V issuer, which waits on its parity.)
+            if (T >= P_BUFS)
+                (void)wait_or_abort(bar0 + 8 * (B_VD_EMPTY + (T - P_BUFS) % VD_BUFS), ((T - P_BUFS) / VD_BUFS) & 1, abort_flag);
             // p as F16 (<= 2^LAZY, relative error 2^-11): one 16-byte row of 8 heads
-            uint8_t* pt = smem + OFF_P + bf * P_B + (L >> 3) * 256 + (L & 7) * 16;
+            uint8_t* pt = smem + OFF_P + (T % P_BUFS) * P_B + (L >> 3) * 256 + (L & 7) * 16;
             *reinterpret_cast<uint4*>(pt) = make_uint4(pack_half2(pr[0], pr[1]), pack_half2(pr[2], pr[3]),
                                                        pack_half2(pr[4], pr[5]), pack_half2(pr[6], pr[7]));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
-            warp_arrive(bar0 + 8 * (B_P_FULL + bf), lane);
+            warp_arrive(bar0 + 8 * (B_P_FULL + T % P_BUFS), lane);
         }
-        if (n_tiles > 0) {
-            // the last P·V; a real bounded wait even after a give-up, so that nothing is in flight at dealloc
-            const int Tl = n_tiles - 1;
+        if (n_tiles > 0 && !gave_up) {
+            const int Tl = n_tiles - 1;   // the last P·V
             if (!mbar_wait(bar0 + 8 * (B_VD_EMPTY + Tl % VD_BUFS), (Tl / VD_BUFS) & 1)) *abort_flag = 1;
             tc_fence_after();
             uint32_t o[16];

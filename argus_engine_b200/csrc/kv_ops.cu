@@ -1,0 +1,162 @@
+// KV-cache write and eviction executors on a device-resident F16/F32 cache: the callers either side of the
+// attention kernels. All three are byte movers bounded by HBM (16-byte vector accesses, one row = head_dim
+// elements), and all are bit-exact with the reference's arithmetic.
+//
+//   kv_scatter        kv_scatter_f32_to_f16 / _batch / f32_to_f32_batch (engine/src/backend/cuda_pc/kernels.cu:305-360):
+//                     new K/V rows [seq][Hkv][D] F32 -> cache rows write_pos.. (F16: round to nearest even)
+//   kv_compact        KVCache::compact_keep_positions[_for_head] (engine/src/kv/kv_cache.rs:1266-1352):
+//                     row write_start+i <- row keep[i], keep ascending
+//   kv_weighted_merge apply_weighted_merges, F32/F16 arms (engine/src/kv/standard_format.rs:754-893):
+//                     into <- into_w*into + sum_j w_j*from_j, every product and sum rounded on its own, list order
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace argus {
+
+// ───────── KV write ─────────
+template <bool DST_F16>
+__global__ void __launch_bounds__(256) kv_scatter_kernel(const float* __restrict__ k_src, const float* __restrict__ v_src,
+                                                         void* __restrict__ k_dst, void* __restrict__ v_dst, int hkv, int d,
+                                                         long long head_stride, long long pos_stride, long long write_pos,
+                                                         long long seq_len) {
+    const int vec_per_row = d / 4;   // four channels per thread
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = seq_len * hkv * vec_per_row;
+    if (idx >= total) return;
+    const int c = (int)(idx % vec_per_row) * 4;
+    const long long row = idx / vec_per_row;   // = s * hkv + h: the source is [seq][Hkv][D]
+    const long long h = row % hkv, s = row / hkv;
+    const long long so = row * d + c;
+    const long long dof = h * head_stride + (write_pos + s) * pos_stride + c;
+    const float4 kx = *reinterpret_cast<const float4*>(k_src + so);
+    const float4 vx = *reinterpret_cast<const float4*>(v_src + so);
+    if constexpr (DST_F16) {
+        __half2 ka = __floats2half2_rn(kx.x, kx.y), kb = __floats2half2_rn(kx.z, kx.w);
+        __half2 va = __floats2half2_rn(vx.x, vx.y), vb = __floats2half2_rn(vx.z, vx.w);
+        *reinterpret_cast<uint2*>(static_cast<__half*>(k_dst) + dof) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&ka), *reinterpret_cast<uint32_t*>(&kb));
+        *reinterpret_cast<uint2*>(static_cast<__half*>(v_dst) + dof) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&va), *reinterpret_cast<uint32_t*>(&vb));
+    } else {
+        *reinterpret_cast<float4*>(static_cast<float*>(k_dst) + dof) = kx;
+        *reinterpret_cast<float4*>(static_cast<float*>(v_dst) + dof) = vx;
+    }
+}
+
+cudaError_t launch_kv_scatter(const float* k_src, const float* v_src, void* k_dst, void* v_dst, bool dst_f16, int hkv,
+                              int d, long long head_stride, long long pos_stride, long long write_pos, long long seq_len,
+                              cudaStream_t st) {
+    const long long total = seq_len * hkv * (d / 4);
+    if (total <= 0) return cudaSuccess;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    if (dst_f16)
+        kv_scatter_kernel<true><<<grid, 256, 0, st>>>(k_src, v_src, k_dst, v_dst, hkv, d, head_stride, pos_stride, write_pos, seq_len);
+    else
+        kv_scatter_kernel<false><<<grid, 256, 0, st>>>(k_src, v_src, k_dst, v_dst, hkv, d, head_stride, pos_stride, write_pos, seq_len);
+    return cudaGetLastError();
+}
+
+// ───────── keep-set compaction ─────────
+// The move is in place and to the left (keep[i] >= write_start + i). Rows i of a chunk [i0, i1) are first gathered
+// into scratch and then written, chunk after chunk in ascending order: a later chunk's sources lie to the right of
+// everything an earlier chunk wrote, and inside a chunk all reads precede all writes (two launches). Rows that
+// already sit at their place are skipped by both. A keep list that is not ascending or that would move a row to
+// the right sets *status = 2 and moves nothing for the offending entry.
+// to_scratch = 1: cache -> scratch; 0: scratch -> cache. Scratch layout [heads][rows of the chunk][row_vecs] uint4.
+__global__ void __launch_bounds__(256) kv_compact_kernel(uint4* __restrict__ cache, uint4* __restrict__ scratch,
+                                                         const int* __restrict__ keep, long long i0, long long n_rows,
+                                                         long long write_start, int head0, int n_heads, int row_vecs,
+                                                         long long head_stride_v, long long pos_stride_v, int to_scratch,
+                                                         int* status) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = n_rows * n_heads * row_vecs;
+    if (idx >= total) return;
+    const int v = (int)(idx % row_vecs);
+    const long long r = (idx / row_vecs) % n_rows;
+    const int hh = (int)(idx / ((long long)row_vecs * n_rows));
+    const long long i = i0 + r;
+    const long long src = keep[i], dst = write_start + i;
+    if (src == dst) return;
+    if (src < dst || (i > 0 && keep[i - 1] >= src)) {
+        if (status != nullptr && v == 0 && hh == 0) atomicExch(status, 2);
+        return;
+    }
+    const long long base = (long long)(head0 + hh) * head_stride_v;
+    uint4* s = scratch + ((long long)hh * n_rows + r) * row_vecs + v;
+    if (to_scratch) *s = cache[base + src * pos_stride_v + v];
+    else cache[base + dst * pos_stride_v + v] = *s;
+}
+
+cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, long long i0, long long n_rows,
+                                   long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
+                                   long long pos_stride_bytes, int to_scratch, int* status, cudaStream_t st) {
+    const int row_vecs = row_bytes / 16;
+    const long long total = n_rows * n_heads * row_vecs;
+    if (total <= 0) return cudaSuccess;
+    kv_compact_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+        static_cast<uint4*>(cache), static_cast<uint4*>(scratch), keep, i0, n_rows, write_start, head0, n_heads, row_vecs,
+        head_stride_bytes / 16, pos_stride_bytes / 16, to_scratch, status);
+    return cudaGetLastError();
+}
+
+// ───────── weighted merge (D2O) ─────────
+// Merges are disjoint (a `from` row is evicted, an `into` row is retained, neither occurs twice), so they run in
+// parallel: CTA = (merge, kv head), thread = channel. from_start is a CSR offset array [n_merges + 1].
+template <typename T>
+__device__ __forceinline__ float load_f32(const T* p);
+template <>
+__device__ __forceinline__ float load_f32<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load_f32<__half>(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ void store_f32(float* p, float x) { *p = x; }
+__device__ __forceinline__ void store_f32(__half* p, float x) { *p = __float2half_rn(x); }
+
+template <typename T>
+__global__ void __launch_bounds__(128) kv_weighted_merge_kernel(T* __restrict__ k, T* __restrict__ v, int d,
+                                                                long long head_stride, long long pos_stride,
+                                                                const int* __restrict__ into_pos,
+                                                                const float* __restrict__ into_w,
+                                                                const int* __restrict__ from_start,
+                                                                const int* __restrict__ from_pos,
+                                                                const float* __restrict__ from_w, int do_k, int do_v) {
+    const int m = blockIdx.x, h = blockIdx.y;
+    const int f0 = from_start[m], f1 = from_start[m + 1];
+    if (f1 <= f0) return;   // an empty `from` list leaves the row untouched
+    const long long base = (long long)h * head_stride;
+    const long long io = base + (long long)into_pos[m] * pos_stride;
+    const float iw = into_w[m];
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        if (do_k) {
+            float acc = __fmul_rn(iw, load_f32(k + io + c));
+            for (int j = f0; j < f1; ++j)
+                acc = __fadd_rn(acc, __fmul_rn(from_w[j], load_f32(k + base + (long long)from_pos[j] * pos_stride + c)));
+            store_f32(k + io + c, acc);
+        }
+        if (do_v) {
+            float acc = __fmul_rn(iw, load_f32(v + io + c));
+            for (int j = f0; j < f1; ++j)
+                acc = __fadd_rn(acc, __fmul_rn(from_w[j], load_f32(v + base + (long long)from_pos[j] * pos_stride + c)));
+            store_f32(v + io + c, acc);
+        }
+    }
+}
+
+cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d, long long head_stride,
+                                     long long pos_stride, const int* into_pos, const float* into_w, const int* from_start,
+                                     const int* from_pos, const float* from_w, int n_merges, int do_k, int do_v,
+                                     cudaStream_t st) {
+    if (n_merges <= 0) return cudaSuccess;
+    const dim3 grid((unsigned)n_merges, (unsigned)hkv);
+    if (f16)
+        kv_weighted_merge_kernel<__half><<<grid, 128, 0, st>>>(static_cast<__half*>(k), static_cast<__half*>(v), d,
+                                                              head_stride, pos_stride, into_pos, into_w, from_start,
+                                                              from_pos, from_w, do_k, do_v);
+    else
+        kv_weighted_merge_kernel<float><<<grid, 128, 0, st>>>(static_cast<float*>(k), static_cast<float*>(v), d,
+                                                             head_stride, pos_stride, into_pos, into_w, from_start,
+                                                             from_pos, from_w, do_k, do_v);
+    return cudaGetLastError();
+}
+
+}  // namespace argus

@@ -277,6 +277,43 @@ ARGUS_B200_API int argus_b200_step_increment(argus_b200_ctx* ctx, void* stream, 
  * waits ran out (0 = clean). The word is cleared by the call. */
 ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
 
+/* ───────────── KV write and eviction executors on a device-resident cache ─────────────
+ * The callers either side of attention. K and V are addressed like in argus_b200_attention_gen: element
+ * (head h, position t, channel c) at h*head_stride + t*pos_stride + c (HeadMajor [Hkv][cap][D]: head_stride =
+ * cap*D, pos_stride = D); kv_dtype ARGUS_B200_KV_F16 or _F32. Pointers and row pitches must be 16-byte
+ * aligned (else ARGUS_B200_E_UNSUPPORTED). All results are bit-identical to the reference's.
+ *
+ * argus_b200_kv_scatter replaces kv_scatter_f32_to_f16, kv_scatter_f32_to_f16_batch and
+ * kv_scatter_f32_to_f32_batch (engine/src/backend/cuda_pc/kernels.cu:305-360, host side
+ * engine/src/backend/cuda_pc.rs:1460-1570): the new rows k_src/v_src [seq_len][Hkv][D] F32 are written to
+ * positions write_pos .. write_pos+seq_len-1 (F16: rounded to nearest even). seq_len = 1 is the decode step.
+ *
+ * argus_b200_kv_compact replaces KVCache::compact_keep_positions and compact_keep_positions_for_head
+ * (engine/src/kv/kv_cache.rs:1266-1352), which exist on the CPU only: position write_start+i receives position
+ * keep[i] for i < n_keep, in place. keep_dev is a DEVICE array, ascending, with keep[i] >= write_start+i (an entry
+ * that breaks this moves nothing and sets the status word to 2, see argus_b200_check_status). head = -1 moves
+ * every KV head, head >= 0 only that one. Like the reference, the call does not touch the sequence length: the
+ * caller sets it to write_start + n_keep. Rows are staged through the context's scratch in ascending chunks.
+ *
+ * argus_b200_kv_weighted_merge replaces apply_weighted_merges for F32 and F16 caches
+ * (engine/src/kv/standard_format.rs:754-893; D2O Eq. 11): for merge m and every head and channel,
+ * into <- into_weight[m]*into + sum_j from_weight[j]*row(from_pos[j]), j in [from_start[m], from_start[m+1]), in
+ * list order, each product and each sum rounded on its own (F16: the F32 result is rounded once at the end).
+ * All five arrays are DEVICE arrays (from_start has n_merges+1 entries); positions are pre-compaction ones; a
+ * merge with an empty list leaves its row untouched. axis: 0 = K and V, 1 = K only, 2 = V only (MergeAxis). */
+ARGUS_B200_API int argus_b200_kv_scatter(argus_b200_ctx* ctx, void* stream, const float* k_src, const float* v_src,
+                                         void* k_dst, void* v_dst, int dst_dtype, int num_heads_kv, int head_dim,
+                                         int64_t capacity, int64_t head_stride, int64_t pos_stride, int64_t write_pos,
+                                         int64_t seq_len);
+ARGUS_B200_API int argus_b200_kv_compact(argus_b200_ctx* ctx, void* stream, void* k, void* v, int kv_dtype,
+                                         int num_heads_kv, int head_dim, int64_t head_stride, int64_t pos_stride,
+                                         const int32_t* keep_dev, int64_t n_keep, int64_t write_start, int head);
+ARGUS_B200_API int argus_b200_kv_weighted_merge(argus_b200_ctx* ctx, void* stream, void* k, void* v, int kv_dtype,
+                                                int num_heads_kv, int head_dim, int64_t head_stride, int64_t pos_stride,
+                                                const int32_t* into_pos, const float* into_weight,
+                                                const int32_t* from_start, const int32_t* from_pos,
+                                                const float* from_weight, int n_merges, int axis);
+
 /* ───────────── Decode without any allocation ─────────────
  * No counterpart in the reference (its CUDA backend allocates freely: managed KV buffers, a lazily grown
  * score scratch, a per-call score buffer in the KIVI plugin). This entry point is for hosts of this library

@@ -244,3 +244,59 @@ def lse_merge(o: np.ndarray, lse: np.ndarray) -> np.ndarray:
     out = np.zeros(o.shape[1], dtype=np.float32)
     lib().orc_lse_merge(_p(o), _p(lse), o.shape[0], o.shape[1], _p(out))
     return out
+
+
+# ── KV write and eviction executors (numpy restatements; test infrastructure like the rest of this file) ──
+
+def kv_scatter(k_src, v_src, k_cache, v_cache, write_pos):
+    """kv_scatter_f32_to_f16[_batch] / kv_scatter_f32_to_f32_batch (engine/src/backend/cuda_pc/kernels.cu:305-360):
+    src [S, Hkv, D] F32 -> HeadMajor cache [Hkv, cap, D] rows write_pos.. (numpy's F32->F16 cast rounds to nearest even,
+    as __float2half does). In place."""
+    S = k_src.shape[0]
+    with np.errstate(over="ignore"):   # values beyond the F16 range become inf, as on the device
+        for s in range(S):
+            k_cache[:, write_pos + s, :] = k_src[s].astype(k_cache.dtype)
+            v_cache[:, write_pos + s, :] = v_src[s].astype(v_cache.dtype)
+
+
+def compact_keep_positions(cache, keep, write_start, head=None):
+    """KVCache::compact_keep_positions / _for_head (engine/src/kv/kv_cache.rs:1266-1352), literally: runs of consecutive
+    source positions become one shift_positions call (a memmove of `count` rows), skipped when source == destination.
+    cache [Hkv, cap, D], in place; head=None moves every head."""
+    if len(keep) == 0:
+        return
+    heads = slice(None) if head is None else slice(head, head + 1)
+
+    def shift(src, dst, count):
+        cache[heads, dst:dst + count, :] = cache[heads, src:src + count, :].copy()
+
+    write_pos = write_start
+    batch_src, batch_dst, batch_count = keep[0], write_pos, 1
+    write_pos += 1
+    for src_pos in keep[1:]:
+        if src_pos == batch_src + batch_count:
+            batch_count += 1
+        else:
+            if batch_src != batch_dst:
+                shift(batch_src, batch_dst, batch_count)
+            batch_src, batch_dst, batch_count = src_pos, write_pos, 1
+        write_pos += 1
+    if batch_src != batch_dst:
+        shift(batch_src, batch_dst, batch_count)
+
+
+def apply_weighted_merges(k_cache, v_cache, merges, axis=0):
+    """apply_weighted_merges, F32 and F16 arms (engine/src/kv/standard_format.rs:754-893): per merge (into, into_weight,
+    [(from, w), ...]) and head, acc = into_w*x[into]; acc += w*x[from] in list order, products and sums rounded to F32
+    one by one; an F16 cache converts on load and rounds once on store. axis 0 both, 1 K only, 2 V only. In place."""
+    f32 = np.float32
+    for into, into_w, frm in merges:
+        if not frm:
+            continue
+        for buf, on in ((k_cache, axis != 2), (v_cache, axis != 1)):
+            if not on:
+                continue
+            acc = f32(into_w) * buf[:, into, :].astype(f32)
+            for pos, w in frm:
+                acc = acc + f32(w) * buf[:, pos, :].astype(f32)
+            buf[:, into, :] = acc.astype(buf.dtype)

@@ -1,0 +1,121 @@
+"""KV write and eviction executors on the device against the numpy restatements of the reference's CPU code
+(oracle.kv_scatter / compact_keep_positions / apply_weighted_merges): bit-exact, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def be():
+    from argus_engine_b200 import B200Backend
+
+    return B200Backend(0)
+
+
+def _cache(rng, hkv, cap, d, dtype):
+    k = rng.standard_normal((hkv, cap, d)).astype(dtype)
+    v = rng.standard_normal((hkv, cap, d)).astype(dtype)
+    return k, v
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("S,write_pos", [(1, 0), (1, 77), (33, 5), (128, 384)])
+def test_kv_scatter_bit_exact(be, dtype, S, write_pos):
+    rng = np.random.default_rng(S + write_pos)
+    hkv, cap, d = 8, 512, 128
+    k, v = _cache(rng, hkv, cap, d, dtype)
+    ks = (rng.standard_normal((S, hkv, d)) * 3).astype(np.float32)
+    vs = (rng.standard_normal((S, hkv, d)) * 3).astype(np.float32)
+    ks[0, 0, :4] = [65504.0, 65520.0, 1e-8, -0.0]   # F16 max, overflow to inf, underflow to zero, signed zero
+    kd, vd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+    be.kv_scatter(torch.from_numpy(ks).cuda(), torch.from_numpy(vs).cuda(), kd, vd, write_pos)
+    orc.kv_scatter(ks, vs, k, v, write_pos)
+    assert np.array_equal(kd.cpu().numpy().view(np.uint8), k.view(np.uint8))
+    assert np.array_equal(vd.cpu().numpy().view(np.uint8), v.view(np.uint8))
+
+
+def test_kv_scatter_rejects_rows_outside_capacity(be):
+    kd = torch.zeros(2, 16, 64, device="cuda", dtype=torch.float16)
+    src = torch.zeros(4, 2, 64, device="cuda")
+    with pytest.raises(RuntimeError):
+        be.kv_scatter(src, src, kd, kd.clone(), 14)
+
+
+def _h2o_like_keep(rng, cur, prefix, heavy, recent):
+    cand = np.arange(prefix, cur - recent)
+    hh = np.sort(rng.choice(cand, size=heavy, replace=False))
+    return np.concatenate([np.arange(prefix), hh, np.arange(cur - recent, cur)]).astype(np.int32)
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("head", [-1, 3])
+@pytest.mark.parametrize("cur,prefix,heavy,recent,write_start", [(1000, 4, 200, 64, 0), (4096, 0, 1500, 128, 0),
+                                                                  (300, 10, 1, 5, 0), (2000, 0, 700, 100, 0)])
+def test_kv_compact_matches_reference_shifts(be, dtype, head, cur, prefix, heavy, recent, write_start):
+    rng = np.random.default_rng(cur + heavy)
+    hkv, cap, d = 8, cur + 32, 128
+    k, v = _cache(rng, hkv, cap, d, dtype)
+    keep = _h2o_like_keep(rng, cur, prefix, heavy, recent)
+    kd, vd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+    be.kv_compact(kd, vd, torch.from_numpy(keep).cuda(), write_start, head)
+    h = None if head < 0 else head
+    orc.compact_keep_positions(k, keep.tolist(), write_start, h)
+    orc.compact_keep_positions(v, keep.tolist(), write_start, h)
+    assert be.check_status() == 0
+    assert np.array_equal(kd.cpu().numpy().view(np.uint8), k.view(np.uint8))
+    assert np.array_equal(vd.cpu().numpy().view(np.uint8), v.view(np.uint8))
+
+
+def test_kv_compact_in_chunks_and_edge_lists(be):
+    """A scratch of 64 KB forces many passes (the order of the passes is what makes the in-place move safe); an empty
+    list and an identity list move nothing; a list that would move a row to the right is refused through the status word."""
+    from argus_engine_b200 import B200Backend
+
+    small = B200Backend(0, workspace_bytes=64 << 10)
+    rng = np.random.default_rng(9)
+    hkv, cap, d = 4, 3000, 128
+    k, v = _cache(rng, hkv, cap, d, np.float16)
+    keep = _h2o_like_keep(rng, 2900, 8, 1200, 256)
+    kd, vd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+    small.kv_compact(kd, vd, torch.from_numpy(keep).cuda(), 0)
+    orc.compact_keep_positions(k, keep.tolist(), 0)
+    orc.compact_keep_positions(v, keep.tolist(), 0)
+    assert small.check_status() == 0
+    assert np.array_equal(kd.cpu().numpy(), k) and np.array_equal(vd.cpu().numpy(), v)
+    before = kd.clone()
+    small.kv_compact(kd, vd, torch.zeros(0, dtype=torch.int32, device="cuda"), 0)
+    small.kv_compact(kd, vd, torch.arange(100, dtype=torch.int32, device="cuda"), 0)
+    assert small.check_status() == 0 and torch.equal(kd, before)
+    small.kv_compact(kd, vd, torch.tensor([0, 1, 2], dtype=torch.int32, device="cuda"), 5)   # would move right
+    assert small.check_status() == 2 and torch.equal(kd, before)
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("axis", [0, 1, 2])
+def test_kv_weighted_merge_bit_exact(be, dtype, axis):
+    rng = np.random.default_rng(axis + 40)
+    hkv, cap, d = 8, 700, 128
+    k, v = _cache(rng, hkv, cap, d, dtype)
+    pos = rng.permutation(cap)
+    merges, used = [], 0
+    for m in range(60):
+        n_from = int(rng.integers(0, 5))   # some merges have an empty list and leave their row alone
+        into = int(pos[used])
+        frm = [(int(pos[used + 1 + j]), float(rng.random() * 0.5)) for j in range(n_from)]
+        used += 1 + n_from
+        merges.append((into, float(0.5 + rng.random() * 0.5), frm))
+    into_pos = np.array([m[0] for m in merges], dtype=np.int32)
+    into_w = np.array([m[1] for m in merges], dtype=np.float32)
+    from_start = np.cumsum([0] + [len(m[2]) for m in merges]).astype(np.int32)
+    from_pos = np.array([p for m in merges for p, _ in m[2]], dtype=np.int32)
+    from_w = np.array([w for m in merges for _, w in m[2]], dtype=np.float32)
+    kd, vd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+    dev = lambda a: torch.from_numpy(a).cuda()
+    be.kv_weighted_merge(kd, vd, dev(into_pos), dev(into_w), dev(from_start), dev(from_pos), dev(from_w), axis)
+    orc.apply_weighted_merges(k, v, [(m[0], np.float32(m[1]), [(p, np.float32(w)) for p, w in m[2]]) for m in merges], axis)
+    assert np.array_equal(kd.cpu().numpy().view(np.uint8), k.view(np.uint8))
+    assert np.array_equal(vd.cpu().numpy().view(np.uint8), v.view(np.uint8))

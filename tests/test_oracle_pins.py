@@ -277,3 +277,48 @@ def test_lse_merge_equals_unsplit():
         os_.append(np.zeros(d))
         ls.append(-np.inf)  # an empty shard is skipped
         np.testing.assert_allclose(orc.lse_merge(np.array(os_), np.array(ls)), full[h], atol=1e-5)
+
+
+# ── KV executors: the numpy restatements against hand-worked cases ──
+
+def test_compact_keep_positions_hand_case():
+    """keep = [0, 1, 5, 6, 9] at write_start 0 (engine/src/kv/kv_cache.rs:1266-1300): the run (0,1) stays, (5,6) moves
+    to 2..3, 9 moves to 4; everything behind position 4 keeps its old contents."""
+    cache = np.arange(2 * 12 * 4, dtype=np.float32).reshape(2, 12, 4)
+    want = cache.copy()
+    want[:, 2] = cache[:, 5]
+    want[:, 3] = cache[:, 6]
+    want[:, 4] = cache[:, 9]
+    orc.compact_keep_positions(cache, [0, 1, 5, 6, 9], 0)
+    assert np.array_equal(cache, want)
+    one = np.arange(2 * 12 * 4, dtype=np.float32).reshape(2, 12, 4)
+    ref = one.copy()
+    orc.compact_keep_positions(one, [3, 4], 1, head=1)   # per-head variant, write_start 1
+    ref[1, 1], ref[1, 2] = ref[1, 3].copy(), ref[1, 4].copy()
+    assert np.array_equal(one, ref)
+
+
+def test_apply_weighted_merges_hand_case():
+    """acc = into_w*into + w1*from1 + w2*from2 with every step rounded to F32 (standard_format.rs:860-875), F16 rounds once
+    at the store (:878-893)."""
+    k = np.zeros((1, 4, 2), dtype=np.float32)
+    k[0, 0], k[0, 1], k[0, 2] = [1.0, 2.0], [10.0, 20.0], [100.0, 200.0]
+    v = k.copy()
+    orc.apply_weighted_merges(k, v, [(0, np.float32(0.5), [(1, np.float32(0.25)), (2, np.float32(0.125))])], axis=1)
+    assert np.array_equal(k[0, 0], np.float32([0.5 + 2.5 + 12.5, 1.0 + 5.0 + 25.0]))
+    assert np.array_equal(v[0, 0], np.float32([1.0, 2.0]))   # key-only merge leaves V alone
+    h = np.float16([[[0.1, 0.2], [0.3, 0.4]]])
+    hv = h.copy()
+    orc.apply_weighted_merges(h, hv, [(0, np.float32(0.7), [(1, np.float32(0.3))])])
+    a = np.float32(0.7) * np.float16([0.1, 0.2]).astype(np.float32)
+    a = a + np.float32(0.3) * np.float16([0.3, 0.4]).astype(np.float32)
+    assert np.array_equal(h[0, 0], a.astype(np.float16))
+
+
+def test_kv_scatter_rounds_to_nearest_even():
+    src = np.float32([[[1.0 + 2 ** -11, 1.0 + 3 * 2 ** -11, 65520.0, 1e-8]]])   # ties to even: 1.0 and 1.00195; inf; 0
+    k = np.zeros((1, 2, 4), dtype=np.float16)
+    v = np.zeros_like(k)
+    orc.kv_scatter(src, src, k, v, 1)
+    assert k[0, 1].tolist() == [1.0, float(np.float16(1.0 + 2 ** -9)), float("inf"), 0.0]
+    assert not k[0, 0].any()
