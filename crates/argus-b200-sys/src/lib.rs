@@ -45,6 +45,22 @@ extern "C" {
         out: *mut c_void, n_heads_q: c_int, n_heads_kv: c_int, seq_len: c_int, cache_seq_len: c_int, head_dim: c_int,
         kv_capacity: i64, batch_size: c_int, is_head_major: c_int, dtype_mode: c_int,
     ) -> c_int;
+    pub fn argus_b200_kv_scatter(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, k_src: *const f32, v_src: *const f32, k_dst: *mut c_void,
+        v_dst: *mut c_void, dst_dtype: c_int, num_heads_kv: c_int, head_dim: c_int, capacity: i64, head_stride: i64,
+        pos_stride: i64, write_pos: i64, seq_len: i64,
+    ) -> c_int;
+    pub fn argus_b200_kv_compact(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, k: *mut c_void, v: *mut c_void, kv_dtype: c_int,
+        num_heads_kv: c_int, head_dim: c_int, head_stride: i64, pos_stride: i64, keep_dev: *const i32, n_keep: i64,
+        write_start: i64, head: c_int,
+    ) -> c_int;
+    pub fn argus_b200_kv_weighted_merge(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, k: *mut c_void, v: *mut c_void, kv_dtype: c_int,
+        num_heads_kv: c_int, head_dim: c_int, head_stride: i64, pos_stride: i64, into_pos: *const i32,
+        into_weight: *const f32, from_start: *const i32, from_pos: *const i32, from_weight: *const f32,
+        n_merges: c_int, axis: c_int,
+    ) -> c_int;
     pub fn argus_b200_kivi_has_quant_attn_kernel(ctx: *const ArgusB200Ctx, bits: c_int) -> c_int;
     pub fn argus_b200_kivi_attention_gen_quant(ctx: *mut ArgusB200Ctx, args: *const CudaQuantAttnArgs) -> c_int;
     pub fn argus_b200_kivi_gather_update_quant(ctx: *mut ArgusB200Ctx, args: *const CudaQuantAttnGatherArgs) -> c_int;
