@@ -275,6 +275,18 @@ class B200Backend:
             ps, into_pos.data_ptr(), into_weight.data_ptr(), from_start.data_ptr(), from_pos.data_ptr(),
             from_weight.data_ptr(), into_pos.numel(), axis))
 
+    def prefill_attention_scores(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_seq_len: int,
+                                 q_start_pos: int, q_window: int, sum_out: Optional[torch.Tensor] = None,
+                                 per_row: Optional[torch.Tensor] = None, per_row_per_head: bool = True,
+                                 window: int = 0) -> None:
+        """prefill_attention_scores: q [S, Hq, D] F32, caches HeadMajor [Hkv, cap, D] F16; sum_out [Hq, cache_seq_len],
+        per_row [q_window, Hq, cache_seq_len] (per head) or [q_window, cache_seq_len] (head mean), pre-zeroed."""
+        dt, hs, ps = self._kv_layout(k_cache)
+        S, hq, d = q.shape
+        self._check(self._lib.argus_b200_prefill_attention_scores(
+            self._h, self._stream(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), dt, hq, k_cache.shape[0], d, S,
+            cache_seq_len, hs, ps, q_start_pos, q_window, window, _ptr(sum_out), _ptr(per_row), int(per_row_per_head)))
+
     def check_status(self) -> int:
         """Synchronises the current stream; non-zero if a kernel's bounded wait ran out since the last check."""
         return int(self._lib.argus_b200_check_status(self._h, self._stream()))

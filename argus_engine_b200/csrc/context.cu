@@ -32,7 +32,7 @@ int Context::cuda_fail(cudaError_t e, const char* what) {
 // Scratch is carved from one allocation made at create time; nothing on the decode path allocates.
 float* Context::scratch(size_t* cursor, size_t bytes) {
     const size_t at = (*cursor + 255) & ~size_t(255);
-    if (at + bytes > ws_bytes) return nullptr;
+    if (at + bytes > ws_bytes - ws_tail_reserved) return nullptr;
     *cursor = at + bytes;
     return reinterpret_cast<float*>(ws + at);
 }

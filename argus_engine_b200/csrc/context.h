@@ -18,12 +18,17 @@ struct Context {
     size_t n_tickets = 0;
     int* status = nullptr;      // device word set by a kernel whose bounded wait ran out
     uint64_t launches = 0;
+    size_t ws_tail_reserved = 0;   // bytes at the top of `ws` a composite call keeps for itself while it calls an entry
     char err[512] = {0};
 
     void set_error(const char* fmt, ...);
     int cuda_fail(cudaError_t e, const char* what);
     float* scratch(size_t* cursor, size_t bytes);
 };
+
+// context.cu: the body of argus_b200_attention_gen[_batched]
+int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_seq* seqs, int n_seqs, float* out,
+                     int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex);
 
 void plan_splits(const int64_t* lens, int n, int hkv, int slots, int waves, int min_chunk, int32_t* chunk,
                  int32_t* nsplit);
@@ -71,6 +76,8 @@ cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d,
                                      long long pos_stride, const int* into_pos, const float* into_w, const int* from_start,
                                      const int* from_pos, const float* from_w, int n_merges, int do_k, int do_v,
                                      cudaStream_t st);
+cudaError_t launch_pfa_reduce(const float* rows, float* sum_out, float* mean_out, int n_rows, int hq, long long prefix_len,
+                              cudaStream_t st);
 // lse_merge.cu
 cudaError_t launch_lse_merge(const float* parts, int n_parts, long long part_stride, int hq, int d, float* out,
                              float* lse_out, cudaStream_t st);

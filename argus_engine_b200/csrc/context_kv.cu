@@ -107,3 +107,84 @@ extern "C" int argus_b200_kv_weighted_merge(argus_b200_ctx* c, void* stream, voi
     ctx->launches += n_merges > 0 ? 1 : 0;
     return ARGUS_B200_OK;
 }
+
+// prefill_attention_scores (engine/src/kv/standard_format.rs:1400-1510): for the trailing q_window query rows of a
+// prefill chunk, the exact softmax probabilities of every head over keys 0..=p, summed over the rows and/or kept per
+// row. Row r is a single-query decode over the first q_start_pos + r + 1 keys with score export, so the rows run as
+// ONE batched decode launch over the same cache (it stays in L2) followed by the accumulation kernel.
+extern "C" int argus_b200_prefill_attention_scores(argus_b200_ctx* c, void* stream, const float* q, const void* k_cache,
+                                                   const void* v_cache, int kv_dtype, int num_heads_q, int num_heads_kv,
+                                                   int head_dim, int seq_len, int cache_seq_len, int64_t head_stride,
+                                                   int64_t pos_stride, int q_start_pos, int q_window, int window,
+                                                   float* sum_out, float* per_row, int per_row_per_head) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    if (!q || !k_cache || !v_cache || num_heads_q <= 0 || num_heads_kv <= 0 || num_heads_q % num_heads_kv != 0 ||
+        head_dim <= 0 || seq_len < 0 || cache_seq_len < 0 || q_start_pos < 0 || q_window < 0 ||
+        q_start_pos + seq_len > cache_seq_len) {
+        ctx->set_error("prefill_attention_scores: null pointer, bad head counts, or q_start_pos + seq_len (%d + %d) beyond "
+                       "cache_seq_len %d", q_start_pos, seq_len, cache_seq_len);
+        return ARGUS_B200_E_INVALID;
+    }
+    if (window > 0 || kv_dtype != ARGUS_B200_KV_F16) {
+        ctx->set_error("prefill_attention_scores: sliding windows and F32 caches are not handled here");
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    const int qwin = std::min(q_window, seq_len);
+    if (qwin == 0 || (!sum_out && !per_row)) return ARGUS_B200_OK;
+    const int qwin_start = seq_len - qwin;
+    const int64_t prefix = cache_seq_len;
+    const size_t row_bytes = (size_t)num_heads_q * prefix * sizeof(float);   // probabilities of one query row
+    const bool direct = per_row && per_row_per_head;                          // the caller's buffer has the decode's layout
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    // Top of the scratch: decode outputs (discarded) and, unless the caller's per-row buffer can take them, the rows.
+    const size_t out_bytes_per_row = (size_t)num_heads_q * head_dim * sizeof(float);
+    const size_t budget = ctx->ws_bytes / 2;
+    int rows_per_pass = std::min(qwin, kMaxBatch);
+    if (!direct) rows_per_pass = (int)std::min<size_t>(rows_per_pass, budget / (row_bytes + out_bytes_per_row));
+    if (rows_per_pass < 1) {
+        ctx->set_error("prefill_attention_scores: scratch of %zu bytes cannot stage one row of %zu bytes", ctx->ws_bytes, row_bytes);
+        return ARGUS_B200_E_WORKSPACE;
+    }
+    const size_t tail = (((size_t)rows_per_pass * (out_bytes_per_row + (direct ? 0 : row_bytes))) + 511) & ~size_t(255);
+    if (tail > ctx->ws_bytes) return ARGUS_B200_E_WORKSPACE;
+    uint8_t* tail_base = ctx->ws + ((ctx->ws_bytes - tail) & ~size_t(255));
+    float* out_buf = reinterpret_cast<float*>(tail_base);
+    float* rows_buf = reinterpret_cast<float*>(tail_base + (((size_t)rows_per_pass * out_bytes_per_row + 255) & ~size_t(255)));
+    struct Guard {
+        Context* c;
+        ~Guard() { c->ws_tail_reserved = 0; }
+    } guard{ctx};
+    ctx->ws_tail_reserved = tail + 256;
+
+    for (int r0 = 0; r0 < qwin; r0 += rows_per_pass) {
+        const int nb = std::min(rows_per_pass, qwin - r0);
+        float* rows = direct ? per_row + (size_t)r0 * num_heads_q * prefix : rows_buf;
+        if (!direct) {
+            cudaError_t e = cudaMemsetAsync(rows, 0, (size_t)nb * row_bytes, st);   // keys behind a row's position stay zero
+            if (e != cudaSuccess) return ctx->cuda_fail(e, "prefill_attention_scores memset");
+        }
+        argus_b200_seq seqs[kMaxBatch];
+        for (int i = 0; i < nb; ++i) {
+            seqs[i].k = k_cache;
+            seqs[i].v = v_cache;
+            seqs[i].seq_len = (int64_t)q_start_pos + qwin_start + r0 + i + 1;
+            seqs[i].head_stride = head_stride;
+            seqs[i].pos_stride = pos_stride;
+        }
+        argus_b200_decode_extras ex;
+        memset(&ex, 0, sizeof(ex));
+        ex.scores = rows;
+        ex.score_stride = prefix;
+        int rc = decode_f16_entry(ctx, st, q + (size_t)(qwin_start + r0) * num_heads_q * head_dim, seqs, nb, out_buf,
+                                  num_heads_q, num_heads_kv, head_dim, kv_dtype, &ex);
+        if (rc != ARGUS_B200_OK) return rc;
+        float* mean = (per_row && !per_row_per_head) ? per_row + (size_t)r0 * prefix : nullptr;
+        cudaError_t e = launch_pfa_reduce(rows, sum_out, mean, nb, num_heads_q, prefix, st);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "prefill_attention_scores reduce launch");
+        ctx->launches += (sum_out || mean) ? 1 : 0;
+    }
+    return ARGUS_B200_OK;
+}

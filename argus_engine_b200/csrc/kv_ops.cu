@@ -6,6 +6,7 @@
 //                     new K/V rows [seq][Hkv][D] F32 -> cache rows write_pos.. (F16: round to nearest even)
 //   kv_compact        KVCache::compact_keep_positions[_for_head] (engine/src/kv/kv_cache.rs:1266-1352):
 //                     row write_start+i <- row keep[i], keep ascending
+//   pfa_reduce        the accumulation half of prefill_attention_scores (engine/src/kv/standard_format.rs:1480-1508)
 //   kv_weighted_merge apply_weighted_merges, F32/F16 arms (engine/src/kv/standard_format.rs:754-893):
 //                     into <- into_w*into + sum_j w_j*from_j, every product and sum rounded on its own, list order
 #include <cuda_fp16.h>
@@ -97,6 +98,38 @@ cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, 
     kv_compact_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
         static_cast<uint4*>(cache), static_cast<uint4*>(scratch), keep, i0, n_rows, write_start, head0, n_heads, row_vecs,
         head_stride_bytes / 16, pos_stride_bytes / 16, to_scratch, status);
+    return cudaGetLastError();
+}
+
+// ───────── prefill attention scores: accumulate the per-row probabilities ─────────
+// rows [n_rows][Hq][prefix_len] are the probabilities of n_rows consecutive query rows. sum_out[h][t] += sum over
+// rows in ascending row order; mean_out[row][t] += rows[row][h][t] * (1/Hq) in ascending head order: the reference's
+// loop orders (head outer, row inner), element by element.
+__global__ void __launch_bounds__(256) pfa_reduce_kernel(const float* __restrict__ rows, float* __restrict__ sum_out,
+                                                         float* __restrict__ mean_out, int n_rows, int hq,
+                                                         long long prefix_len, float inv_heads) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n_sum = sum_out ? (long long)hq * prefix_len : 0;
+    if (idx < n_sum) {
+        float acc = sum_out[idx];
+        for (int r = 0; r < n_rows; ++r) acc = __fadd_rn(acc, rows[(long long)r * hq * prefix_len + idx]);
+        sum_out[idx] = acc;
+        return;
+    }
+    const long long j = idx - n_sum;
+    if (mean_out == nullptr || j >= (long long)n_rows * prefix_len) return;
+    const long long r = j / prefix_len, t = j % prefix_len;
+    float acc = mean_out[j];
+    for (int h = 0; h < hq; ++h) acc = __fadd_rn(acc, __fmul_rn(rows[(r * hq + h) * prefix_len + t], inv_heads));
+    mean_out[j] = acc;
+}
+
+cudaError_t launch_pfa_reduce(const float* rows, float* sum_out, float* mean_out, int n_rows, int hq, long long prefix_len,
+                              cudaStream_t st) {
+    const long long total = (sum_out ? (long long)hq * prefix_len : 0) + (mean_out ? (long long)n_rows * prefix_len : 0);
+    if (total <= 0 || n_rows <= 0) return cudaSuccess;
+    pfa_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(rows, sum_out, mean_out, n_rows, hq, prefix_len,
+                                                                       1.0f / (float)hq);
     return cudaGetLastError();
 }
 

@@ -314,6 +314,26 @@ ARGUS_B200_API int argus_b200_kv_weighted_merge(argus_b200_ctx* ctx, void* strea
                                                 const int32_t* from_start, const int32_t* from_pos,
                                                 const float* from_weight, int n_merges, int axis);
 
+/* prefill_attention_scores (engine/src/kv/standard_format.rs:1400-1510; the H2O prefill seed, CPU-only in the
+ * reference, which reads K back from the device for it): for the trailing min(q_window, seq_len) query rows of a
+ * prefill chunk, row r at absolute position p = q_start_pos + r, the softmax probabilities of every query head over
+ * keys 0..=p (scale 1/sqrt(head_dim), GQA head h reads KV head h / (Hq/Hkv)).
+ *   q        [seq_len][Hq][D] F32 (device), the chunk's queries
+ *   sum_out  [Hq][cache_seq_len] += sum over the rows (nullable)                      -- IMP-2
+ *   per_row  per_row_per_head != 0: [q_window][Hq][cache_seq_len] = the row's probabilities;
+ *            per_row_per_head == 0: [q_window][cache_seq_len] += mean over heads (nullable) -- IMP-4
+ * As in the reference the caller zeroes the buffers first and entries behind a row's position are not written.
+ * Within the decode tolerance of the reference (its own test is bit-exact against a scalar loop; a GPU softmax is
+ * not), accumulation orders as the reference's. A sliding window (`window` > 0) and F32 caches are declined
+ * (ARGUS_B200_E_UNSUPPORTED). K and V are addressed as in argus_b200_attention_gen; V is read by the decode
+ * kernel this call is built on. */
+ARGUS_B200_API int argus_b200_prefill_attention_scores(argus_b200_ctx* ctx, void* stream, const float* q,
+                                                       const void* k_cache, const void* v_cache, int kv_dtype,
+                                                       int num_heads_q, int num_heads_kv, int head_dim, int seq_len,
+                                                       int cache_seq_len, int64_t head_stride, int64_t pos_stride,
+                                                       int q_start_pos, int q_window, int window, float* sum_out,
+                                                       float* per_row, int per_row_per_head);
+
 /* ───────────── Decode without any allocation ─────────────
  * No counterpart in the reference (its CUDA backend allocates freely: managed KV buffers, a lazily grown
  * score scratch, a per-call score buffer in the KIVI plugin). This entry point is for hosts of this library

@@ -300,3 +300,41 @@ def apply_weighted_merges(k_cache, v_cache, merges, axis=0):
             for pos, w in frm:
                 acc = acc + f32(w) * buf[:, pos, :].astype(f32)
             buf[:, into, :] = acc.astype(buf.dtype)
+
+
+def prefill_attention_scores(q, k, n_heads_kv, q_start_pos, q_window, cache_seq_len, window=None):
+    """prefill_attention_scores (engine/src/kv/standard_format.rs:1400-1510), step by step as the reference: for each
+    head h and each trailing row r (p = q_start_pos + r, keys lo..=p): scalar F32 dot in channel order, * 1/sqrt(D),
+    max, exp(logit - max) with an F32 running denominator, prob = e / denom. q [S, Hq, D] F32, k [Hkv, cap, D] (any float
+    dtype, read as F32). Returns (sum_out [Hq, prefix], per_row [qwin, Hq, prefix], head_mean [qwin, prefix])."""
+    f32 = np.float32
+    S, hq, d = q.shape
+    g = hq // n_heads_kv
+    prefix = cache_seq_len
+    qwin = min(q_window, S)
+    qwin_start = S - qwin
+    scale = f32(1.0) / np.sqrt(f32(d))
+    inv_heads = f32(1.0) / f32(hq)
+    sum_out = np.zeros((hq, prefix), dtype=f32)
+    per_row = np.zeros((qwin, hq, prefix), dtype=f32)
+    head_mean = np.zeros((qwin, prefix), dtype=f32)
+    kf = k.astype(f32)
+    for h in range(hq):
+        kvh = h // g
+        for r in range(qwin_start, S):
+            p = q_start_pos + r
+            lo = 0 if window is None else max(0, p - max(window - 1, 0))
+            keys = kf[kvh, lo:p + 1]                       # [n, D]
+            dot = np.zeros(keys.shape[0], dtype=f32)
+            for c in range(d):                              # the reference's channel-order scalar accumulation
+                dot = dot + q[r, h, c] * keys[:, c]
+            logit = dot * scale
+            e = np.exp(logit - logit.max()).astype(f32)
+            denom = f32(0.0)
+            for x in e:                                     # sequential F32 sum
+                denom = f32(denom + x)
+            prob = (e / denom).astype(f32)
+            sum_out[h, lo:p + 1] += prob
+            per_row[r - qwin_start, h, lo:p + 1] = prob
+            head_mean[r - qwin_start, lo:p + 1] += prob * inv_heads
+    return sum_out, per_row, head_mean

@@ -119,3 +119,50 @@ def test_kv_weighted_merge_bit_exact(be, dtype, axis):
     orc.apply_weighted_merges(k, v, [(m[0], np.float32(m[1]), [(p, np.float32(w)) for p, w in m[2]]) for m in merges], axis)
     assert np.array_equal(kd.cpu().numpy().view(np.uint8), k.view(np.uint8))
     assert np.array_equal(vd.cpu().numpy().view(np.uint8), v.view(np.uint8))
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(8, 2, 128), (4, 4, 64), (32, 8, 128)])
+@pytest.mark.parametrize("S,q_start,q_window", [(40, 0, 32), (6, 0, 3), (17, 300, 8), (5, 0, 9)])
+def test_prefill_attention_scores_vs_reference_restatement(be, hq, hkv, d, S, q_start, q_window):
+    """The H2O prefill seed (engine/src/kv/standard_format.rs:1400-1510): summed, per-row and head-mean outputs of the
+    trailing query window against the step-by-step restatement, at the score tolerance of the decode tests; the summed
+    output is bit-identical to the sum of the per-row output in row order (the reference's cross-check, section 3b)."""
+    rng = np.random.default_rng(hq * 1000 + S + q_start)
+    T = q_start + S
+    cap = T + 11
+    q = (rng.standard_normal((S, hq, d)) * 0.8).astype(np.float32)
+    k = rng.standard_normal((hkv, cap, d)).astype(np.float16)
+    v = rng.standard_normal((hkv, cap, d)).astype(np.float16)
+    want_sum, want_rows, want_mean = orc.prefill_attention_scores(q, k, hkv, q_start, q_window, T)
+    qwin = min(q_window, S)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    sum_out = torch.zeros(hq, T, device="cuda")
+    rows = torch.zeros(qwin, hq, T, device="cuda")
+    be.prefill_attention_scores(qd, kd, vd, T, q_start, q_window, sum_out=sum_out, per_row=rows, per_row_per_head=True)
+    mean = torch.zeros(qwin, T, device="cuda")
+    sum2 = torch.zeros(hq, T, device="cuda")
+    be.prefill_attention_scores(qd, kd, vd, T, q_start, q_window, sum_out=sum2, per_row=mean, per_row_per_head=False)
+    assert be.check_status() == 0
+    tol = dict(atol=1e-7, rtol=1e-2)
+    np.testing.assert_allclose(rows.cpu().numpy(), want_rows, **tol)
+    np.testing.assert_allclose(sum_out.cpu().numpy(), want_sum, atol=1e-6, rtol=1e-2)
+    np.testing.assert_allclose(mean.cpu().numpy(), want_mean, atol=1e-7, rtol=1e-2)
+    assert torch.equal(sum_out, sum2)                      # the staged route gives the same bits as the direct one
+    acc = torch.zeros(hq, T, device="cuda")
+    for r in range(qwin):
+        acc = acc + rows[r]
+    assert torch.equal(acc, sum_out)
+    assert np.allclose(rows.cpu().numpy().sum(-1), 1.0, atol=1e-5)   # each row is a distribution over keys 0..=p
+    # the keep list an eviction would compute from the seed is the one the reference's scores give
+    flat = sum_out.sum(0).cpu().numpy()
+    heavy = max(1, T // 8)
+    assert orc.keep_top_k(T, 2, 4, heavy, flat) == orc.keep_top_k(T, 2, 4, heavy, want_sum.sum(0)) or T < 16
+
+
+def test_prefill_attention_scores_declines_window(be):
+    q = torch.zeros(4, 4, 64, device="cuda")
+    k = torch.zeros(4, 16, 64, device="cuda", dtype=torch.float16)
+    s = torch.zeros(4, 4, device="cuda")
+    with pytest.raises(RuntimeError):
+        be.prefill_attention_scores(q, k, k, 4, 0, 2, sum_out=s, window=3)

@@ -322,3 +322,25 @@ def test_kv_scatter_rounds_to_nearest_even():
     orc.kv_scatter(src, src, k, v, 1)
     assert k[0, 1].tolist() == [1.0, float(np.float16(1.0 + 2 ** -9)), float("inf"), 0.0]
     assert not k[0, 0].any()
+
+
+def test_prefill_attention_scores_on_the_reference_test_inputs():
+    """Inputs of pfa_bit_exact_matches_eager_reference (engine/src/kv/standard_format.rs:3397-3460): q[i] = ((i % 13) - 6)*0.1,
+    k[i] = ((i % 17) - 8)*0.07, head_dim 8, seq_len 6, q_window 3, HeadMajor capacity 16, GQA 4:2, with and without a
+    sliding window of 4. Each window row is a distribution over its visible keys, so every head's summed seed has mass
+    q_window, keys outside a row's band get nothing, and the per-row outputs add up to the summed one bit for bit."""
+    nq, nkv, d, S, cap, qw = 4, 2, 8, 6, 16, 3
+    q = np.array([((i % 13) - 6.0) * 0.1 for i in range(S * nq * d)], dtype=np.float32).reshape(S, nq, d)
+    k = np.array([((i % 17) - 8.0) * 0.07 for i in range(nkv * cap * d)], dtype=np.float32).reshape(nkv, cap, d)
+    for window in (None, 4):
+        s, rows, mean = orc.prefill_attention_scores(q, k, nkv, 0, qw, S, window)
+        assert np.allclose(s.sum(1), qw, atol=1e-5)
+        acc = np.zeros_like(s)
+        for r in range(qw):
+            acc += rows[r]
+        assert np.array_equal(acc, s)
+        for step, r in enumerate(range(S - qw, S)):
+            lo = 0 if window is None else max(0, r - 3)
+            assert not rows[step, :, :lo].any() and not rows[step, :, r + 1:].any()
+            assert (rows[step, :, lo:r + 1] > 0).all()
+        assert np.allclose(mean, rows.mean(1), atol=1e-7)
