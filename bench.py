@@ -259,7 +259,7 @@ def other_configs(be, peaks, which):
         fl = wl.prefill_flops(B, S, S, 32, 128)
         res["c4_prefill_bf16"] = {"ms": med, "tflops": fl / med / 1e9, "frac_of_bf16_peak": fl / med / 1e9 / peaks["bf16_tflops"],
                                   "frac_of_bf16_sustained": fl / med / 1e9 / peaks["bf16_tflops_sustained"],
-                                  "flops": fl, "p_operand": "split (hi + residual) so that BF16 outputs hold 2e-3"}
+                                  "flops": fl, "p_operand": "F16 P against an F16 copy of each V tile made in shared memory (holds 2e-3)"}
     return res
 
 
