@@ -30,6 +30,19 @@ struct Context {
 int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_seq* seqs, int n_seqs, float* out,
                      int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex);
 
+// cudaFuncSetAttribute applies to the current device only, so the "already raised" memo of a kernel's dynamic
+// shared-memory limit is kept per device (a process may hold one context per GPU).
+constexpr int kMaxDevices = 64;
+inline cudaError_t ensure_dynamic_smem(const void* kernel, int bytes, bool (&done)[kMaxDevices]) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < kMaxDevices && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < kMaxDevices) done[dev] = true;
+    return e;
+}
+
 void plan_splits(const int64_t* lens, int n, int hkv, int slots, int waves, int min_chunk, int32_t* chunk,
                  int32_t* nsplit);
 
@@ -71,7 +84,7 @@ cudaError_t launch_kv_scatter(const float* k_src, const float* v_src, void* k_ds
                               cudaStream_t st);
 cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, long long i0, long long n_rows,
                                    long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
-                                   long long pos_stride_bytes, int to_scratch, int* status, cudaStream_t st);
+                                   long long pos_stride_bytes, int first, int* status, cudaStream_t st);
 cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d, long long head_stride,
                                      long long pos_stride, const int* into_pos, const float* into_w, const int* from_start,
                                      const int* from_pos, const float* from_w, int n_merges, int do_k, int do_v,

@@ -65,7 +65,9 @@ extern "C" int argus_b200_kv_compact(argus_b200_ctx* c, void* stream, void* k, v
     }
     const int head0 = head < 0 ? 0 : head, n_heads = head < 0 ? num_heads_kv : 1;
     const int64_t row_bytes = (int64_t)head_dim * eb;
-    const int64_t rows_per_pass = (int64_t)(ctx->ws_bytes / (size_t)(row_bytes * n_heads));
+    // Chunks of at most 32768 rows: a chunk whose first row moves at least that far needs no staging, and with an
+    // H2O-like keep list the distance passes the chunk length after the first chunk or two.
+    const int64_t rows_per_pass = std::min<int64_t>(32768, (int64_t)(ctx->ws_bytes / (size_t)(row_bytes * n_heads)));
     if (rows_per_pass < 1) {
         ctx->set_error("kv_compact: scratch of %zu bytes does not hold one row of every head", ctx->ws_bytes);
         return ARGUS_B200_E_WORKSPACE;
@@ -75,9 +77,9 @@ extern "C" int argus_b200_kv_compact(argus_b200_ctx* c, void* stream, void* k, v
         const int64_t n = std::min(rows_per_pass, n_keep - i0);
         for (int which = 0; which < 2; ++which) {
             void* cache = which == 0 ? k : v;
-            for (int to_scratch = 1; to_scratch >= 0; --to_scratch) {
+            for (int first = 1; first >= 0; --first) {
                 cudaError_t e = launch_kv_compact_pass(cache, ctx->ws, keep_dev, i0, n, write_start, head0, n_heads,
-                                                       (int)row_bytes, head_stride * eb, pos_stride * eb, to_scratch,
+                                                       (int)row_bytes, head_stride * eb, pos_stride * eb, first,
                                                        ctx->status, st);
                 if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_compact launch");
                 ctx->launches += 1;

@@ -17,6 +17,7 @@
 // Score export writes the scaled logits; finalize_scores_kernel turns them into probabilities once the
 // global log-sum-exp is known.
 #include "decode_epilogue.cuh"
+#include "context.h"
 #include "decode_params.h"
 #include "ptx.cuh"
 
@@ -241,13 +242,10 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
 template <int D, int WARPS, int STAGES>
 static cudaError_t launch_decode_f16_t(const DecodeParams& p, const DecodeBatch& bt, int n_items, cudaStream_t st) {
     using Cfg = DecodeF16Cfg<D, WARPS, STAGES>;
-    static bool attr_done = false;
+    static bool attr_done[kMaxDevices] = {};
     auto kern = decode_f16_kernel<D, WARPS, STAGES>;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_B);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    cudaError_t ea = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::SMEM_B, attr_done);
+    if (ea != cudaSuccess) return ea;
     kern<<<n_items * p.hkv, WARPS * 32, Cfg::SMEM_B, st>>>(p, bt);
     return cudaGetLastError();
 }

@@ -25,7 +25,6 @@ namespace argus {
 
 constexpr size_t kStaticScratchBytes = size_t(4) << 20;   // 4 MiB per device
 constexpr int kStaticTickets = 256;                        // one per KV head
-constexpr int kMaxDevices = 64;
 
 // Host code must never pass this name to a kernel: on the host it is only a stand-in for the symbol.
 // The device address is looked up once per device with cudaGetSymbolAddress below.

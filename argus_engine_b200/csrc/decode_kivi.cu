@@ -20,6 +20,7 @@
 #include <stdlib.h>
 
 #include "decode_epilogue.cuh"
+#include "context.h"
 #include "decode_params.h"
 #include "ptx.cuh"
 
@@ -409,13 +410,10 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
 template <int D, int BITS, int WARPS, int STAGES, int MINB = 2>
 static cudaError_t launch_kivi_t(const DecodeParams& p, const KiviBatch& bt, int n_items, cudaStream_t st) {
     using Cfg = DecodeKiviCfg<D, BITS, WARPS, STAGES>;
-    static bool attr_done = false;
+    static bool attr_done[kMaxDevices] = {};
     auto kern = decode_kivi_kernel<D, BITS, WARPS, STAGES, MINB>;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_B);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    cudaError_t ea = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::SMEM_B, attr_done);
+    if (ea != cudaSuccess) return ea;
     kern<<<n_items * p.hkv, WARPS * 32, Cfg::SMEM_B, st>>>(p, bt);
     return cudaGetLastError();
 }

@@ -23,6 +23,7 @@
 #include <stdint.h>
 
 #include "decode_epilogue.cuh"
+#include "context.h"
 #include "decode_params.h"
 #include "ptx.cuh"
 
@@ -698,13 +699,9 @@ decode_kivi_tc_kernel(const __grid_constant__ DecodeParams p, const __grid_const
 
 // Packed-part splits of this kernel are planned in whole tiles of 4 groups; one CTA per SM.
 cudaError_t launch_decode_kivi_tc(const DecodeParams& p, const KiviBatch& bt, int n_items, cudaStream_t st) {
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(ktc::decode_kivi_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             ktc::SMEM_B);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    static bool attr_done[kMaxDevices] = {};
+    cudaError_t ea = ensure_dynamic_smem(reinterpret_cast<const void*>(ktc::decode_kivi_tc_kernel), ktc::SMEM_B, attr_done);
+    if (ea != cudaSuccess) return ea;
     ktc::decode_kivi_tc_kernel<<<n_items * p.hkv, ktc::THREADS, ktc::SMEM_B, st>>>(p, bt);
     return cudaGetLastError();
 }

@@ -59,17 +59,23 @@ cudaError_t launch_kv_scatter(const float* k_src, const float* v_src, void* k_ds
 }
 
 // ───────── keep-set compaction ─────────
-// The move is in place and to the left (keep[i] >= write_start + i). Rows i of a chunk [i0, i1) are first gathered
-// into scratch and then written, chunk after chunk in ascending order: a later chunk's sources lie to the right of
-// everything an earlier chunk wrote, and inside a chunk all reads precede all writes (two launches). Rows that
-// already sit at their place are skipped by both. A keep list that is not ascending or that would move a row to
-// the right sets *status = 2 and moves nothing for the offending entry.
-// to_scratch = 1: cache -> scratch; 0: scratch -> cache. Scratch layout [heads][rows of the chunk][row_vecs] uint4.
+// The move is in place and to the left (keep[i] >= write_start + i), and the distance keep[i] - (write_start + i)
+// never shrinks along an ascending list. Rows are moved chunk after chunk in ascending order, so that a later
+// chunk's sources lie to the right of everything written before. Inside a chunk [i0, i0 + n):
+//   * if its first row moves by at least n positions, every source of the chunk lies right of every destination of
+//     the chunk: the first launch copies the rows directly and the second one returns at once;
+//   * otherwise a destination may be another row's source: the first launch gathers the rows into scratch, the
+//     second writes them (all reads precede all writes).
+// Rows already in place are skipped. An entry that is not above its predecessor or that would move a row to the
+// right is skipped and sets *status = 2; the contents of the cache are then unspecified.
+// first = 1: direct copy or cache -> scratch; 0: scratch -> cache. Scratch layout [heads][rows of the chunk][row_vecs].
 __global__ void __launch_bounds__(256) kv_compact_kernel(uint4* __restrict__ cache, uint4* __restrict__ scratch,
                                                          const int* __restrict__ keep, long long i0, long long n_rows,
                                                          long long write_start, int head0, int n_heads, int row_vecs,
-                                                         long long head_stride_v, long long pos_stride_v, int to_scratch,
+                                                         long long head_stride_v, long long pos_stride_v, int first,
                                                          int* status) {
+    const bool direct = (long long)keep[i0] - (write_start + i0) >= n_rows;   // the same answer in every thread
+    if (direct && !first) return;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long total = n_rows * n_heads * row_vecs;
     if (idx >= total) return;
@@ -85,19 +91,20 @@ __global__ void __launch_bounds__(256) kv_compact_kernel(uint4* __restrict__ cac
     }
     const long long base = (long long)(head0 + hh) * head_stride_v;
     uint4* s = scratch + ((long long)hh * n_rows + r) * row_vecs + v;
-    if (to_scratch) *s = cache[base + src * pos_stride_v + v];
+    if (direct) cache[base + dst * pos_stride_v + v] = cache[base + src * pos_stride_v + v];
+    else if (first) *s = cache[base + src * pos_stride_v + v];
     else cache[base + dst * pos_stride_v + v] = *s;
 }
 
 cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, long long i0, long long n_rows,
                                    long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
-                                   long long pos_stride_bytes, int to_scratch, int* status, cudaStream_t st) {
+                                   long long pos_stride_bytes, int first, int* status, cudaStream_t st) {
     const int row_vecs = row_bytes / 16;
     const long long total = n_rows * n_heads * row_vecs;
     if (total <= 0) return cudaSuccess;
     kv_compact_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
         static_cast<uint4*>(cache), static_cast<uint4*>(scratch), keep, i0, n_rows, write_start, head0, n_heads, row_vecs,
-        head_stride_bytes / 16, pos_stride_bytes / 16, to_scratch, status);
+        head_stride_bytes / 16, pos_stride_bytes / 16, first, status);
     return cudaGetLastError();
 }
 

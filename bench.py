@@ -260,6 +260,39 @@ def other_configs(be, peaks, which):
         res["c4_prefill_bf16"] = {"ms": med, "tflops": fl / med / 1e9, "frac_of_bf16_peak": fl / med / 1e9 / peaks["bf16_tflops"],
                                   "frac_of_bf16_sustained": fl / med / 1e9 / peaks["bf16_tflops_sustained"],
                                   "flops": fl, "p_operand": "F16 P against an F16 copy of each V tile made in shared memory (holds 2e-3)"}
+    if "kv" in which:
+        # the callers either side of attention on a device-resident F16 cache [Hkv=8, 256K tokens, D=128] (1 GiB of K+V)
+        hkv, d, cap = 8, 128, 1 << 18
+        gen = torch.Generator(device="cuda").manual_seed(5)
+        k = torch.randn(hkv, cap, d, device="cuda", generator=gen).to(torch.float16)
+        v = torch.randn(hkv, cap, d, device="cuda", generator=gen).to(torch.float16)
+        cpu = torch.Generator().manual_seed(5)
+        heavy = (torch.randperm(cap - 4 - 4096, generator=cpu)[: cap // 2].sort().values + 4)
+        keep = torch.cat([torch.arange(4), heavy, torch.arange(cap - 4096, cap)]).to(torch.int32).cuda()
+        med, _ = _time_events(lambda: be.kv_compact(k, v, keep, 0), 5)   # later repeats move the same row count
+        moved = int(keep.numel()) * hkv * d * 2 * 2                      # K and V rows that change place (upper bound)
+        kvres = {"compact_keep_positions": {"ms": med, "rows_kept": int(keep.numel()), "of": cap,
+                                            "algorithmic_gbs": 2 * moved / med / 1e6,
+                                            "frac_of_hbm_peak": 2 * moved / med / 1e6 / peaks["hbm_gbs"],
+                                            "note": "H2O-like keep list: 4 sink + 50 % heavy hitters + 4096 recent; bytes = rows read + written once"}}
+        S = 4096
+        ks = torch.randn(S, hkv, d, device="cuda", generator=gen)
+        vs = torch.randn(S, hkv, d, device="cuda", generator=gen)
+        med, _ = _time_events(lambda: be.kv_scatter(ks, vs, k, v, 1000), 20)
+        kvres["kv_scatter_prefill_4096_rows"] = {"us": med * 1e3, "gbs": S * hkv * d * (4 + 2) * 2 / med / 1e6}
+        M = 32768
+        perm = torch.randperm(cap, generator=cpu)
+        into, frm = perm[:M].to(torch.int32).cuda(), perm[M:2 * M].to(torch.int32).cuda()
+        iw, fw = torch.full((M,), 0.6, device="cuda"), torch.full((M,), 0.4, device="cuda")
+        fs = torch.arange(M + 1, dtype=torch.int32, device="cuda")
+        med, _ = _time_events(lambda: be.kv_weighted_merge(k, v, into, iw, fs, frm, fw), 10)
+        kvres["weighted_merge_32768_pairs"] = {"us": med * 1e3, "gbs": M * hkv * d * 2 * 2 * 3 / med / 1e6}
+        S = 4096
+        qf = torch.randn(S, 32, d, device="cuda", generator=gen)
+        sum_out = torch.zeros(32, S, device="cuda")
+        med, _ = _time_events(lambda: be.prefill_attention_scores(qf, k, v, S, 0, 32, sum_out=sum_out), 20)
+        kvres["prefill_attention_scores_S4096_window32"] = {"us": med * 1e3}
+        res["kv_executors"] = kvres
     return res
 
 
@@ -470,7 +503,7 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--others", default="c1,c3,c4", help="comma list of further configs to time at N=1 ('' = none)")
+    ap.add_argument("--others", default="c1,c3,c4,kv", help="comma list of further configs to time at N=1 ('' = none)")
     ap.add_argument("--no-sharded", dest="sharded", action="store_false", help="skip the sharded 1M-token decode")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -291,9 +291,11 @@ ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
  * argus_b200_kv_compact replaces KVCache::compact_keep_positions and compact_keep_positions_for_head
  * (engine/src/kv/kv_cache.rs:1266-1352), which exist on the CPU only: position write_start+i receives position
  * keep[i] for i < n_keep, in place. keep_dev is a DEVICE array, ascending, with keep[i] >= write_start+i (an entry
- * that breaks this moves nothing and sets the status word to 2, see argus_b200_check_status). head = -1 moves
+ * that breaks this is skipped and sets the status word to 2, see argus_b200_check_status; the cache contents are
+ * then unspecified). head = -1 moves
  * every KV head, head >= 0 only that one. Like the reference, the call does not touch the sequence length: the
- * caller sets it to write_start + n_keep. Rows are staged through the context's scratch in ascending chunks.
+ * caller sets it to write_start + n_keep. Rows move in ascending chunks, through the context's scratch where a
+ * chunk's sources and destinations can overlap.
  *
  * argus_b200_kv_weighted_merge replaces apply_weighted_merges for F32 and F16 caches
  * (engine/src/kv/standard_format.rs:754-893; D2O Eq. 11): for merge m and every head and channel,
