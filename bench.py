@@ -173,6 +173,9 @@ def workload_config(name, case):
             "l2": "inputs (310 MB) exceed the 126 MB L2; two KV copies are alternated between steps"}
 
 
+NCU_TRAFFIC_BYTES = 313.8e6   # per launch of decode_f16_kernel on configs[1], from the committed ncu summary
+
+
 def _time_events(fn, iters, warmup=3):
     """Median and mean device time (ms) of fn() over `iters` calls, CUDA events on the current stream."""
     import torch
@@ -447,6 +450,40 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_val = world * step_bytes / e2e_s / 1e12
+
+    # The same with the KV cache where the engine keeps it, in device memory: a decode step then moves q and the new
+    # token's K/V row from the host, writes the row into the cache (argus_b200_kv_scatter, one call per sequence as the
+    # engine's per-sequence cache objects would), runs the attention call and reads the output back.
+    knew = torch.stack([torch.from_numpy(case.k[i][:, case.lens[i] - 1, :].astype(np.float32)) for i in range(B)]).pin_memory()
+    vnew = torch.stack([torch.from_numpy(case.v[i][:, case.lens[i] - 1, :].astype(np.float32)) for i in range(B)]).pin_memory()
+    dknew, dvnew = torch.empty(B, hkv, d, device="cuda"), torch.empty(B, hkv, d, device="cuda")
+
+    def resident_step():
+        dq.copy_(hq_pin, non_blocking=True)
+        dknew.copy_(knew, non_blocking=True)
+        dvnew.copy_(vnew, non_blocking=True)
+        for i in range(B):
+            be.kv_scatter(dknew[i:i + 1], dvnew[i:i + 1], dk[i], dv[i], int(case.lens[i]) - 1)
+        be.attention_gen_batched(dq, dk, dv, case.lens, out, hq, hkv, d)
+        out_pin.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+        return float(out_pin[0, 0, 0])
+
+    resident_step()
+    barrier()
+    n_res = max(20, min(args.steps, 200))
+    t0 = time.perf_counter()
+    for _ in range(n_res):
+        resident_step()
+    res_s = (time.perf_counter() - t0) / n_res
+    if dist is not None:
+        t = torch.tensor([res_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res_s = float(t.item())
+    e2e_resident = {"value": world * step_bytes / res_s / 1e12, "unit": UNIT, "ms_per_step": res_s * 1e3, "steps": n_res,
+                    "h2d_bytes_per_step": int(q.numel() * 4 + 2 * knew.numel() * 4), "d2h_bytes_per_step": d2h,
+                    "note": "KV cache resident in HBM as in the engine; per step: q + new K/V rows H2D, 16 KV-row writes, "
+                            "the attention call, output D2H, host sync; the output equals that of the timed step"}
     sampler.stop()
 
     cpu = None
@@ -480,11 +517,15 @@ def run_b200(args):
             "config": workload_config("c2", case),
             "roofline": {"bound": "hbm", "kernel": "decode_f16_kernel<128,4,3>", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "peak_source": peaks["source"], "traffic": None,
+                         "peak_source": peaks["source"], "traffic": NCU_TRAFFIC_BYTES,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
+                                           "workload (profiles/decode_f16_c2_batched_decode.md)",
                          "algorithmic_bytes_per_launch": step_bytes},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_s * 1e3, "steps": n_e2e},
+                    "ms_per_step": e2e_s * 1e3, "steps": n_e2e,
+                    "note": "conservative: the whole KV cache of the step is copied from pinned host memory every step"},
+            "e2e_kv_resident": e2e_resident,
             "gpu_launches": int(launches),
             "clocks": sampler.summary(),
             "parity_max_abs_vs_oracle": parity,
