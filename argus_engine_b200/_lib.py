@@ -107,6 +107,7 @@ def load_library() -> C.CDLL:
     lib.argus_b200_kv_scatter.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64]
     lib.argus_b200_prefill_attention_scores.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i64, i32, i32, i32,
                                                         vp, vp, i32]
+    lib.argus_b200_kv_scatter_batched.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]
     lib.argus_b200_kv_compact.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, i64, i64, i32]
     lib.argus_b200_kv_weighted_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, vp, vp, vp, vp, i32, i32]
     lib.argus_b200_attention_gen_static.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64]

@@ -86,10 +86,14 @@ class B200Backend:
         """(head_stride, pos_stride, is_head_major) by the reference's shape rule
         (engine/src/backend.rs:336-339): HeadMajor iff rank>=3, shape[-3]==Hkv and shape[-3]!=shape[-2]."""
         shp = k_cache.shape
-        d = shp[-1]
+        if k_cache.stride(-1) != 1:
+            raise ValueError("the channel dimension of a KV cache must be contiguous")
+        # strides come from the tensor, so that a view of a larger cache (a slice of positions) is addressed correctly
         if len(shp) >= 3 and shp[-3] == num_heads_kv and shp[-3] != shp[-2]:
-            return shp[-2] * d, d, True
-        return d, num_heads_kv * d, False
+            return k_cache.stride(-3), k_cache.stride(-2), True
+        if len(shp) >= 3:
+            return k_cache.stride(-2), k_cache.stride(-3), False
+        return shp[-1], num_heads_kv * shp[-1], False
 
     # ── Backend::attention_gen ──
     def attention_gen(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
@@ -253,6 +257,19 @@ class B200Backend:
         self._check(self._lib.argus_b200_kv_scatter(self._h, self._stream(), k_src.data_ptr(), v_src.data_ptr(),
                                                     k_cache.data_ptr(), v_cache.data_ptr(), dt, hkv, d, k_cache.shape[1],
                                                     hs, ps, write_pos, S))
+
+    def kv_scatter_batched(self, k_src: torch.Tensor, v_src: torch.Tensor, k_caches, v_caches, write_pos) -> None:
+        """One new row per sequence in one launch: k_src/v_src [B, Hkv, D] F32 -> cache b at position write_pos[b]."""
+        n = len(k_caches)
+        B, hkv, d = k_src.shape
+        arr = (Seq * n)()
+        cap = (C.c_int64 * n)()
+        for i in range(n):
+            dt, hs, ps = self._kv_layout(k_caches[i])
+            arr[i] = Seq(k_caches[i].data_ptr(), v_caches[i].data_ptr(), int(write_pos[i]), hs, ps)
+            cap[i] = k_caches[i].shape[1]
+        self._check(self._lib.argus_b200_kv_scatter_batched(self._h, self._stream(), k_src.data_ptr(), v_src.data_ptr(), arr,
+                                                            cap, n, dt, hkv, d))
 
     def kv_compact(self, k_cache: torch.Tensor, v_cache: torch.Tensor, keep: torch.Tensor, write_start: int,
                    head: int = -1) -> None:

@@ -82,6 +82,9 @@ cudaError_t launch_kv_f32_to_f16(const float* src, void* dst, int hkv, long long
 cudaError_t launch_kv_scatter(const float* k_src, const float* v_src, void* k_dst, void* v_dst, bool dst_f16, int hkv,
                               int d, long long head_stride, long long pos_stride, long long write_pos, long long seq_len,
                               cudaStream_t st);
+cudaError_t launch_kv_scatter_rows(const float* k_src, const float* v_src, void* const* k_dst, void* const* v_dst,
+                                   const long long* head_stride, const long long* pos_stride, const long long* write_pos,
+                                   int n, bool dst_f16, int hkv, int d, cudaStream_t st);
 cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, long long i0, long long n_rows,
                                    long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
                                    long long pos_stride_bytes, int first, int* status, cudaStream_t st);

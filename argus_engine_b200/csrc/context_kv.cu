@@ -46,6 +46,47 @@ extern "C" int argus_b200_kv_scatter(argus_b200_ctx* c, void* stream, const floa
     return ARGUS_B200_OK;
 }
 
+extern "C" int argus_b200_kv_scatter_batched(argus_b200_ctx* c, void* stream, const float* k_src, const float* v_src,
+                                             const argus_b200_seq* seqs, const int64_t* capacity, int n_seqs, int dst_dtype,
+                                             int num_heads_kv, int head_dim) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    const int eb = elt_bytes(dst_dtype);
+    if (!k_src || !v_src || !seqs || !capacity || eb < 0 || n_seqs < 0 || n_seqs > kMaxBatch || num_heads_kv <= 0 ||
+        head_dim <= 0) {
+        ctx->set_error("kv_scatter_batched: null pointer, bad dtype or more than %d sequences", kMaxBatch);
+        return ARGUS_B200_E_INVALID;
+    }
+    void* kd[kMaxBatch];
+    void* vd[kMaxBatch];
+    long long hs[kMaxBatch], ps[kMaxBatch], wp[kMaxBatch];
+    bool aligned = head_dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(k_src) | reinterpret_cast<uintptr_t>(v_src)) & 15) == 0;
+    for (int i = 0; i < n_seqs; ++i) {
+        if (!seqs[i].k || !seqs[i].v || seqs[i].seq_len < 0 || seqs[i].seq_len >= capacity[i]) {
+            ctx->set_error("kv_scatter_batched: sequence %d: null cache or position %lld outside capacity %lld", i,
+                           (long long)seqs[i].seq_len, (long long)capacity[i]);
+            return ARGUS_B200_E_INVALID;
+        }
+        kd[i] = const_cast<void*>(seqs[i].k);
+        vd[i] = const_cast<void*>(seqs[i].v);
+        hs[i] = seqs[i].head_stride;
+        ps[i] = seqs[i].pos_stride;
+        wp[i] = seqs[i].seq_len;
+        aligned = aligned && ((reinterpret_cast<uintptr_t>(kd[i]) | reinterpret_cast<uintptr_t>(vd[i])) & 15) == 0 &&
+                  (hs[i] * eb) % 16 == 0 && (ps[i] * eb) % 16 == 0;
+    }
+    if (!aligned) {
+        ctx->set_error("kv_scatter_batched: head_dim %% 4, 16-byte aligned pointers and row pitches are required");
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    cudaError_t e = launch_kv_scatter_rows(k_src, v_src, kd, vd, hs, ps, wp, n_seqs, dst_dtype == ARGUS_B200_KV_F16,
+                                           num_heads_kv, head_dim, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_scatter_batched launch");
+    ctx->launches += n_seqs > 0 ? 1 : 0;
+    return ARGUS_B200_OK;
+}
+
 extern "C" int argus_b200_kv_compact(argus_b200_ctx* c, void* stream, void* k, void* v, int kv_dtype, int num_heads_kv,
                                      int head_dim, int64_t head_stride, int64_t pos_stride, const int32_t* keep_dev,
                                      int64_t n_keep, int64_t write_start, int head) {

@@ -58,6 +58,58 @@ cudaError_t launch_kv_scatter(const float* k_src, const float* v_src, void* k_ds
     return cudaGetLastError();
 }
 
+// One new row for each of n sequences in ONE launch (a batched decode step): sequence b's row [Hkv][D] goes to
+// position write_pos[b] of its own cache. The descriptor table travels as a kernel parameter.
+struct KvRowBatch {
+    void* k[64];
+    void* v[64];
+    long long head_stride[64];
+    long long pos_stride[64];
+    long long write_pos[64];
+};
+template <bool DST_F16>
+__global__ void __launch_bounds__(256) kv_scatter_rows_kernel(const float* __restrict__ k_src, const float* __restrict__ v_src,
+                                                              const __grid_constant__ KvRowBatch bt, int n, int hkv, int d) {
+    const int vec_per_row = d / 4;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n * hkv * vec_per_row) return;
+    const int c = (idx % vec_per_row) * 4;
+    const int h = (idx / vec_per_row) % hkv, b = idx / (vec_per_row * hkv);
+    const long long so = ((long long)b * hkv + h) * d + c;
+    const long long dof = h * bt.head_stride[b] + bt.write_pos[b] * bt.pos_stride[b] + c;
+    const float4 kx = *reinterpret_cast<const float4*>(k_src + so);
+    const float4 vx = *reinterpret_cast<const float4*>(v_src + so);
+    if constexpr (DST_F16) {
+        __half2 ka = __floats2half2_rn(kx.x, kx.y), kb = __floats2half2_rn(kx.z, kx.w);
+        __half2 va = __floats2half2_rn(vx.x, vx.y), vb = __floats2half2_rn(vx.z, vx.w);
+        *reinterpret_cast<uint2*>(static_cast<__half*>(bt.k[b]) + dof) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&ka), *reinterpret_cast<uint32_t*>(&kb));
+        *reinterpret_cast<uint2*>(static_cast<__half*>(bt.v[b]) + dof) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&va), *reinterpret_cast<uint32_t*>(&vb));
+    } else {
+        *reinterpret_cast<float4*>(static_cast<float*>(bt.k[b]) + dof) = kx;
+        *reinterpret_cast<float4*>(static_cast<float*>(bt.v[b]) + dof) = vx;
+    }
+}
+
+cudaError_t launch_kv_scatter_rows(const float* k_src, const float* v_src, void* const* k_dst, void* const* v_dst,
+                                   const long long* head_stride, const long long* pos_stride, const long long* write_pos,
+                                   int n, bool dst_f16, int hkv, int d, cudaStream_t st) {
+    if (n <= 0) return cudaSuccess;
+    KvRowBatch bt;
+    for (int i = 0; i < n; ++i) {
+        bt.k[i] = k_dst[i];
+        bt.v[i] = v_dst[i];
+        bt.head_stride[i] = head_stride[i];
+        bt.pos_stride[i] = pos_stride[i];
+        bt.write_pos[i] = write_pos[i];
+    }
+    const int total = n * hkv * (d / 4);
+    if (dst_f16) kv_scatter_rows_kernel<true><<<(total + 255) / 256, 256, 0, st>>>(k_src, v_src, bt, n, hkv, d);
+    else kv_scatter_rows_kernel<false><<<(total + 255) / 256, 256, 0, st>>>(k_src, v_src, bt, n, hkv, d);
+    return cudaGetLastError();
+}
+
 // ───────── keep-set compaction ─────────
 // The move is in place and to the left (keep[i] >= write_start + i), and the distance keep[i] - (write_start + i)
 // never shrinks along an ascending list. Rows are moved chunk after chunk in ascending order, so that a later

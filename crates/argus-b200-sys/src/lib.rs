@@ -1,5 +1,15 @@
 //! FFI declarations for `include/argus_b200.h` and the trait glue that registers the B200 kernels behind
-//! argus-engine's own plugin surface. The `#[repr(C)]` argument structs of `argus-extension-api` are passed
+//! argus-engine's own plugin surface. The `/// `argus_b200_seq`: one sequence of a batched call (strides in elements).
+#[repr(C)]
+pub struct ArgusB200Seq {
+    pub k: *const c_void,
+    pub v: *const c_void,
+    pub seq_len: i64,
+    pub head_stride: i64,
+    pub pos_stride: i64,
+}
+
+#[repr(C)]` argument structs of `argus-extension-api` are passed
 //! through unchanged: the C header declares byte-identical PODs (checked there with `static_assert`, here with
 //! the `const` assertions at the bottom).
 
@@ -45,10 +55,20 @@ extern "C" {
         out: *mut c_void, n_heads_q: c_int, n_heads_kv: c_int, seq_len: c_int, cache_seq_len: c_int, head_dim: c_int,
         kv_capacity: i64, batch_size: c_int, is_head_major: c_int, dtype_mode: c_int,
     ) -> c_int;
+    pub fn argus_b200_prefill_attention_scores(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, k_cache: *const c_void, v_cache: *const c_void,
+        kv_dtype: c_int, num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, seq_len: c_int, cache_seq_len: c_int,
+        head_stride: i64, pos_stride: i64, q_start_pos: c_int, q_window: c_int, window: c_int, sum_out: *mut f32,
+        per_row: *mut f32, per_row_per_head: c_int,
+    ) -> c_int;
     pub fn argus_b200_kv_scatter(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, k_src: *const f32, v_src: *const f32, k_dst: *mut c_void,
         v_dst: *mut c_void, dst_dtype: c_int, num_heads_kv: c_int, head_dim: c_int, capacity: i64, head_stride: i64,
         pos_stride: i64, write_pos: i64, seq_len: i64,
+    ) -> c_int;
+    pub fn argus_b200_kv_scatter_batched(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, k_src: *const f32, v_src: *const f32, seqs: *const ArgusB200Seq,
+        capacity: *const i64, n_seqs: c_int, dst_dtype: c_int, num_heads_kv: c_int, head_dim: c_int,
     ) -> c_int;
     pub fn argus_b200_kv_compact(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, k: *mut c_void, v: *mut c_void, kv_dtype: c_int,

@@ -307,6 +307,13 @@ ARGUS_B200_API int argus_b200_kv_scatter(argus_b200_ctx* ctx, void* stream, cons
                                          void* k_dst, void* v_dst, int dst_dtype, int num_heads_kv, int head_dim,
                                          int64_t capacity, int64_t head_stride, int64_t pos_stride, int64_t write_pos,
                                          int64_t seq_len);
+/* The decode-step form for a batch (no counterpart in the reference, which has no batched decode): ONE launch writes
+ * the new row k_src/v_src [n_seqs][Hkv][D] F32 of every sequence into that sequence's own cache at position
+ * seqs[b].seq_len (the sequence's length BEFORE the write, which must be below capacity[b]). `seqs` and `capacity`
+ * are HOST arrays read during the call; seqs[b] is the descriptor argus_b200_attention_gen_batched takes. */
+ARGUS_B200_API int argus_b200_kv_scatter_batched(argus_b200_ctx* ctx, void* stream, const float* k_src,
+                                                 const float* v_src, const argus_b200_seq* seqs, const int64_t* capacity,
+                                                 int n_seqs, int dst_dtype, int num_heads_kv, int head_dim);
 ARGUS_B200_API int argus_b200_kv_compact(argus_b200_ctx* ctx, void* stream, void* k, void* v, int kv_dtype,
                                          int num_heads_kv, int head_dim, int64_t head_stride, int64_t pos_stride,
                                          const int32_t* keep_dev, int64_t n_keep, int64_t write_start, int head);

@@ -38,6 +38,24 @@ def test_kv_scatter_bit_exact(be, dtype, S, write_pos):
     assert np.array_equal(vd.cpu().numpy().view(np.uint8), v.view(np.uint8))
 
 
+def test_kv_scatter_batched_one_row_per_sequence(be):
+    """The decode-step form: one launch writes each sequence's new row at that sequence's own length."""
+    rng = np.random.default_rng(21)
+    hkv, d, lens, caps = 8, 128, [5, 1000, 77, 4095], [16, 1024, 128, 4096]
+    ks = (rng.standard_normal((len(lens), hkv, d)) * 2).astype(np.float32)
+    vs = (rng.standard_normal((len(lens), hkv, d)) * 2).astype(np.float32)
+    caches = [_cache(rng, hkv, cap, d, np.float16) for cap in caps]
+    kd = [torch.from_numpy(k).cuda() for k, _ in caches]
+    vd = [torch.from_numpy(v).cuda() for _, v in caches]
+    be.kv_scatter_batched(torch.from_numpy(ks).cuda(), torch.from_numpy(vs).cuda(), kd, vd, lens)
+    for i, (k, v) in enumerate(caches):
+        orc.kv_scatter(ks[i:i + 1], vs[i:i + 1], k, v, lens[i])
+        assert np.array_equal(kd[i].cpu().numpy().view(np.uint8), k.view(np.uint8))
+        assert np.array_equal(vd[i].cpu().numpy().view(np.uint8), v.view(np.uint8))
+    with pytest.raises(RuntimeError):   # a full cache has no room for the row
+        be.kv_scatter_batched(torch.from_numpy(ks).cuda(), torch.from_numpy(vs).cuda(), kd, vd, [5, 1000, 128, 10])
+
+
 def test_kv_scatter_rejects_rows_outside_capacity(be):
     kd = torch.zeros(2, 16, 64, device="cuda", dtype=torch.float16)
     src = torch.zeros(4, 2, 64, device="cuda")
