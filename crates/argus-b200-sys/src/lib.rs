@@ -1,15 +1,5 @@
 //! FFI declarations for `include/argus_b200.h` and the trait glue that registers the B200 kernels behind
-//! argus-engine's own plugin surface. The `/// `argus_b200_seq`: one sequence of a batched call (strides in elements).
-#[repr(C)]
-pub struct ArgusB200Seq {
-    pub k: *const c_void,
-    pub v: *const c_void,
-    pub seq_len: i64,
-    pub head_stride: i64,
-    pub pos_stride: i64,
-}
-
-#[repr(C)]` argument structs of `argus-extension-api` are passed
+//! argus-engine's own plugin surface. The `#[repr(C)]` argument structs of `argus-extension-api` are passed
 //! through unchanged: the C header declares byte-identical PODs (checked there with `static_assert`, here with
 //! the `const` assertions at the bottom).
 
@@ -21,6 +11,16 @@ use argus_extension_api::{
     CudaScoreReduceMakeArgs, CudaScoreReduceReg, CUDA_QUANT_ATTN_REGS, CUDA_SCORE_REDUCERS,
 };
 use linkme::distributed_slice;
+
+/// `argus_b200_seq`: one sequence of a batched call (strides in elements).
+#[repr(C)]
+pub struct ArgusB200Seq {
+    pub k: *const c_void,
+    pub v: *const c_void,
+    pub seq_len: i64,
+    pub head_stride: i64,
+    pub pos_stride: i64,
+}
 
 #[repr(C)]
 pub struct ArgusB200Ctx {
