@@ -108,6 +108,7 @@ def load_library() -> C.CDLL:
     lib.argus_b200_prefill_attention_scores.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i64, i32, i32, i32,
                                                         vp, vp, i32]
     lib.argus_b200_kv_scatter_batched.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]
+    lib.argus_b200_d2o_nearest.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, vp, i32, vp, i32, vp, vp]
     lib.argus_b200_kv_compact.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, i64, i64, i32]
     lib.argus_b200_kv_weighted_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, vp, vp, vp, vp, i32, i32]
     lib.argus_b200_attention_gen_static.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64]

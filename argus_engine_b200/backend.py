@@ -292,6 +292,17 @@ class B200Backend:
             ps, into_pos.data_ptr(), into_weight.data_ptr(), from_start.data_ptr(), from_pos.data_ptr(),
             from_weight.data_ptr(), into_pos.numel(), axis))
 
+    def d2o_nearest(self, k_cache: torch.Tensor, evict_pos: torch.Tensor, retain_pos: torch.Tensor):
+        """find_nearest_layer_wide_via for every evicted position: (nearest retained position int32 [E], similarity f32 [E])."""
+        dt, hs, ps = self._kv_layout(k_cache)
+        n_e, n_r = evict_pos.numel(), retain_pos.numel()
+        nearest = torch.empty(n_e, dtype=torch.int32, device=k_cache.device)
+        sim = torch.empty(n_e, dtype=torch.float32, device=k_cache.device)
+        self._check(self._lib.argus_b200_d2o_nearest(self._h, self._stream(), k_cache.data_ptr(), dt, k_cache.shape[0],
+                                                     k_cache.shape[2], hs, ps, _ptr(evict_pos) if n_e else None, n_e,
+                                                     _ptr(retain_pos) if n_r else None, n_r, nearest.data_ptr(), sim.data_ptr()))
+        return nearest, sim
+
     def prefill_attention_scores(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_seq_len: int,
                                  q_start_pos: int, q_window: int, sum_out: Optional[torch.Tensor] = None,
                                  per_row: Optional[torch.Tensor] = None, per_row_per_head: bool = True,

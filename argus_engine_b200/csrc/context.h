@@ -92,6 +92,9 @@ cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d,
                                      long long pos_stride, const int* into_pos, const float* into_w, const int* from_start,
                                      const int* from_pos, const float* from_w, int n_merges, int do_k, int do_v,
                                      cudaStream_t st);
+cudaError_t launch_d2o_nearest(const void* k, bool f16, long long head_stride, long long pos_stride, int hkv, int d,
+                               const int* evict, int n_evict, const int* retain, int n_retain, float* norms,
+                               unsigned long long* best, int* nearest, float* sim_out, cudaStream_t st);
 cudaError_t launch_pfa_reduce(const float* rows, float* sum_out, float* mean_out, int n_rows, int hq, long long prefix_len,
                               cudaStream_t st);
 // lse_merge.cu

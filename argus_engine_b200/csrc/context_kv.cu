@@ -231,3 +231,37 @@ extern "C" int argus_b200_prefill_attention_scores(argus_b200_ctx* c, void* stre
     }
     return ARGUS_B200_OK;
 }
+
+extern "C" int argus_b200_d2o_nearest(argus_b200_ctx* c, void* stream, const void* k_cache, int kv_dtype, int num_heads_kv,
+                                      int head_dim, int64_t head_stride, int64_t pos_stride, const int32_t* evict_pos,
+                                      int n_evict, const int32_t* retain_pos, int n_retain, int32_t* nearest_out,
+                                      float* sim_out) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    const int eb = elt_bytes(kv_dtype);
+    if (!k_cache || eb < 0 || num_heads_kv <= 0 || head_dim <= 0 || n_evict < 0 || n_retain < 0 ||
+        (n_evict > 0 && (!evict_pos || !nearest_out || !sim_out)) || (n_retain > 0 && !retain_pos)) {
+        ctx->set_error("d2o_nearest: null pointer, bad dtype or negative counts");
+        return ARGUS_B200_E_INVALID;
+    }
+    if (head_dim % 32 != 0 || (n_evict + 31) / 32 > 65535) {
+        ctx->set_error("d2o_nearest: head_dim must be a multiple of 32 and at most 2M evicted positions per call");
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    if (n_evict == 0) return ARGUS_B200_OK;
+    size_t cur = 0;
+    float* norms = ctx->scratch(&cur, (size_t)(n_evict + n_retain) * sizeof(float));
+    float* best = ctx->scratch(&cur, (size_t)n_evict * sizeof(unsigned long long));
+    if (!norms || !best) {
+        ctx->set_error("d2o_nearest: scratch of %zu bytes is too small", ctx->ws_bytes);
+        return ARGUS_B200_E_WORKSPACE;
+    }
+    cudaError_t e = launch_d2o_nearest(k_cache, kv_dtype == ARGUS_B200_KV_F16, head_stride, pos_stride, num_heads_kv, head_dim,
+                                       evict_pos, n_evict, retain_pos, n_retain, norms,
+                                       reinterpret_cast<unsigned long long*>(best), nearest_out, sim_out,
+                                       static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "d2o_nearest launch");
+    ctx->launches += n_retain > 0 ? 3 : 2;
+    return ARGUS_B200_OK;
+}

@@ -252,3 +252,143 @@ cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d,
 }
 
 }  // namespace argus
+
+namespace argus {
+
+// ───────── D2O nearest retained token (Eq. 8) ─────────
+// find_nearest_layer_wide_via + cosine_similarity (crates/techniques/d2o/src/lib.rs:187-255): for every evicted
+// position, the retained position whose head-concatenated K row has the largest cosine similarity, the first one in
+// list order on ties, never the evicted position itself. The reference accumulates dot and the two squared norms
+// over the Hkv*D channels in order, one rounding per product and per sum; the kernels below do exactly that (so the
+// similarities and therefore the selected indices are bit-identical): the norms once per listed row, the dot
+// products in 32 x 32 tiles of (evicted, retained) pairs, 2 x 2 pairs per thread, channels in ascending order.
+template <typename T>
+__global__ void __launch_bounds__(128) d2o_norms_kernel(const T* __restrict__ k, long long head_stride, long long pos_stride,
+                                                        int hkv, int d, const int* __restrict__ evict, int n_evict,
+                                                        const int* __restrict__ retain, int n_retain,
+                                                        float* __restrict__ norms) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_evict + n_retain) return;
+    const long long pos = i < n_evict ? evict[i] : retain[i - n_evict];
+    float acc = 0.f;
+    for (int h = 0; h < hkv; ++h) {
+        const T* row = k + h * head_stride + pos * pos_stride;
+        for (int c = 0; c < d; ++c) {
+            const float x = load_f32(row + c);
+            acc = __fadd_rn(acc, __fmul_rn(x, x));
+        }
+    }
+    norms[i] = acc;
+}
+
+__device__ __forceinline__ unsigned long long d2o_key(float sim, int list_index) {
+    sim = sim + 0.0f;   // -0 -> +0: the reference's `>` does not tell them apart
+    const uint32_t u = __float_as_uint(sim);
+    const uint32_t ord = u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u);
+    return ((unsigned long long)ord << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)list_index);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) d2o_pairs_kernel(const T* __restrict__ k, long long head_stride, long long pos_stride,
+                                                        int hkv, int d, const int* __restrict__ evict, int n_evict,
+                                                        const int* __restrict__ retain, int n_retain,
+                                                        const float* __restrict__ norms, unsigned long long* __restrict__ best) {
+    __shared__ float sa[32][33], sb[32][33];
+    __shared__ int pa[32], pb[32];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int e0 = blockIdx.y * 32, r0 = blockIdx.x * 32;
+    if (threadIdx.x < 32) pa[threadIdx.x] = e0 + threadIdx.x < n_evict ? evict[e0 + threadIdx.x] : -1;
+    else if (threadIdx.x < 64) pb[threadIdx.x - 32] = r0 + threadIdx.x - 32 < n_retain ? retain[r0 + threadIdx.x - 32] : -1;
+    __syncthreads();
+    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    const int dim = hkv * d;
+    for (int g0 = 0; g0 < dim; g0 += 32) {
+        // 64 rows x 32 channels of this chunk -> shared memory as F32 (d is a multiple of 32: a chunk stays in one head)
+        const int h = g0 / d, c0 = g0 % d;
+        for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+            const int r = e >> 5, c = e & 31;
+            const int pos = r < 32 ? pa[r] : pb[r - 32];
+            const float x = pos >= 0 ? load_f32(k + h * head_stride + (long long)pos * pos_stride + c0 + c) : 0.f;
+            if (r < 32) sa[r][c] = x;
+            else sb[r - 32][c] = x;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int c = 0; c < 32; ++c) {
+            const float a0 = sa[2 * ty][c], a1 = sa[2 * ty + 1][c], b0 = sb[2 * tx][c], b1 = sb[2 * tx + 1][c];
+            acc[0][0] = __fadd_rn(acc[0][0], __fmul_rn(a0, b0));
+            acc[0][1] = __fadd_rn(acc[0][1], __fmul_rn(a0, b1));
+            acc[1][0] = __fadd_rn(acc[1][0], __fmul_rn(a1, b0));
+            acc[1][1] = __fadd_rn(acc[1][1], __fmul_rn(a1, b1));
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int ei = e0 + 2 * ty + i;
+        unsigned long long key = 0;   // 0 = no candidate
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int ri = r0 + 2 * tx + j;
+            if (ei < n_evict && ri < n_retain && pb[2 * tx + j] != pa[2 * ty + i]) {
+                const float denom = __fsqrt_rn(__fmul_rn(norms[ei], norms[n_evict + ri]));
+                const float sim = denom < 1e-10f ? 0.f : __fdiv_rn(acc[i][j], denom);
+                if (sim == sim && sim != -INFINITY) {   // NaN and -inf never beat the reference's initial -inf
+                    const unsigned long long kk = d2o_key(sim, ri);
+                    key = kk > key ? kk : key;
+                }
+            }
+        }
+        // the 16 threads with this ty share the evicted rows: reduce over tx, one atomic per row and block
+#pragma unroll
+        for (int sh = 8; sh > 0; sh >>= 1) {
+            const unsigned long long o = __shfl_xor_sync(0xffffffffu, key, sh);
+            key = o > key ? o : key;
+        }
+        if (tx == 0 && key != 0 && ei < n_evict) atomicMax(best + ei, key);
+    }
+}
+
+__global__ void __launch_bounds__(256) d2o_finalize_kernel(const unsigned long long* __restrict__ best,
+                                                           const int* __restrict__ evict, int n_evict,
+                                                           const int* __restrict__ retain, int n_retain,
+                                                           int* __restrict__ nearest, float* __restrict__ sim_out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_evict) return;
+    const unsigned long long key = best[i];
+    if (key == 0) {   // no valid target: the first retained position (or the evicted one), similarity 0
+        nearest[i] = n_retain > 0 ? retain[0] : evict[i];
+        sim_out[i] = 0.f;
+        return;
+    }
+    const uint32_t ord = (uint32_t)(key >> 32);
+    nearest[i] = retain[0xFFFFFFFFu - (uint32_t)key];
+    sim_out[i] = __uint_as_float(ord ^ ((ord >> 31) ? 0x80000000u : 0xFFFFFFFFu));
+}
+
+cudaError_t launch_d2o_nearest(const void* k, bool f16, long long head_stride, long long pos_stride, int hkv, int d,
+                               const int* evict, int n_evict, const int* retain, int n_retain, float* norms,
+                               unsigned long long* best, int* nearest, float* sim_out, cudaStream_t st) {
+    if (n_evict <= 0) return cudaSuccess;
+    cudaError_t e = cudaMemsetAsync(best, 0, (size_t)n_evict * sizeof(unsigned long long), st);
+    if (e != cudaSuccess) return e;
+    const int rows = n_evict + n_retain;
+    const dim3 grid((unsigned)((n_retain + 31) / 32), (unsigned)((n_evict + 31) / 32));
+    if (f16) {
+        d2o_norms_kernel<__half><<<(rows + 127) / 128, 128, 0, st>>>(static_cast<const __half*>(k), head_stride, pos_stride, hkv,
+                                                                     d, evict, n_evict, retain, n_retain, norms);
+        if (n_retain > 0)
+            d2o_pairs_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(k), head_stride, pos_stride, hkv, d, evict,
+                                                            n_evict, retain, n_retain, norms, best);
+    } else {
+        d2o_norms_kernel<float><<<(rows + 127) / 128, 128, 0, st>>>(static_cast<const float*>(k), head_stride, pos_stride, hkv, d,
+                                                                    evict, n_evict, retain, n_retain, norms);
+        if (n_retain > 0)
+            d2o_pairs_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(k), head_stride, pos_stride, hkv, d, evict,
+                                                           n_evict, retain, n_retain, norms, best);
+    }
+    d2o_finalize_kernel<<<(n_evict + 255) / 256, 256, 0, st>>>(best, evict, n_evict, retain, n_retain, nearest, sim_out);
+    return cudaGetLastError();
+}
+
+}  // namespace argus

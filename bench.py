@@ -295,6 +295,11 @@ def other_configs(be, peaks, which):
         sum_out = torch.zeros(32, S, device="cuda")
         med, _ = _time_events(lambda: be.prefill_attention_scores(qf, k, v, S, 0, 32, sum_out=sum_out), 20)
         kvres["prefill_attention_scores_S4096_window32"] = {"us": med * 1e3}
+        ne, nr = 4096, 8192
+        ev, rt = perm[:ne].to(torch.int32).cuda(), perm[ne:ne + nr].sort().values.to(torch.int32).cuda()
+        med, _ = _time_events(lambda: be.d2o_nearest(k, ev, rt), 5)
+        kvres["d2o_nearest_4096x8192"] = {"ms": med, "pair_dots_per_s": ne * nr / med * 1e3,
+                                          "note": "1024-channel sequential-order F32 dot products (bit-exact index selection)"}
         res["kv_executors"] = kvres
     return res
 

@@ -70,6 +70,11 @@ extern "C" {
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, k_src: *const f32, v_src: *const f32, seqs: *const ArgusB200Seq,
         capacity: *const i64, n_seqs: c_int, dst_dtype: c_int, num_heads_kv: c_int, head_dim: c_int,
     ) -> c_int;
+    pub fn argus_b200_d2o_nearest(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, k_cache: *const c_void, kv_dtype: c_int, num_heads_kv: c_int,
+        head_dim: c_int, head_stride: i64, pos_stride: i64, evict_pos: *const i32, n_evict: c_int,
+        retain_pos: *const i32, n_retain: c_int, nearest_out: *mut i32, sim_out: *mut f32,
+    ) -> c_int;
     pub fn argus_b200_kv_compact(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, k: *mut c_void, v: *mut c_void, kv_dtype: c_int,
         num_heads_kv: c_int, head_dim: c_int, head_stride: i64, pos_stride: i64, keep_dev: *const i32, n_keep: i64,

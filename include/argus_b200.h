@@ -323,6 +323,18 @@ ARGUS_B200_API int argus_b200_kv_weighted_merge(argus_b200_ctx* ctx, void* strea
                                                 const int32_t* from_start, const int32_t* from_pos,
                                                 const float* from_weight, int n_merges, int axis);
 
+/* D2O Eq. 8, find_nearest_layer_wide_via with cosine_similarity (crates/techniques/d2o/src/lib.rs:187-255; CPU-only in
+ * the reference): for each evicted position the retained position whose K row (all KV heads concatenated) has the
+ * largest cosine similarity - the first one in list order on ties, never the evicted position itself; no valid
+ * target gives retain_pos[0] (or the evicted position when the list is empty) and similarity 0. Dot products and
+ * squared norms are accumulated channel by channel with one rounding per product and per sum, as the reference
+ * does, so similarities and selected positions are bit-identical. evict_pos / retain_pos / nearest_out / sim_out are
+ * DEVICE arrays. head_dim must be a multiple of 32. */
+ARGUS_B200_API int argus_b200_d2o_nearest(argus_b200_ctx* ctx, void* stream, const void* k_cache, int kv_dtype,
+                                          int num_heads_kv, int head_dim, int64_t head_stride, int64_t pos_stride,
+                                          const int32_t* evict_pos, int n_evict, const int32_t* retain_pos, int n_retain,
+                                          int32_t* nearest_out, float* sim_out);
+
 /* prefill_attention_scores (engine/src/kv/standard_format.rs:1400-1510; the H2O prefill seed, CPU-only in the
  * reference, which reads K back from the device for it): for the trailing min(q_window, seq_len) query rows of a
  * prefill chunk, row r at absolute position p = q_start_pos + r, the softmax probabilities of every query head over

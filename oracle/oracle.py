@@ -338,3 +338,43 @@ def prefill_attention_scores(q, k, n_heads_kv, q_start_pos, q_window, cache_seq_
             per_row[r - qwin_start, h, lo:p + 1] = prob
             head_mean[r - qwin_start, lo:p + 1] += prob * inv_heads
     return sum_out, per_row, head_mean
+
+
+def d2o_find_nearest(k_cache, evict_pos, retain_pos):
+    """find_nearest_layer_wide_via + cosine_similarity (crates/techniques/d2o/src/lib.rs:187-255): k_cache [Hkv, cap, D];
+    per evicted position the retained position of the largest cosine similarity between head-concatenated K rows
+    (strict `>`: first in list order on ties; the evicted position itself is skipped; no valid target -> retain[0] or the
+    evicted position, similarity 0). dot and the squared norms are accumulated channel by channel in F32, one rounding
+    per product and per sum, exactly like the scalar loop. Returns (nearest int32 [E], sim float32 [E])."""
+    f32 = np.float32
+    hkv, _, d = k_cache.shape
+    ev = np.asarray(evict_pos, dtype=np.int64)
+    rt = np.asarray(retain_pos, dtype=np.int64)
+    nearest = np.zeros(len(ev), dtype=np.int32)
+    sims = np.zeros(len(ev), dtype=f32)
+    if len(ev) == 0:
+        return nearest, sims
+    rows_e = k_cache[:, ev, :].astype(f32).transpose(1, 0, 2).reshape(len(ev), hkv * d)
+    rows_r = k_cache[:, rt, :].astype(f32).transpose(1, 0, 2).reshape(len(rt), hkv * d) if len(rt) else np.zeros((0, hkv * d), f32)
+    dot = np.zeros((len(ev), len(rt)), dtype=f32)
+    na = np.zeros(len(ev), dtype=f32)
+    nb = np.zeros(len(rt), dtype=f32)
+    for c in range(hkv * d):
+        a, b = rows_e[:, c], rows_r[:, c]
+        dot = dot + a[:, None] * b[None, :]
+        na = na + a * a
+        nb = nb + b * b
+    with np.errstate(divide="ignore", invalid="ignore"):
+        denom = np.sqrt(na[:, None] * nb[None, :]).astype(f32)
+        sim = np.where(denom < f32(1e-10), f32(0.0), (dot / denom).astype(f32)).astype(f32)
+    for i, e in enumerate(ev):
+        best_pos = int(rt[0]) if len(rt) else int(e)
+        best = -np.inf
+        for j, r in enumerate(rt):
+            if r == e:
+                continue
+            if sim[i, j] > best:
+                best, best_pos = sim[i, j], int(r)
+        nearest[i] = best_pos
+        sims[i] = f32(0.0) if best == -np.inf else best
+    return nearest, sims

@@ -184,3 +184,41 @@ def test_prefill_attention_scores_declines_window(be):
     s = torch.zeros(4, 4, device="cuda")
     with pytest.raises(RuntimeError):
         be.prefill_attention_scores(q, k, k, 4, 0, 2, sum_out=s, window=3)
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("hkv,d,n_e,n_r", [(8, 128, 70, 333), (2, 64, 5, 40), (4, 128, 33, 1)])
+def test_d2o_nearest_bit_exact(be, dtype, hkv, d, n_e, n_r):
+    """D2O Eq. 8 (crates/techniques/d2o/src/lib.rs:187-255): the selected retained position and the similarity of every
+    evicted position equal the step-by-step restatement bit for bit - including exact ties (duplicated rows: the first
+    in list order wins), an evicted position that also sits in the retained list (skipped) and an all-zero row."""
+    rng = np.random.default_rng(n_e * 7 + n_r)
+    cap = 1024
+    k = rng.standard_normal((hkv, cap, d)).astype(dtype)
+    pos = rng.permutation(cap)
+    evict = pos[:n_e].astype(np.int32)
+    retain = np.sort(pos[n_e:n_e + n_r]).astype(np.int32)
+    if n_r >= 40:
+        k[:, retain[7]] = k[:, retain[3]]          # an exact tie between two retained rows
+        k[:, evict[0]] = k[:, retain[3]] * dtype(0.5)   # ... which the first evicted row points at
+        k[:, retain[11]] = 0                       # zero norm: similarity 0 by the denominator guard
+        retain[20] = evict[1]                      # an evicted position inside the retained list is skipped
+    want_pos, want_sim = orc.d2o_find_nearest(k, evict, retain)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    got_pos, got_sim = be.d2o_nearest(dev(k), dev(evict), dev(retain))
+    assert np.array_equal(got_pos.cpu().numpy(), want_pos)
+    assert np.array_equal(got_sim.cpu().numpy().view(np.uint32), want_sim.view(np.uint32))
+    if n_r >= 40:
+        assert want_pos[0] == retain[3] and want_pos[1] != evict[1]
+
+
+def test_d2o_nearest_empty_lists(be):
+    k = torch.randn(2, 64, 64, device="cuda").half()
+    ev = torch.tensor([5, 9], dtype=torch.int32, device="cuda")
+    none = torch.zeros(0, dtype=torch.int32, device="cuda")
+    pos, sim = be.d2o_nearest(k, ev, none)
+    assert pos.tolist() == [5, 9] and sim.tolist() == [0.0, 0.0]          # empty retained list: itself, similarity 0
+    pos, sim = be.d2o_nearest(k, ev, torch.tensor([5], dtype=torch.int32, device="cuda"))
+    assert pos.tolist()[0] == 5 and sim.tolist()[0] == 0.0                 # only itself to choose from
+    pos, sim = be.d2o_nearest(k, none, ev)
+    assert pos.numel() == 0

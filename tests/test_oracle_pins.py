@@ -344,3 +344,20 @@ def test_prefill_attention_scores_on_the_reference_test_inputs():
             assert not rows[step, :, :lo].any() and not rows[step, :, r + 1:].any()
             assert (rows[step, :, lo:r + 1] > 0).all()
         assert np.allclose(mean, rows.mean(1), atol=1e-7)
+
+
+def test_d2o_find_nearest_reference_case():
+    """find_nearest_picks_most_similar_retained (crates/techniques/d2o/src/lib.rs:888-910) in spirit: with one head of
+    dimension 2 the evicted row (1, 0) is nearest to the retained row pointing the same way; orthogonal and opposite rows
+    lose; similarity of parallel rows is exactly 1."""
+    k = np.zeros((1, 4, 2), dtype=np.float32)
+    k[0, 0] = [1.0, 0.0]      # evicted
+    k[0, 1] = [0.0, 1.0]      # orthogonal
+    k[0, 2] = [2.0, 0.0]      # parallel
+    k[0, 3] = [-1.0, 0.0]     # opposite
+    pos, sim = orc.d2o_find_nearest(k, [0], [1, 2, 3])
+    assert pos.tolist() == [2] and sim.tolist() == [1.0]
+    pos, sim = orc.d2o_find_nearest(k, [0], [0])          # only itself: first of the list, similarity 0
+    assert pos.tolist() == [0] and sim.tolist() == [0.0]
+    pos, sim = orc.d2o_find_nearest(k, [0], [])
+    assert pos.tolist() == [0] and sim.tolist() == [0.0]
