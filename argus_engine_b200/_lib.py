@@ -14,6 +14,10 @@ class ArgusB200Error(RuntimeError):
         self.code = code
 
 
+class PagedSeq(C.Structure):
+    _fields_ = [("page_table", C.c_void_p), ("seq_len", C.c_int64)]
+
+
 class Seq(C.Structure):
     _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("seq_len", C.c_int64), ("head_stride", C.c_int64),
                 ("pos_stride", C.c_int64)]
@@ -109,6 +113,7 @@ def load_library() -> C.CDLL:
                                                         vp, vp, i32]
     lib.argus_b200_kv_scatter_batched.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]
     lib.argus_b200_d2o_nearest.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, vp, i32, vp, i32, vp, vp]
+    lib.argus_b200_attention_gen_paged.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i64, i64, i64, vp]
     lib.argus_b200_kv_compact.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, i64, i64, i32]
     lib.argus_b200_kv_weighted_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, vp, vp, vp, vp, i32, i32]
     lib.argus_b200_attention_gen_static.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64]

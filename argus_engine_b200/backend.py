@@ -13,7 +13,7 @@ from typing import Optional, Sequence
 import torch
 
 from ._lib import (ArgusB200Error, DecodeExtrasC, KiviSeq, QuantAttnArgs, QuantDequantFlushArgs, QuantGatherArgs,
-                   QuantScatterResidualArgs, ScoreReduceArgs, Seq, load_library)
+                   QuantScatterResidualArgs, PagedSeq, ScoreReduceArgs, Seq, load_library)
 
 KV_F32, KV_F16 = 0, 1
 
@@ -128,6 +128,19 @@ class B200Backend:
         self._check(self._lib.argus_b200_attention_gen_batched(
             self._h, self._stream(), q.data_ptr(), arr, n, out.data_ptr(), num_heads_q, num_heads_kv, head_dim, dt,
             self._extras(extras)))
+
+    def attention_gen_paged(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_tables, seq_lens,
+                            out: torch.Tensor, num_heads_q: int, extras: Optional[DecodeExtras] = None) -> None:
+        """Batched decode over paged F16 caches. Pools [n_pages, Hkv, page_tokens, D]; page_tables: one int32 device
+        tensor per sequence; q/out [B, Hq, D]."""
+        n_pages, hkv, ptok, d = k_pool.shape
+        n = len(page_tables)
+        arr = (PagedSeq * n)()
+        for i in range(n):
+            arr[i] = PagedSeq(page_tables[i].data_ptr() if page_tables[i] is not None else None, int(seq_lens[i]))
+        self._check(self._lib.argus_b200_attention_gen_paged(
+            self._h, self._stream(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), arr, n, out.data_ptr(), num_heads_q,
+            hkv, d, ptok, k_pool.stride(0), k_pool.stride(1), k_pool.stride(2), self._extras(extras)))
 
     # ── Backend::flash_attention_prefill ──
     def flash_attention_prefill(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,

@@ -82,7 +82,8 @@ static int env_int(const char* name, int dflt) {
 }
 
 int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_seq* seqs, int n_seqs,
-                     float* out, int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex) {
+                     float* out, int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex,
+                     const PagedInfo* paged) {
     if (!ctx) return ARGUS_B200_E_INVALID;
     ctx->err[0] = 0;
     if (!q || !seqs || !out || n_seqs <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || d <= 0) {
@@ -105,6 +106,16 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
 
     DecodeBatch bt;
     memset(&bt, 0, sizeof(bt));
+    if (paged) {
+        if (kv_dtype != ARGUS_B200_KV_F16 || paged->page_tokens <= 0 || paged->page_tokens % 16 != 0 ||
+            (paged->page_stride & 7) || !paged->page_tables) {
+            ctx->set_error("attention_gen_paged: F16 pools, page_tokens a positive multiple of 16 and a page stride that is a "
+                           "multiple of 8 elements are required");
+            return ARGUS_B200_E_UNSUPPORTED;
+        }
+        bt.page_tokens = paged->page_tokens;
+        bt.page_stride = paged->page_stride;
+    }
     int64_t lens[kMaxBatch];
     int64_t max_len = 0;
     for (int i = 0; i < n_seqs; ++i) {
@@ -120,6 +131,13 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
                 ctx->set_error("attention_gen: sequence %d: K/V must be 16-byte aligned with strides that are multiples of 8 elements", i);
                 return ARGUS_B200_E_INVALID;
             }
+        }
+        if (paged) {
+            if (s.seq_len > 0 && !paged->page_tables[i]) {
+                ctx->set_error("attention_gen_paged: sequence %d has no page table", i);
+                return ARGUS_B200_E_INVALID;
+            }
+            bt.page_table[i] = paged->page_tables[i];
         }
         bt.k[i] = s.k;
         bt.v[i] = s.v;
@@ -311,6 +329,31 @@ int argus_b200_attention_gen_batched(argus_b200_ctx* ctx, void* stream, const fl
                                      int kv_dtype, const argus_b200_decode_extras* extras) {
     return argus::decode_f16_entry(reinterpret_cast<Context*>(ctx), static_cast<cudaStream_t>(stream), q, seqs, n_seqs,
                                    out, num_heads_q, num_heads_kv, head_dim, kv_dtype, extras);
+}
+
+int argus_b200_attention_gen_paged(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_pool,
+                                   const void* v_pool, const argus_b200_paged_seq* seqs, int n_seqs, float* out,
+                                   int num_heads_q, int num_heads_kv, int head_dim, int page_tokens, int64_t page_stride,
+                                   int64_t head_stride, int64_t pos_stride, const argus_b200_decode_extras* extras) {
+    Context* c = reinterpret_cast<Context*>(ctx);
+    if (!c) return ARGUS_B200_E_INVALID;
+    if (!seqs || n_seqs <= 0 || n_seqs > argus::kMaxBatch) {
+        c->set_error("attention_gen_paged: null sequence table or more than %d sequences", argus::kMaxBatch);
+        return ARGUS_B200_E_INVALID;
+    }
+    argus_b200_seq flat[argus::kMaxBatch];
+    const int32_t* tables[argus::kMaxBatch];
+    for (int i = 0; i < n_seqs; ++i) {
+        flat[i].k = k_pool;
+        flat[i].v = v_pool;
+        flat[i].seq_len = seqs[i].seq_len;
+        flat[i].head_stride = head_stride;
+        flat[i].pos_stride = pos_stride;
+        tables[i] = seqs[i].page_table;
+    }
+    argus::PagedInfo pg{tables, page_tokens, page_stride};
+    return argus::decode_f16_entry(c, static_cast<cudaStream_t>(stream), q, flat, n_seqs, out, num_heads_q, num_heads_kv,
+                                   head_dim, ARGUS_B200_KV_F16, extras, &pg);
 }
 
 int argus_b200_attention_gen(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_cache,

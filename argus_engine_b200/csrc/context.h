@@ -27,8 +27,14 @@ struct Context {
 };
 
 // context.cu: the body of argus_b200_attention_gen[_batched]
+struct PagedInfo {   // paged form: seqs[i].k / .v are the page pools, strides address a row inside a page
+    const int32_t* const* page_tables;   // host array of n_seqs device pointers
+    int page_tokens;
+    int64_t page_stride;
+};
 int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_seq* seqs, int n_seqs, float* out,
-                     int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex);
+                     int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex,
+                     const PagedInfo* paged = nullptr);
 
 // cudaFuncSetAttribute applies to the current device only, so the "already raised" memo of a kernel's dynamic
 // shared-memory limit is kept per device (a process may hold one context per GPU).

@@ -36,7 +36,7 @@ struct DecodeF16Cfg {
     static constexpr int CTA_TOK = WARPS * WT;    // tokens consumed per CTA sweep
 };
 
-template <int D, int WARPS, int STAGES>
+template <int D, int WARPS, int STAGES, bool PAGED = false>
 __global__ void __launch_bounds__(WARPS * 32, 2)
 decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant__ DecodeBatch bt) {
     using Cfg = DecodeF16Cfg<D, WARPS, STAGES>;
@@ -67,16 +67,22 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
     const int64_t pos_stride = bt.pos_stride[b];
     const uint32_t wsm = smem_u32(smem) + warp * STAGES * STAGE_B;
 
-    auto issue = [&](int j, int slot) {
+    // Paged cache: a warp tile (16 tokens from a multiple of 16) lies inside one page. The page number of a tile is
+    // loaded one iteration before the tile is issued, so that the lookup never sits in front of the copies.
+    const int32_t* ptab = PAGED ? bt.page_table[b] : nullptr;
+    const int P = PAGED ? bt.page_tokens : 1;
+    auto page_of = [&](int j) -> int { return __ldg(ptab + (t0 + (warp + j * WARPS) * WT) / P); };
+    auto issue = [&](int j, int slot, int page) {
         const int tokb = t0 + (warp + j * WARPS) * WT;
         const uint32_t sb = wsm + slot * STAGE_B;
+        const int64_t pbase = PAGED ? (int64_t)page * bt.page_stride - (int64_t)(tokb / P) * P * pos_stride : 0;
 #pragma unroll
         for (int i = 0; i < (WT * CH) / 32; ++i) {
             const int id = lane + 32 * i;
             const int row = id / CH, c = id % CH;
             const int tok = tokb + row;
             const bool ok = tok < t1;
-            const int64_t off = (int64_t)(ok ? tok : t0) * pos_stride + c * 8;
+            const int64_t off = pbase + (int64_t)(ok ? tok : tokb) * pos_stride + c * 8;
             const uint32_t dst = sb + row * ROW_B + ((c ^ (row & 7)) << 4);
             cp_async16(dst, kbase + off, ok);
             cp_async16(dst + TILE_B, vbase + off, ok);
@@ -86,9 +92,10 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
     // ── prologue: start the ring, then fetch q while the copies fly ──
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < my_tiles) issue(s, s);
+        if (s < my_tiles) issue(s, s, PAGED ? page_of(s) : 0);
         cp_async_commit();
     }
+    int page_next = (PAGED && STAGES - 1 < my_tiles) ? page_of(STAGES - 1) : 0;
 
     // A-operand fragments of q*scale*log2(e): rows 0..7 = F16 rounding, rows 8..15 = residual.
     const int head = kv * p.group + quad;          // query head of this lane's MMA row
@@ -132,8 +139,9 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
         __syncwarp();
         {
             const int jn = j + STAGES - 1;
-            if (jn < my_tiles) issue(jn, jn % STAGES);
+            if (jn < my_tiles) issue(jn, jn % STAGES, page_next);
             cp_async_commit();
+            if (PAGED && jn + 1 < my_tiles) page_next = page_of(jn + 1);
         }
         const uint32_t sb = wsm + (j % STAGES) * STAGE_B;
         const int tokb = t0 + (warp + j * WARPS) * WT;
@@ -239,11 +247,11 @@ __global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_const
 }
 
 // ── host-side launchers ──
-template <int D, int WARPS, int STAGES>
+template <int D, int WARPS, int STAGES, bool PAGED = false>
 static cudaError_t launch_decode_f16_t(const DecodeParams& p, const DecodeBatch& bt, int n_items, cudaStream_t st) {
     using Cfg = DecodeF16Cfg<D, WARPS, STAGES>;
     static bool attr_done[kMaxDevices] = {};
-    auto kern = decode_f16_kernel<D, WARPS, STAGES>;
+    auto kern = decode_f16_kernel<D, WARPS, STAGES, PAGED>;
     cudaError_t ea = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::SMEM_B, attr_done);
     if (ea != cudaSuccess) return ea;
     kern<<<n_items * p.hkv, WARPS * 32, Cfg::SMEM_B, st>>>(p, bt);
@@ -253,6 +261,11 @@ static cudaError_t launch_decode_f16_t(const DecodeParams& p, const DecodeBatch&
 int decode_f16_cta_tokens(int head_dim) { return head_dim == 64 ? DecodeF16Cfg<64, 4, 4>::CTA_TOK : DecodeF16Cfg<128, 4, 3>::CTA_TOK; }
 
 cudaError_t launch_decode_f16(const DecodeParams& p, const DecodeBatch& bt, int head_dim, int n_items, cudaStream_t st) {
+    if (bt.page_tokens > 0) {
+        if (head_dim == 128) return launch_decode_f16_t<128, 4, 3, true>(p, bt, n_items, st);
+        if (head_dim == 64) return launch_decode_f16_t<64, 4, 4, true>(p, bt, n_items, st);
+        return cudaErrorInvalidValue;
+    }
     if (head_dim == 128) return launch_decode_f16_t<128, 4, 3>(p, bt, n_items, st);
     if (head_dim == 64) return launch_decode_f16_t<64, 4, 4>(p, bt, n_items, st);
     return cudaErrorInvalidValue;

@@ -20,6 +20,11 @@ struct DecodeBatch {
     int32_t seq_len[kMaxBatch];
     int32_t chunk[kMaxBatch];           // tokens per split of this sequence (multiple of 16)
     int32_t item_start[kMaxBatch + 1];  // prefix sum of splits per sequence
+    // Paged caches (page_tokens > 0): k/v point at page pools; token t of sequence b lives in page
+    // page_table[b][t / page_tokens] at row t % page_tokens: base + page*page_stride + head*head_stride + row*pos_stride.
+    const int32_t* page_table[kMaxBatch];
+    int64_t page_stride;                // elements
+    int32_t page_tokens;                // multiple of 16, so that a 16-token warp tile never straddles two pages
 };
 
 // KIVI-packed sequences. Splits [0, n_qsplits[b]) of sequence b cover chunk_groups[b] 32-token groups of the

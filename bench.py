@@ -300,6 +300,40 @@ def other_configs(be, peaks, which):
         med, _ = _time_events(lambda: be.d2o_nearest(k, ev, rt), 5)
         kvres["d2o_nearest_4096x8192"] = {"ms": med, "pair_dots_per_s": ne * nr / med * 1e3,
                                           "note": "1024-channel sequential-order F32 dot products (bit-exact index selection)"}
+        del k, v
+        # paged layout option: configs[1]'s tokens in a shuffled pool of 256-token pages, same kernel with a page lookup
+        case = wl.config2()
+        ptok = 256
+        npg = [(t + ptok - 1) // ptok for t in case.lens]
+        order = torch.randperm(sum(npg), generator=cpu)
+        pools = []
+        for _ in range(2):   # two pools alternate so that a step does not find the other step's pages in L2
+            pools.append((torch.zeros(sum(npg), 8, ptok, 128, device="cuda", dtype=torch.float16),
+                          torch.zeros(sum(npg), 8, ptok, 128, device="cuda", dtype=torch.float16)))
+        tables, nxt = [], 0
+        for i, t in enumerate(case.lens):
+            ids = order[nxt:nxt + npg[i]]
+            nxt += npg[i]
+            kd_, vd_ = dev(case.k[i]), dev(case.v[i])
+            for j, pg in enumerate(ids.tolist()):
+                lo, hi = j * ptok, min((j + 1) * ptok, t)
+                for kp, vp in pools:
+                    kp[pg, :, :hi - lo] = kd_[:, lo:hi]
+                    vp[pg, :, :hi - lo] = vd_[:, lo:hi]
+            tables.append(ids.to(torch.int32).cuda())
+        qd = dev(case.q)
+        outp = torch.zeros(len(case.lens), 32, 128, device="cuda")
+        flip = [0]
+
+        def paged_step():
+            kp, vp = pools[flip[0] & 1]
+            flip[0] += 1
+            be.attention_gen_paged(qd, kp, vp, tables, case.lens, outp, 32)
+
+        med, _ = _time_events(paged_step, 50)
+        nbytes = decode_bytes(case)
+        kvres["paged_decode_c2_256_token_pages"] = {"us_per_layer_step": med * 1e3, "achieved_gbs": nbytes / med / 1e6,
+                                                    "frac_of_hbm_peak": nbytes / med / 1e6 / peaks["hbm_gbs"]}
         res["kv_executors"] = kvres
     return res
 

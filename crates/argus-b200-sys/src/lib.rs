@@ -22,6 +22,13 @@ pub struct ArgusB200Seq {
     pub pos_stride: i64,
 }
 
+/// `argus_b200_paged_seq`: one sequence of a paged decode call.
+#[repr(C)]
+pub struct ArgusB200PagedSeq {
+    pub page_table: *const i32,
+    pub seq_len: i64,
+}
+
 #[repr(C)]
 pub struct ArgusB200Ctx {
     _private: [u8; 0],
@@ -60,6 +67,12 @@ extern "C" {
         kv_dtype: c_int, num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, seq_len: c_int, cache_seq_len: c_int,
         head_stride: i64, pos_stride: i64, q_start_pos: c_int, q_window: c_int, window: c_int, sum_out: *mut f32,
         per_row: *mut f32, per_row_per_head: c_int,
+    ) -> c_int;
+    pub fn argus_b200_attention_gen_paged(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, k_pool: *const c_void, v_pool: *const c_void,
+        seqs: *const ArgusB200PagedSeq, n_seqs: c_int, out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int,
+        head_dim: c_int, page_tokens: c_int, page_stride: i64, head_stride: i64, pos_stride: i64,
+        extras: *const ArgusB200DecodeExtras,
     ) -> c_int;
     pub fn argus_b200_kv_scatter(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, k_src: *const f32, v_src: *const f32, k_dst: *mut c_void,

@@ -113,6 +113,24 @@ ARGUS_B200_API int argus_b200_attention_gen_batched(argus_b200_ctx* ctx, void* s
                                      int num_heads_q, int num_heads_kv, int head_dim, int kv_dtype,
                                      const argus_b200_decode_extras* extras);
 
+/* The same over PAGED F16 caches (the paged layout option of a KVCacheFormat for batched serving; no counterpart in
+ * the reference, whose caches are contiguous per sequence): K and V live in page pools; token t of sequence b is row
+ * t % page_tokens of page seqs[b].page_table[t / page_tokens], and element (page, kv_head, row, c) sits at
+ * pool + page*page_stride + kv_head*head_stride + row*pos_stride + c (strides in elements, multiples of 8; a page
+ * laid out [Hkv][page_tokens][D] has head_stride = page_tokens*D, pos_stride = D, page_stride = Hkv*page_tokens*D).
+ * page_tokens is a multiple of 16. `seqs` is a HOST array read during the call, the page tables are DEVICE arrays of
+ * ceil(seq_len / page_tokens) page numbers. Same outputs, extras and split plan as argus_b200_attention_gen_batched:
+ * for the same tokens the results are bit-identical to the contiguous form. */
+typedef struct argus_b200_paged_seq {
+    const int32_t* page_table;
+    int64_t seq_len;
+} argus_b200_paged_seq;
+ARGUS_B200_API int argus_b200_attention_gen_paged(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_pool,
+                                                  const void* v_pool, const argus_b200_paged_seq* seqs, int n_seqs,
+                                                  float* out, int num_heads_q, int num_heads_kv, int head_dim,
+                                                  int page_tokens, int64_t page_stride, int64_t head_stride,
+                                                  int64_t pos_stride, const argus_b200_decode_extras* extras);
+
 /* ───────────── KIVI capability: CudaQuantAttnBackend (crates/argus-extension-api/src/lib.rs:3087-3104) ─────────────
  * The four structs below are byte-for-byte the #[repr(C)] PODs of the reference (same field order and
  * types; usize = size_t, u64 device pointers, bool = uint8_t); the Rust FFI crate passes them through

@@ -171,3 +171,45 @@ def test_argument_errors(be):
     with pytest.raises(ArgusB200Error) as e:   # 8 query heads over 3 KV heads
         be.attention_gen(q, k, k, torch.zeros_like(q), 8, 3, 64, 16)
     assert e.value.code == -1
+
+
+@pytest.mark.parametrize("d,page_tokens", [(128, 16), (128, 256), (64, 64)])
+def test_paged_cache_is_bit_identical_to_contiguous(be, d, page_tokens):
+    """Paged layout option: the same tokens scattered over a shuffled page pool give the same bits as the contiguous
+    caches (same split plan, same tile order), outputs and fused score vectors alike, and match the oracle."""
+    from argus_engine_b200 import DecodeExtras
+
+    lens = [5000, 333, 16, 4097, 1]
+    hq, hkv = 16, 4
+    case = wl.decode_case(77 + d, lens, hq, hkv, d)
+    B, stride = len(lens), 5008
+    ks, vs = [_dev(k) for k in case.k], [_dev(v) for v in case.v]
+    out_c = torch.zeros(B, hq, d, device="cuda")
+    ex_c = DecodeExtras(head_scores=torch.zeros(B, hkv, stride, device="cuda"), score_stride=stride)
+    be.attention_gen_batched(_dev(case.q), ks, vs, lens, out_c, hq, hkv, d, extras=ex_c)
+    # pool: every sequence's pages land at random places of one pool
+    n_pages = sum((t + page_tokens - 1) // page_tokens for t in lens)
+    rng = np.random.default_rng(5)
+    perm = rng.permutation(n_pages + 3)
+    k_pool = torch.zeros(n_pages + 3, hkv, page_tokens, d, device="cuda", dtype=torch.float16)
+    v_pool = torch.zeros_like(k_pool)
+    tables, nxt = [], 0
+    for i, t in enumerate(lens):
+        npg = (t + page_tokens - 1) // page_tokens
+        ids = perm[nxt:nxt + npg]
+        nxt += npg
+        for j, pg in enumerate(ids):
+            lo, hi = j * page_tokens, min((j + 1) * page_tokens, t)
+            k_pool[pg, :, :hi - lo] = ks[i][:, lo:hi]
+            v_pool[pg, :, :hi - lo] = vs[i][:, lo:hi]
+        tables.append(torch.from_numpy(ids.astype(np.int32)).cuda())
+    out_p = torch.full((B, hq, d), float("nan"), device="cuda")
+    ex_p = DecodeExtras(head_scores=torch.zeros(B, hkv, stride, device="cuda"), score_stride=stride)
+    be.attention_gen_paged(_dev(case.q), k_pool, v_pool, tables, lens, out_p, hq, extras=ex_p)
+    torch.cuda.synchronize()
+    assert be.check_status() == 0
+    assert torch.equal(out_p, out_c)
+    assert torch.equal(ex_p.head_scores, ex_c.head_scores)
+    for i in range(B):
+        want, _ = _oracle(case, i)
+        np.testing.assert_allclose(out_p[i].cpu().numpy(), want, atol=OUT_ATOL, rtol=OUT_RTOL)
