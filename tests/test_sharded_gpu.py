@@ -86,3 +86,37 @@ def test_two_process_nccl():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "SHARDED_OK" in r.stdout
+
+
+def test_exchange_wait_runs_out_when_a_rank_never_pushes():
+    """Failure detection without a fault: rank 1 never pushes, so rank 0's wait for rank 1's flags reaches its iteration
+    limit; the kernel returns, the status word reads 3, the unmerged heads are zero and the context stays usable."""
+    from argus_engine_b200 import B200Backend
+
+    be = B200Backend(0)
+    N, hq, d = 2, 4, 128
+    plen = hq * d + hq
+    bufs = [torch.zeros(2 * N * plen + 2 * N * hq, device="cuda") for _ in range(N)]
+    peer_parts = [b.data_ptr() for b in bufs]
+    peer_flags = [b.data_ptr() + 4 * 2 * N * plen for b in bufs]
+    part = torch.randn(plen, device="cuda")
+    out = torch.full((hq, d), float("nan"), device="cuda")
+    be.exchange_merge(part, peer_parts, peer_flags, 0, hq, d, out, step=1, parts_parity_stride=N * plen,
+                      flags_parity_stride=N * hq, phases=1)          # rank 0 pushes ...
+    be.exchange_merge(part, peer_parts, peer_flags, 0, hq, d, out, step=1, parts_parity_stride=N * plen,
+                      flags_parity_stride=N * hq, phases=2)          # ... and waits for a rank 1 that never comes
+    assert be.check_status() == 3
+    assert torch.count_nonzero(out) == 0
+    # the context and the device are fine: a complete exchange on the next step works
+    want = torch.zeros(hq, d, device="cuda")
+    parts = torch.stack([part, part])
+    be.lse_merge(parts, hq, d, want)
+    for r in range(N):
+        be.exchange_merge(part, peer_parts, peer_flags, r, hq, d, out, step=2, parts_parity_stride=N * plen,
+                          flags_parity_stride=N * hq, phases=1)
+    be.exchange_merge(part, peer_parts, peer_flags, 0, hq, d, out, step=2, parts_parity_stride=N * plen,
+                      flags_parity_stride=N * hq, phases=2)
+    torch.cuda.synchronize()
+    assert be.check_status() == 0
+    assert torch.allclose(out, want, atol=1e-6, rtol=1e-6)
+    be.close()
