@@ -170,8 +170,8 @@ extern "C" int argus_b200_prefill_attention_scores(argus_b200_ctx* c, void* stre
                        "cache_seq_len %d", q_start_pos, seq_len, cache_seq_len);
         return ARGUS_B200_E_INVALID;
     }
-    if (window > 0 || kv_dtype != ARGUS_B200_KV_F16) {
-        ctx->set_error("prefill_attention_scores: sliding windows and F32 caches are not handled here");
+    if (kv_dtype != ARGUS_B200_KV_F16) {
+        ctx->set_error("prefill_attention_scores: F32 caches are not handled here");
         return ARGUS_B200_E_UNSUPPORTED;
     }
     const int qwin = std::min(q_window, seq_len);
@@ -186,6 +186,9 @@ extern "C" int argus_b200_prefill_attention_scores(argus_b200_ctx* c, void* stre
     const size_t out_bytes_per_row = (size_t)num_heads_q * head_dim * sizeof(float);
     const size_t budget = ctx->ws_bytes / 2;
     int rows_per_pass = std::min(qwin, kMaxBatch);
+    // Sliding window (lo = p - (w-1) > 0 for some row): the rows start at different keys, so each row is its own call on
+    // a cache pointer moved to its first key, with its probabilities landing at offset lo of its score row.
+    if (window > 0) rows_per_pass = 1;
     if (!direct) rows_per_pass = (int)std::min<size_t>(rows_per_pass, budget / (row_bytes + out_bytes_per_row));
     if (rows_per_pass < 1) {
         ctx->set_error("prefill_attention_scores: scratch of %zu bytes cannot stage one row of %zu bytes", ctx->ws_bytes, row_bytes);
@@ -210,16 +213,21 @@ extern "C" int argus_b200_prefill_attention_scores(argus_b200_ctx* c, void* stre
             if (e != cudaSuccess) return ctx->cuda_fail(e, "prefill_attention_scores memset");
         }
         argus_b200_seq seqs[kMaxBatch];
+        int64_t lo = 0;   // first visible key (sliding window; one row per pass then)
+        if (window > 0) {
+            const int64_t pos = (int64_t)q_start_pos + qwin_start + r0;
+            lo = std::max<int64_t>(0, pos - (window - 1));
+        }
         for (int i = 0; i < nb; ++i) {
-            seqs[i].k = k_cache;
-            seqs[i].v = v_cache;
-            seqs[i].seq_len = (int64_t)q_start_pos + qwin_start + r0 + i + 1;
+            seqs[i].k = static_cast<const __half*>(k_cache) + lo * pos_stride;
+            seqs[i].v = static_cast<const __half*>(v_cache) + lo * pos_stride;
+            seqs[i].seq_len = (int64_t)q_start_pos + qwin_start + r0 + i + 1 - lo;
             seqs[i].head_stride = head_stride;
             seqs[i].pos_stride = pos_stride;
         }
         argus_b200_decode_extras ex;
         memset(&ex, 0, sizeof(ex));
-        ex.scores = rows;
+        ex.scores = rows + lo;
         ex.score_stride = prefix;
         int rc = decode_f16_entry(ctx, st, q + (size_t)(qwin_start + r0) * num_heads_q * head_dim, seqs, nb, out_buf,
                                   num_heads_q, num_heads_kv, head_dim, kv_dtype, &ex);

@@ -356,15 +356,15 @@ ARGUS_B200_API int argus_b200_d2o_nearest(argus_b200_ctx* ctx, void* stream, con
 /* prefill_attention_scores (engine/src/kv/standard_format.rs:1400-1510; the H2O prefill seed, CPU-only in the
  * reference, which reads K back from the device for it): for the trailing min(q_window, seq_len) query rows of a
  * prefill chunk, row r at absolute position p = q_start_pos + r, the softmax probabilities of every query head over
- * keys 0..=p (scale 1/sqrt(head_dim), GQA head h reads KV head h / (Hq/Hkv)).
+ * keys lo..=p (scale 1/sqrt(head_dim), GQA head h reads KV head h / (Hq/Hkv)); lo = 0, or max(0, p - (window-1))
+ * with a sliding window (`window` > 0).
  *   q        [seq_len][Hq][D] F32 (device), the chunk's queries
  *   sum_out  [Hq][cache_seq_len] += sum over the rows (nullable)                      -- IMP-2
  *   per_row  per_row_per_head != 0: [q_window][Hq][cache_seq_len] = the row's probabilities;
  *            per_row_per_head == 0: [q_window][cache_seq_len] += mean over heads (nullable) -- IMP-4
  * As in the reference the caller zeroes the buffers first and entries behind a row's position are not written.
  * Within the decode tolerance of the reference (its own test is bit-exact against a scalar loop; a GPU softmax is
- * not), accumulation orders as the reference's. A sliding window (`window` > 0) and F32 caches are declined
- * (ARGUS_B200_E_UNSUPPORTED). K and V are addressed as in argus_b200_attention_gen; V is read by the decode
+ * not), accumulation orders as the reference's. F32 caches are declined (ARGUS_B200_E_UNSUPPORTED). K and V are addressed as in argus_b200_attention_gen; V is read by the decode
  * kernel this call is built on. */
 ARGUS_B200_API int argus_b200_prefill_attention_scores(argus_b200_ctx* ctx, void* stream, const float* q,
                                                        const void* k_cache, const void* v_cache, int kv_dtype,

@@ -178,12 +178,28 @@ def test_prefill_attention_scores_vs_reference_restatement(be, hq, hkv, d, S, q_
     assert orc.keep_top_k(T, 2, 4, heavy, flat) == orc.keep_top_k(T, 2, 4, heavy, want_sum.sum(0)) or T < 16
 
 
-def test_prefill_attention_scores_declines_window(be):
-    q = torch.zeros(4, 4, 64, device="cuda")
-    k = torch.zeros(4, 16, 64, device="cuda", dtype=torch.float16)
-    s = torch.zeros(4, 4, device="cuda")
-    with pytest.raises(RuntimeError):
-        be.prefill_attention_scores(q, k, k, 4, 0, 2, sum_out=s, window=3)
+@pytest.mark.parametrize("window", [4, 64, 1000])
+def test_prefill_attention_scores_sliding_window(be, window):
+    """Sliding-window band (engine/src/kv/standard_format.rs:1455-1461): row at position p sees keys
+    max(0, p - (w-1))..=p; keys outside a row's band stay zero."""
+    rng = np.random.default_rng(window)
+    hq, hkv, d, S, q_start, qw = 8, 2, 128, 70, 130, 16
+    T = q_start + S
+    q = (rng.standard_normal((S, hq, d)) * 0.8).astype(np.float32)
+    k = rng.standard_normal((hkv, T + 8, d)).astype(np.float16)
+    v = rng.standard_normal((hkv, T + 8, d)).astype(np.float16)
+    want_sum, want_rows, want_mean = orc.prefill_attention_scores(q, k, hkv, q_start, qw, T, window)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    sum_out = torch.zeros(hq, T, device="cuda")
+    rows = torch.zeros(qw, hq, T, device="cuda")
+    be.prefill_attention_scores(dev(q), dev(k), dev(v), T, q_start, qw, sum_out=sum_out, per_row=rows, window=window)
+    mean = torch.zeros(qw, T, device="cuda")
+    be.prefill_attention_scores(dev(q), dev(k), dev(v), T, q_start, qw, per_row=mean, per_row_per_head=False, window=window)
+    assert be.check_status() == 0
+    np.testing.assert_allclose(rows.cpu().numpy(), want_rows, atol=1e-7, rtol=1e-2)
+    np.testing.assert_allclose(sum_out.cpu().numpy(), want_sum, atol=1e-6, rtol=1e-2)
+    np.testing.assert_allclose(mean.cpu().numpy(), want_mean, atol=1e-7, rtol=1e-2)
+    assert (rows.cpu().numpy() != 0).sum() == (want_rows != 0).sum()   # nothing written outside the bands
 
 
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
