@@ -109,6 +109,8 @@ cudaError_t launch_lse_merge(const float* parts, int n_parts, long long part_str
 // decode_kivi.cu
 cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int head_dim, int bits, int n_items,
                                cudaStream_t st);
+int decode_kivi_ctas_per_sm(int head_dim, int bits);
+int decode_kivi_plan_slots_per_sm(int head_dim, int bits);
 // decode_kivi_tc.cu: Q4, head_dim 128, tcgen05 form; packed splits are planned in tiles of 4 groups, one CTA per SM
 cudaError_t launch_decode_kivi_tc(const DecodeParams& p, const KiviBatch& bt, int n_items, cudaStream_t st);
 

@@ -95,14 +95,20 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
 
     // Packed part: the same proportional planner as the F16 path, in tokens, then expressed in 32-token groups.
     int32_t chunk[kMaxBatch], nsplit[kMaxBatch];
-    const int waves = 1;
+    // About 5/3 of the resident CTA slots (3 per SM for the Q4 head_dim-128 instantiation, 2 otherwise): planning 2 per
+    // SM where 3 are resident left a third of the slots empty, and somewhat more CTAs than slots lets the block scheduler
+    // even out the tail (185 -> 144 us on the benchmark shape). ARGUS_B200_KIVI_WAVES / _SLOTS override for experiments.
+    const char* w_s = getenv("ARGUS_B200_KIVI_WAVES");
+    const char* sl_s = getenv("ARGUS_B200_KIVI_SLOTS");
+    const int waves = (w_s && *w_s) ? std::max(1, atoi(w_s)) : 1;
+    const int slots_per_sm = (sl_s && *sl_s) ? std::max(1, atoi(sl_s)) : decode_kivi_plan_slots_per_sm(d, bits);
     // Q4 at head_dim 128 has a second kernel, the tcgen05 form (one CTA per SM, tiles of 4 groups), selected by
     // ARGUS_B200_KIVI_TC=1. The mma.sync kernel stays the default: measured on the benchmark shape it is ~10 % faster.
     const char* tc_s = getenv("ARGUS_B200_KIVI_TC");   // read per call: tests switch between the two kernels
     const int tc_env = (tc_s && *tc_s) ? atoi(tc_s) : 0;
     const bool use_tc = tc_env != 0 && bits == 4 && d == 128 && res_aligned;
     if (use_tc) plan_splits(qlens, n_seqs, hkv, ctx->num_sms, waves, 4 * 32 * 2, chunk, nsplit);
-    else plan_splits(qlens, n_seqs, hkv, ctx->num_sms * 2, waves, 4 * 32 * 2, chunk, nsplit);
+    else plan_splits(qlens, n_seqs, hkv, ctx->num_sms * slots_per_sm, waves, 4 * 32 * 2, chunk, nsplit);
     int items = 0;
     for (int i = 0; i < n_seqs; ++i) {
         const int groups = (int)(qlens[i] / 32);

@@ -145,8 +145,8 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                 qreg[h][e] = (h < p.group) ? p.q[((int64_t)b * p.hq + kv * p.group + h) * D + lane * EPL + e] * p.scale_log2 : 0.f;
             }
         }
-        for (int r = r0 + warp; r < r1; r += WARPS) {
-            float kr[EPL], vr[EPL];
+        // two tokens per step, both rows requested before either is used: the loop is bound by the latency of its loads
+        auto load_row = [&](int r, float (&kr)[EPL], float (&vr)[EPL]) {
             const int64_t off = ((int64_t)kv * bt.res_cap + r) * D + lane * EPL;
             if (bt.res_is_f16) {
 #pragma unroll
@@ -161,6 +161,8 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                     vr[e] = static_cast<const float*>(bt.res_v[b])[off + e];
                 }
             }
+        };
+        auto token = [&](int r, const float (&kr)[EPL], const float (&vr)[EPL]) {
 #pragma unroll
             for (int h = 0; h < kMaxGroup; ++h) {
                 if (h >= p.group) break;
@@ -179,6 +181,14 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
 #pragma unroll
                 for (int e = 0; e < EPL; ++e) oacc[h][e] = oacc[h][e] * alpha + pr * vr[e];
             }
+        };
+        for (int r = r0 + warp; r < r1; r += 2 * WARPS) {
+            float ka[EPL], va[EPL], kb[EPL], vb[EPL];
+            const bool two = r + WARPS < r1;
+            load_row(r, ka, va);
+            load_row(two ? r + WARPS : r, kb, vb);
+            token(r, ka, va);
+            if (two) token(r + WARPS, kb, vb);
         }
 #pragma unroll
         for (int h = 0; h < kMaxGroup; ++h) {
@@ -418,11 +428,24 @@ static cudaError_t launch_kivi_t(const DecodeParams& p, const KiviBatch& bt, int
     return cudaGetLastError();
 }
 
+static int kivi_q4_variant() {
+    static const int variant = getenv("ARGUS_B200_KIVI_VARIANT") ? atoi(getenv("ARGUS_B200_KIVI_VARIANT")) : 0;
+    return variant;
+}
+
+// CTAs of the selected instantiation that are resident per SM: the split planner fills exactly one such wave.
+int decode_kivi_ctas_per_sm(int head_dim, int bits) { return (head_dim == 128 && bits == 4 && kivi_q4_variant() != 1) ? 3 : 2; }
+
+// CTA slots per SM the split planner fills. More CTAs than are resident, so that the block scheduler hands out the
+// tail: measured on B=8 x 32K tokens, Q4 (3 resident): 2 -> 185 us, 3 -> 154, 5 -> 144, 8 -> 144; Q8 (2 resident):
+// 2 -> 191, 3 -> 152, 4 -> 154.
+int decode_kivi_plan_slots_per_sm(int head_dim, int bits) { return decode_kivi_ctas_per_sm(head_dim, bits) == 3 ? 5 : 3; }
+
 cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int head_dim, int bits, int n_items,
                                cudaStream_t st) {
     if (head_dim == 128) {
         if (bits == 4) {
-            static const int variant = getenv("ARGUS_B200_KIVI_VARIANT") ? atoi(getenv("ARGUS_B200_KIVI_VARIANT")) : 0;
+            const int variant = kivi_q4_variant();
             if (variant == 1) return launch_kivi_t<128, 4, 4, 4>(p, bt, n_items, st);
             return launch_kivi_t<128, 4, 4, 3, 3>(p, bt, n_items, st);   // 3 CTAs per SM: +17 % over 2 CTAs of 4 stages
         }
