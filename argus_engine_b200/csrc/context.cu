@@ -158,7 +158,8 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
     const int waves = env_int("ARGUS_B200_DECODE_WAVES", 1);
     const int min_chunk = env_int("ARGUS_B200_DECODE_MIN_CHUNK", 2 * decode_f16_cta_tokens(d));
     int32_t nsplit[kMaxBatch];
-    plan_splits(lens, n_seqs, hkv, ctx->num_sms * 2, waves, min_chunk, bt.chunk, nsplit);
+    const int slots_per_sm = env_int("ARGUS_B200_DECODE_SLOTS", 2);
+    plan_splits(lens, n_seqs, hkv, ctx->num_sms * slots_per_sm, waves, min_chunk, bt.chunk, nsplit);
     int items = 0;
     for (int i = 0; i < n_seqs; ++i) {
         bt.item_start[i] = items;
