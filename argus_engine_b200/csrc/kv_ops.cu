@@ -128,12 +128,12 @@ __global__ void __launch_bounds__(256) kv_compact_kernel(uint4* __restrict__ cac
                                                          int* status) {
     const bool direct = (long long)keep[i0] - (write_start + i0) >= n_rows;   // the same answer in every thread
     if (direct && !first) return;
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long total = n_rows * n_heads * row_vecs;
-    if (idx >= total) return;
-    const int v = (int)(idx % row_vecs);
-    const long long r = (idx / row_vecs) % n_rows;
-    const int hh = (int)(idx / ((long long)row_vecs * n_rows));
+    // blockIdx.y = head of the pass; a chunk has at most 32768 rows, so 32-bit index arithmetic is enough
+    const unsigned t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (unsigned)n_rows * (unsigned)row_vecs) return;
+    const unsigned r = t / (unsigned)row_vecs;
+    const int v = (int)(t - r * (unsigned)row_vecs);
+    const int hh = (int)blockIdx.y;
     const long long i = i0 + r;
     const long long src = keep[i], dst = write_start + i;
     if (src == dst) return;
@@ -152,9 +152,10 @@ cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, 
                                    long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
                                    long long pos_stride_bytes, int first, int* status, cudaStream_t st) {
     const int row_vecs = row_bytes / 16;
-    const long long total = n_rows * n_heads * row_vecs;
-    if (total <= 0) return cudaSuccess;
-    kv_compact_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+    const long long per_head = n_rows * row_vecs;
+    if (per_head <= 0 || n_heads <= 0) return cudaSuccess;
+    if (per_head > 0x7fffffffLL || n_heads > 65535) return cudaErrorInvalidValue;
+    kv_compact_kernel<<<dim3((unsigned)((per_head + 255) / 256), (unsigned)n_heads), 256, 0, st>>>(
         static_cast<uint4*>(cache), static_cast<uint4*>(scratch), keep, i0, n_rows, write_start, head0, n_heads, row_vecs,
         head_stride_bytes / 16, pos_stride_bytes / 16, first, status);
     return cudaGetLastError();
