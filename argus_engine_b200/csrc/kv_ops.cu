@@ -235,11 +235,98 @@ __global__ void __launch_bounds__(128) kv_weighted_merge_kernel(T* __restrict__ 
     }
 }
 
+// The same merge with four channels per thread and all KV heads of a merge in one CTA (thread = (head, 4 channels)):
+// the list of a merge is read once per CTA and rows move as 8- or 16-byte vectors. Per element the products and
+// sums are the ones above, in the same order. Needs d, the strides and the base addresses to be multiples of 4
+// elements.
+template <typename T>
+struct Vec4;
+template <>
+struct Vec4<float> {
+    float4 raw;
+    __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = raw; }
+    __device__ __forceinline__ void get(float (&x)[4]) const { x[0] = raw.x; x[1] = raw.y; x[2] = raw.z; x[3] = raw.w; }
+    __device__ __forceinline__ void set(const float (&x)[4]) { raw = make_float4(x[0], x[1], x[2], x[3]); }
+};
+template <>
+struct Vec4<__half> {
+    uint2 raw;
+    __device__ __forceinline__ void load(const __half* p) { raw = *reinterpret_cast<const uint2*>(p); }
+    __device__ __forceinline__ void store(__half* p) const { *reinterpret_cast<uint2*>(p) = raw; }
+    __device__ __forceinline__ void get(float (&x)[4]) const {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+    }
+    __device__ __forceinline__ void set(const float (&x)[4]) {
+        const __half2 a = __halves2half2(__float2half_rn(x[0]), __float2half_rn(x[1]));
+        const __half2 b = __halves2half2(__float2half_rn(x[2]), __float2half_rn(x[3]));
+        raw.x = *reinterpret_cast<const uint32_t*>(&a);
+        raw.y = *reinterpret_cast<const uint32_t*>(&b);
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) kv_weighted_merge_vec_kernel(T* __restrict__ k, T* __restrict__ v, int d, int hkv,
+                                                                    long long head_stride, long long pos_stride,
+                                                                    const int* __restrict__ into_pos,
+                                                                    const float* __restrict__ into_w,
+                                                                    const int* __restrict__ from_start,
+                                                                    const int* __restrict__ from_pos,
+                                                                    const float* __restrict__ from_w, int do_k, int do_v) {
+    const int m = blockIdx.x;
+    const int f0 = from_start[m], f1 = from_start[m + 1];
+    if (f1 <= f0) return;   // an empty `from` list leaves the row untouched
+    const long long ipos = into_pos[m];
+    const float iw = into_w[m];
+    const int vecs = d >> 2;
+    for (int t = threadIdx.x; t < hkv * vecs; t += blockDim.x) {
+        const int h = t / vecs, c = (t - h * vecs) << 2;
+        const long long base = (long long)h * head_stride + c;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            if (which == 0 ? !do_k : !do_v) continue;
+            T* buf = which == 0 ? k : v;
+            Vec4<T> x;
+            float acc[4], val[4];
+            x.load(buf + base + ipos * pos_stride);
+            x.get(val);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = __fmul_rn(iw, val[e]);
+            for (int j = f0; j < f1; ++j) {
+                const float w = from_w[j];
+                x.load(buf + base + (long long)from_pos[j] * pos_stride);
+                x.get(val);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] = __fadd_rn(acc[e], __fmul_rn(w, val[e]));
+            }
+            x.set(acc);
+            x.store(buf + base + ipos * pos_stride);
+        }
+    }
+}
+
 cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d, long long head_stride,
                                      long long pos_stride, const int* into_pos, const float* into_w, const int* from_start,
                                      const int* from_pos, const float* from_w, int n_merges, int do_k, int do_v,
                                      cudaStream_t st) {
     if (n_merges <= 0) return cudaSuccess;
+    const size_t vec_bytes = f16 ? 8 : 16;
+    const bool vec_ok = (d % 4 == 0) && (head_stride % 4 == 0) && (pos_stride % 4 == 0) &&
+                        (!do_k || reinterpret_cast<uintptr_t>(k) % vec_bytes == 0) &&
+                        (!do_v || reinterpret_cast<uintptr_t>(v) % vec_bytes == 0);
+    if (vec_ok) {
+        if (f16)
+            kv_weighted_merge_vec_kernel<__half><<<(unsigned)n_merges, 256, 0, st>>>(
+                static_cast<__half*>(k), static_cast<__half*>(v), d, hkv, head_stride, pos_stride, into_pos, into_w, from_start,
+                from_pos, from_w, do_k, do_v);
+        else
+            kv_weighted_merge_vec_kernel<float><<<(unsigned)n_merges, 256, 0, st>>>(
+                static_cast<float*>(k), static_cast<float*>(v), d, hkv, head_stride, pos_stride, into_pos, into_w, from_start,
+                from_pos, from_w, do_k, do_v);
+        return cudaGetLastError();
+    }
     const dim3 grid((unsigned)n_merges, (unsigned)hkv);
     if (f16)
         kv_weighted_merge_kernel<__half><<<grid, 128, 0, st>>>(static_cast<__half*>(k), static_cast<__half*>(v), d,

@@ -114,9 +114,10 @@ def test_kv_compact_in_chunks_and_edge_lists(be):
 
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
 @pytest.mark.parametrize("axis", [0, 1, 2])
-def test_kv_weighted_merge_bit_exact(be, dtype, axis):
+@pytest.mark.parametrize("d", [128, 66])   # 66: not a multiple of 4 channels, the one-channel-per-thread kernel
+def test_kv_weighted_merge_bit_exact(be, dtype, axis, d):
     rng = np.random.default_rng(axis + 40)
-    hkv, cap, d = 8, 700, 128
+    hkv, cap = 8, 700
     k, v = _cache(rng, hkv, cap, d, dtype)
     pos = rng.permutation(cap)
     merges, used = [], 0
