@@ -21,36 +21,36 @@ __global__ void __launch_bounds__(256) kv_scatter_kernel(const float* __restrict
                                                          void* __restrict__ k_dst, void* __restrict__ v_dst, int hkv, int d,
                                                          long long head_stride, long long pos_stride, long long write_pos,
                                                          long long seq_len) {
-    const int vec_per_row = d / 4;   // four channels per thread
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long total = seq_len * hkv * vec_per_row;
-    if (idx >= total) return;
-    const int c = (int)(idx % vec_per_row) * 4;
-    const long long row = idx / vec_per_row;   // = s * hkv + h: the source is [seq][Hkv][D]
-    const long long h = row % hkv, s = row / hkv;
-    const long long so = row * d + c;
-    const long long dof = h * head_stride + (write_pos + s) * pos_stride + c;
-    const float4 kx = *reinterpret_cast<const float4*>(k_src + so);
-    const float4 vx = *reinterpret_cast<const float4*>(v_src + so);
-    if constexpr (DST_F16) {
-        __half2 ka = __floats2half2_rn(kx.x, kx.y), kb = __floats2half2_rn(kx.z, kx.w);
-        __half2 va = __floats2half2_rn(vx.x, vx.y), vb = __floats2half2_rn(vx.z, vx.w);
-        *reinterpret_cast<uint2*>(static_cast<__half*>(k_dst) + dof) =
-            make_uint2(*reinterpret_cast<uint32_t*>(&ka), *reinterpret_cast<uint32_t*>(&kb));
-        *reinterpret_cast<uint2*>(static_cast<__half*>(v_dst) + dof) =
-            make_uint2(*reinterpret_cast<uint32_t*>(&va), *reinterpret_cast<uint32_t*>(&vb));
-    } else {
-        *reinterpret_cast<float4*>(static_cast<float*>(k_dst) + dof) = kx;
-        *reinterpret_cast<float4*>(static_cast<float*>(v_dst) + dof) = vx;
+    // CTA = one source row block [Hkv][D] (position s); thread = (head, four channels)
+    const int vec_per_row = d / 4;
+    const long long s = blockIdx.x;
+    if (s >= seq_len) return;
+    for (int t = threadIdx.x; t < hkv * vec_per_row; t += blockDim.x) {
+        const int h = t / vec_per_row, c = (t - h * vec_per_row) * 4;
+        const long long so = (s * hkv + h) * d + c;
+        const long long dof = h * head_stride + (write_pos + s) * pos_stride + c;
+        const float4 kx = *reinterpret_cast<const float4*>(k_src + so);
+        const float4 vx = *reinterpret_cast<const float4*>(v_src + so);
+        if constexpr (DST_F16) {
+            __half2 ka = __floats2half2_rn(kx.x, kx.y), kb = __floats2half2_rn(kx.z, kx.w);
+            __half2 va = __floats2half2_rn(vx.x, vx.y), vb = __floats2half2_rn(vx.z, vx.w);
+            *reinterpret_cast<uint2*>(static_cast<__half*>(k_dst) + dof) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&ka), *reinterpret_cast<uint32_t*>(&kb));
+            *reinterpret_cast<uint2*>(static_cast<__half*>(v_dst) + dof) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&va), *reinterpret_cast<uint32_t*>(&vb));
+        } else {
+            *reinterpret_cast<float4*>(static_cast<float*>(k_dst) + dof) = kx;
+            *reinterpret_cast<float4*>(static_cast<float*>(v_dst) + dof) = vx;
+        }
     }
 }
 
 cudaError_t launch_kv_scatter(const float* k_src, const float* v_src, void* k_dst, void* v_dst, bool dst_f16, int hkv,
                               int d, long long head_stride, long long pos_stride, long long write_pos, long long seq_len,
                               cudaStream_t st) {
-    const long long total = seq_len * hkv * (d / 4);
-    if (total <= 0) return cudaSuccess;
-    const unsigned grid = (unsigned)((total + 255) / 256);
+    if (seq_len <= 0 || hkv <= 0 || d < 4) return cudaSuccess;
+    if (seq_len > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const unsigned grid = (unsigned)seq_len;
     if (dst_f16)
         kv_scatter_kernel<true><<<grid, 256, 0, st>>>(k_src, v_src, k_dst, v_dst, hkv, d, head_stride, pos_stride, write_pos, seq_len);
     else
