@@ -349,7 +349,7 @@ namespace argus {
 // list order on ties, never the evicted position itself. The reference accumulates dot and the two squared norms
 // over the Hkv*D channels in order, one rounding per product and per sum; the kernels below do exactly that (so the
 // similarities and therefore the selected indices are bit-identical): the norms once per listed row, the dot
-// products in 32 x 32 tiles of (evicted, retained) pairs, 2 x 2 pairs per thread, channels in ascending order.
+// products in 64 x 64 tiles of (evicted, retained) pairs, 4 x 4 pairs per thread, channels in ascending order.
 template <typename T>
 __global__ void __launch_bounds__(128) d2o_norms_kernel(const T* __restrict__ k, long long head_stride, long long pos_stride,
                                                         int hkv, int d, const int* __restrict__ evict, int n_evict,
@@ -381,44 +381,53 @@ __global__ void __launch_bounds__(256) d2o_pairs_kernel(const T* __restrict__ k,
                                                         int hkv, int d, const int* __restrict__ evict, int n_evict,
                                                         const int* __restrict__ retain, int n_retain,
                                                         const float* __restrict__ norms, unsigned long long* __restrict__ best) {
-    __shared__ float sa[32][33], sb[32][33];
-    __shared__ int pa[32], pb[32];
+    // 64 x 64 pairs per CTA, 4 x 4 per thread; a 32-channel chunk of the 128 rows sits in shared memory channel-major,
+    // so a thread fetches its four rows of either side with one 16-byte load per channel.
+    constexpr int TP = 64, LD = TP + 4;
+    __shared__ __align__(16) float sa[32][LD], sb[32][LD];
+    __shared__ int pa[TP], pb[TP];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-    const int e0 = blockIdx.y * 32, r0 = blockIdx.x * 32;
-    if (threadIdx.x < 32) pa[threadIdx.x] = e0 + threadIdx.x < n_evict ? evict[e0 + threadIdx.x] : -1;
-    else if (threadIdx.x < 64) pb[threadIdx.x - 32] = r0 + threadIdx.x - 32 < n_retain ? retain[r0 + threadIdx.x - 32] : -1;
+    const int e0 = blockIdx.y * TP, r0 = blockIdx.x * TP;
+    if (threadIdx.x < TP) pa[threadIdx.x] = e0 + threadIdx.x < n_evict ? evict[e0 + threadIdx.x] : -1;
+    else if (threadIdx.x < 2 * TP) pb[threadIdx.x - TP] = r0 + threadIdx.x - TP < n_retain ? retain[r0 + threadIdx.x - TP] : -1;
     __syncthreads();
-    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
     const int dim = hkv * d;
     for (int g0 = 0; g0 < dim; g0 += 32) {
-        // 64 rows x 32 channels of this chunk -> shared memory as F32 (d is a multiple of 32: a chunk stays in one head)
+        // 128 rows x 32 channels of this chunk -> shared memory as F32 (d is a multiple of 32: a chunk stays in one head)
         const int h = g0 / d, c0 = g0 % d;
-        for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+        for (int e = threadIdx.x; e < 2 * TP * 32; e += 256) {
             const int r = e >> 5, c = e & 31;
-            const int pos = r < 32 ? pa[r] : pb[r - 32];
+            const int pos = r < TP ? pa[r] : pb[r - TP];
             const float x = pos >= 0 ? load_f32(k + h * head_stride + (long long)pos * pos_stride + c0 + c) : 0.f;
-            if (r < 32) sa[r][c] = x;
-            else sb[r - 32][c] = x;
+            if (r < TP) sa[c][r] = x;
+            else sb[c][r - TP] = x;
         }
         __syncthreads();
-#pragma unroll 8
+#pragma unroll 4
         for (int c = 0; c < 32; ++c) {
-            const float a0 = sa[2 * ty][c], a1 = sa[2 * ty + 1][c], b0 = sb[2 * tx][c], b1 = sb[2 * tx + 1][c];
-            acc[0][0] = __fadd_rn(acc[0][0], __fmul_rn(a0, b0));
-            acc[0][1] = __fadd_rn(acc[0][1], __fmul_rn(a0, b1));
-            acc[1][0] = __fadd_rn(acc[1][0], __fmul_rn(a1, b0));
-            acc[1][1] = __fadd_rn(acc[1][1], __fmul_rn(a1, b1));
+            const float4 a4 = *reinterpret_cast<const float4*>(&sa[c][4 * ty]);
+            const float4 b4 = *reinterpret_cast<const float4*>(&sb[c][4 * tx]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int ei = e0 + 2 * ty + i;
+    for (int i = 0; i < 4; ++i) {
+        const int ei = e0 + 4 * ty + i;
         unsigned long long key = 0;   // 0 = no candidate
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int ri = r0 + 2 * tx + j;
-            if (ei < n_evict && ri < n_retain && pb[2 * tx + j] != pa[2 * ty + i]) {
+        for (int j = 0; j < 4; ++j) {
+            const int ri = r0 + 4 * tx + j;
+            if (ei < n_evict && ri < n_retain && pb[4 * tx + j] != pa[4 * ty + i]) {
                 const float denom = __fsqrt_rn(__fmul_rn(norms[ei], norms[n_evict + ri]));
                 const float sim = denom < 1e-10f ? 0.f : __fdiv_rn(acc[i][j], denom);
                 if (sim == sim && sim != -INFINITY) {   // NaN and -inf never beat the reference's initial -inf
@@ -461,7 +470,7 @@ cudaError_t launch_d2o_nearest(const void* k, bool f16, long long head_stride, l
     cudaError_t e = cudaMemsetAsync(best, 0, (size_t)n_evict * sizeof(unsigned long long), st);
     if (e != cudaSuccess) return e;
     const int rows = n_evict + n_retain;
-    const dim3 grid((unsigned)((n_retain + 31) / 32), (unsigned)((n_evict + 31) / 32));
+    const dim3 grid((unsigned)((n_retain + 63) / 64), (unsigned)((n_evict + 63) / 64));
     if (f16) {
         d2o_norms_kernel<__half><<<(rows + 127) / 128, 128, 0, st>>>(static_cast<const __half*>(k), head_stride, pos_stride, hkv,
                                                                      d, evict, n_evict, retain, n_retain, norms);
