@@ -7,28 +7,30 @@
 
 namespace argus {
 
+// Block = (d/4 threads along a row) x (rows); blockIdx.y = KV head: no index division.
 __global__ void __launch_bounds__(256) kv_f32_to_f16_kernel(const float* __restrict__ src, __half* __restrict__ dst,
-                                                            int hkv, long long T, int d, long long head_stride,
+                                                            long long T, int d, long long head_stride,
                                                             long long pos_stride) {
-    const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;   // 4 channels per thread
-    const long long total = (long long)hkv * T * d;
-    if (idx >= total) return;
-    const int c = (int)(idx % d);
-    const long long row = idx / d;
-    const long long t = row % T, h = row / T;
+    const long long t = (long long)blockIdx.x * blockDim.y + threadIdx.y;
+    if (t >= T) return;
+    const int c = threadIdx.x * 4;   // 4 channels per thread
+    const long long h = blockIdx.y;
     const float4 v = *reinterpret_cast<const float4*>(src + h * head_stride + t * pos_stride + c);
-    __half2* o = reinterpret_cast<__half2*>(dst + idx);
+    __half2* o = reinterpret_cast<__half2*>(dst + (h * T + t) * d + c);
     o[0] = __floats2half2_rn(v.x, v.y);
     o[1] = __floats2half2_rn(v.z, v.w);
 }
 
 cudaError_t launch_kv_f32_to_f16(const float* src, void* dst, int hkv, long long T, int d, long long head_stride,
                                  long long pos_stride, cudaStream_t st) {
-    const long long total = (long long)hkv * T * d;
-    if (total <= 0) return cudaSuccess;
-    const long long threads = total / 4;
-    kv_f32_to_f16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(src, static_cast<__half*>(dst), hkv, T, d,
-                                                                          head_stride, pos_stride);
+    if (hkv <= 0 || T <= 0 || d <= 0) return cudaSuccess;
+    const int vpr = d / 4;
+    if (d % 4 != 0 || vpr > 256 || hkv > 65535) return cudaErrorInvalidValue;
+    const int rows = 256 / vpr;
+    const long long blocks = (T + rows - 1) / rows;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+    kv_f32_to_f16_kernel<<<dim3((unsigned)blocks, (unsigned)hkv), dim3((unsigned)vpr, (unsigned)rows), 0, st>>>(
+        src, static_cast<__half*>(dst), T, d, head_stride, pos_stride);
     return cudaGetLastError();
 }
 
