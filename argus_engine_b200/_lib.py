@@ -60,6 +60,13 @@ class KiviSeq(C.Structure):
                 ("q_tokens", C.c_int64), ("res_tokens", C.c_int64)]
 
 
+class ExchangeC(C.Structure):
+    """argus_b200_exchange."""
+    _fields_ = [("peer_parts", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)), ("step_counters", C.c_void_p),
+                ("merged_lse", C.c_void_p), ("parts_parity_stride", C.c_int64), ("flags_parity_stride", C.c_int64),
+                ("n_ranks", C.c_int), ("rank", C.c_int), ("phases", C.c_int)]
+
+
 class ScoreReduceArgs(C.Structure):
     """CudaScoreReduceArgs (crates/argus-extension-api/src/lib.rs:2909-2933)."""
     _fields_ = [("cu_stream", C.c_void_p), ("score_buf", C.c_uint64), ("importance", C.c_uint64),
@@ -92,6 +99,10 @@ def load_library() -> C.CDLL:
                                              C.POINTER(DecodeExtrasC)]
     lib.argus_b200_attention_gen_batched.argtypes = [vp, vp, vp, C.POINTER(Seq), i32, vp, i32, i32, i32, i32,
                                                      C.POINTER(DecodeExtrasC)]
+    lib.argus_b200_decode_step_batched.argtypes = [vp, vp, vp, vp, vp, C.POINTER(Seq), C.POINTER(i64), i32, vp, i32, i32, i32, i32,
+                                                   C.POINTER(DecodeExtrasC)]
+    lib.argus_b200_decode_step.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i32, i64, i64,
+                                           C.POINTER(DecodeExtrasC)]
     lib.argus_b200_kivi_has_quant_attn_kernel.argtypes = [vp, i32]
     lib.argus_b200_kivi_attention_gen_quant.argtypes = [vp, C.POINTER(QuantAttnArgs)]
     lib.argus_b200_kivi_gather_update_quant.argtypes = [vp, C.POINTER(QuantGatherArgs)]
@@ -108,13 +119,15 @@ def load_library() -> C.CDLL:
     lib.argus_b200_exchange_merge.argtypes = [vp, vp, vp, C.POINTER(vp), C.POINTER(vp), i32, i32, i32, vp, i64, i64, i32, i32,
                                               vp, vp, i32]
     lib.argus_b200_step_increment.argtypes = [vp, vp, vp]
+    lib.argus_b200_attention_gen_sharded.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64,
+                                                     C.POINTER(ExchangeC)]
     lib.argus_b200_kv_scatter.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64]
     lib.argus_b200_prefill_attention_scores.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i64, i32, i32, i32,
                                                         vp, vp, i32]
     lib.argus_b200_kv_scatter_batched.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]
     lib.argus_b200_d2o_nearest.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, vp, i32, vp, i32, vp, vp]
     lib.argus_b200_attention_gen_paged.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i64, i64, i64, vp]
-    lib.argus_b200_kv_compact.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, i64, i64, i32]
+    lib.argus_b200_kv_compact.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, i64, i64, i32]
     lib.argus_b200_kv_weighted_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, vp, vp, vp, vp, i32, i32]
     lib.argus_b200_attention_gen_static.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64]
     lib.argus_b200_static_scratch_bytes.restype = C.c_size_t

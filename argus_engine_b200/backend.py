@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from ._lib import (ArgusB200Error, DecodeExtrasC, KiviSeq, QuantAttnArgs, QuantDequantFlushArgs, QuantGatherArgs,
+from ._lib import (ArgusB200Error, DecodeExtrasC, ExchangeC, KiviSeq, QuantAttnArgs, QuantDequantFlushArgs, QuantGatherArgs,
                    QuantScatterResidualArgs, PagedSeq, ScoreReduceArgs, Seq, load_library)
 
 KV_F32, KV_F16 = 0, 1
@@ -128,6 +128,31 @@ class B200Backend:
         self._check(self._lib.argus_b200_attention_gen_batched(
             self._h, self._stream(), q.data_ptr(), arr, n, out.data_ptr(), num_heads_q, num_heads_kv, head_dim, dt,
             self._extras(extras)))
+
+    def decode_step_batched(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_caches, v_caches, write_pos,
+                            out: torch.Tensor, num_heads_q: int, num_heads_kv: int, head_dim: int,
+                            extras: Optional[DecodeExtras] = None) -> None:
+        """KV write + attention of one decode step in one call. k_new/v_new [B, Hkv, D] F32 are stored at position
+        write_pos[b] (the sequence's length before the step) of cache b [Hkv, cap, D]; the attention covers
+        write_pos[b] + 1 positions. q/out [B, Hq, D]."""
+        n = len(k_caches)
+        arr = (Seq * n)()
+        cap = (C.c_int64 * n)()
+        for i in range(n):
+            hs, ps, _ = self.kv_strides(k_caches[i], num_heads_kv)
+            arr[i] = Seq(k_caches[i].data_ptr(), v_caches[i].data_ptr(), int(write_pos[i]), hs, ps)
+            cap[i] = k_caches[i].shape[-2] if k_caches[i].dim() >= 3 and k_caches[i].shape[-3] == num_heads_kv else k_caches[i].shape[0]
+        dt = KV_F16 if k_caches[0].dtype == torch.float16 else KV_F32
+        self._check(self._lib.argus_b200_decode_step_batched(
+            self._h, self._stream(), q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), arr, cap, n, out.data_ptr(), num_heads_q,
+            num_heads_kv, head_dim, dt, self._extras(extras)))
+
+    def decode_step(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor,
+                    v_cache: torch.Tensor, out: torch.Tensor, num_heads_q: int, num_heads_kv: int, head_dim: int,
+                    cache_seq_len: int, extras: Optional[DecodeExtras] = None) -> None:
+        """Single-sequence form: k_new/v_new [Hkv, D] F32 written at position cache_seq_len, attention over cache_seq_len+1."""
+        self.decode_step_batched(q, k_new, v_new, [k_cache], [v_cache], [cache_seq_len], out, num_heads_q, num_heads_kv,
+                                 head_dim, extras)
 
     def attention_gen_paged(self, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_tables, seq_lens,
                             out: torch.Tensor, num_heads_q: int, extras: Optional[DecodeExtras] = None) -> None:
@@ -251,6 +276,24 @@ class B200Backend:
             self._h, self._stream(), local_part.data_ptr(), pp, pf, n, rank, step, _ptr(step_dev), parts_parity_stride,
             flags_parity_stride, num_heads_q, head_dim, out.data_ptr(), _ptr(lse_out), phases))
 
+    def attention_gen_sharded(self, q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
+                              num_heads_q: int, num_heads_kv: int, head_dim: int, shard_len: int, peer_parts, peer_flags,
+                              rank: int, step_counters: torch.Tensor, parts_parity_stride: int, flags_parity_stride: int,
+                              merged_lse: Optional[torch.Tensor] = None, phases: int = 3) -> None:
+        """One launch per step of a sequence-sharded decode: split-KV decode over this rank's K/V slice whose epilogue
+        pushes the (o, lse) partial to every rank and merges. peer_parts / peer_flags: device addresses (ints), one per
+        rank; step_counters: int32 device tensor [Hkv], zero before the first step."""
+        n = len(peer_parts)
+        pp = (C.c_void_p * n)(*peer_parts)
+        pf = (C.c_void_p * n)(*peer_flags)
+        xc = ExchangeC(pp, pf, step_counters.data_ptr(), _ptr(merged_lse), parts_parity_stride, flags_parity_stride, n, rank,
+                       phases)
+        hs, ps, _ = self.kv_strides(k_shard, num_heads_kv)
+        dt = KV_F16 if k_shard.dtype == torch.float16 else KV_F32
+        self._check(self._lib.argus_b200_attention_gen_sharded(
+            self._h, self._stream(), q.data_ptr(), k_shard.data_ptr(), v_shard.data_ptr(), out.data_ptr(), num_heads_q,
+            num_heads_kv, head_dim, shard_len, dt, hs, ps, C.byref(xc)))
+
     def step_increment(self, step_dev: torch.Tensor) -> None:
         self._check(self._lib.argus_b200_step_increment(self._h, self._stream(), step_dev.data_ptr()))
 
@@ -292,8 +335,8 @@ class B200Backend:
         if keep.dtype != torch.int32 or not keep.is_cuda:
             raise ValueError("keep must be an int32 device tensor")
         self._check(self._lib.argus_b200_kv_compact(self._h, self._stream(), k_cache.data_ptr(), v_cache.data_ptr(), dt,
-                                                    k_cache.shape[0], k_cache.shape[2], hs, ps, keep.data_ptr(),
-                                                    keep.numel(), write_start, head))
+                                                    k_cache.shape[0], k_cache.shape[2], k_cache.shape[1], hs, ps,
+                                                    keep.data_ptr(), keep.numel(), write_start, head))
 
     def kv_weighted_merge(self, k_cache: torch.Tensor, v_cache: torch.Tensor, into_pos: torch.Tensor,
                           into_weight: torch.Tensor, from_start: torch.Tensor, from_pos: torch.Tensor,

@@ -76,14 +76,14 @@ void plan_splits(const int64_t* lens, int n, int hkv, int slots, int waves, int 
     }
 }
 
-static int env_int(const char* name, int dflt) {
+int env_int(const char* name, int dflt) {
     const char* s = getenv(name);
     return (s && *s) ? atoi(s) : dflt;
 }
 
 int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_seq* seqs, int n_seqs,
                      float* out, int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex,
-                     const PagedInfo* paged) {
+                     const PagedInfo* paged, const argus_b200_exchange* xc, const float* k_new, const float* v_new) {
     if (!ctx) return ARGUS_B200_E_INVALID;
     ctx->err[0] = 0;
     if (!q || !seqs || !out || n_seqs <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || d <= 0) {
@@ -155,10 +155,25 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
         return ARGUS_B200_E_INVALID;
     }
 
-    const int waves = env_int("ARGUS_B200_DECODE_WAVES", 1);
-    const int min_chunk = env_int("ARGUS_B200_DECODE_MIN_CHUNK", 2 * decode_f16_cta_tokens(d));
+    if (xc) {
+        // sequence-sharded form: one sequence, the (o, lse) partial goes to the peers from inside the kernel
+        if (n_seqs != 1 || paged || want_scores || (hq & 3) || xc->n_ranks <= 0 || xc->n_ranks > kMaxRanks || xc->rank < 0 ||
+            xc->rank >= xc->n_ranks || !xc->peer_parts || !xc->peer_flags || !xc->step_counters || (xc->phases & 3) == 0 ||
+            (xc->parts_parity_stride & 3) || (xc->flags_parity_stride < 0)) {
+            ctx->set_error("attention_gen_sharded: one contiguous sequence, Hq a multiple of 4, no score outputs, 1..%d ranks "
+                           "and parity strides that are multiples of 4 are required", kMaxRanks);
+            return ARGUS_B200_E_INVALID;
+        }
+        for (int s = 0; s < xc->n_ranks; ++s)
+            if (!xc->peer_parts[s] || !xc->peer_flags[s] || (reinterpret_cast<uintptr_t>(xc->peer_parts[s]) & 15)) {
+                ctx->set_error("attention_gen_sharded: receive buffer of rank %d is null or not 16-byte aligned", s);
+                return ARGUS_B200_E_INVALID;
+            }
+    }
+    const int waves = ctx->opt.decode_waves > 0 ? ctx->opt.decode_waves : 1;
+    const int min_chunk = ctx->opt.decode_min_chunk > 0 ? ctx->opt.decode_min_chunk : 2 * decode_f16_cta_tokens(d);
     int32_t nsplit[kMaxBatch];
-    const int slots_per_sm = env_int("ARGUS_B200_DECODE_SLOTS", 2);
+    const int slots_per_sm = ctx->opt.decode_slots > 0 ? ctx->opt.decode_slots : 2;
     plan_splits(lens, n_seqs, hkv, ctx->num_sms * slots_per_sm, waves, min_chunk, bt.chunk, nsplit);
     int items = 0;
     for (int i = 0; i < n_seqs; ++i) {
@@ -235,6 +250,21 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
     p.logit_stride = logit_stride;
     p.lse2 = lse2;
     p.status = ctx->status;
+    p.k_new = k_new;   // F16 contiguous caches only; the callers route the other cases through the KV write kernel
+    p.v_new = v_new;
+    if (xc) {
+        for (int s = 0; s < xc->n_ranks; ++s) {
+            p.xc.parts[s] = xc->peer_parts[s];
+            p.xc.flags[s] = xc->peer_flags[s];
+        }
+        p.xc.step_ctr = xc->step_counters;
+        p.xc.merged_lse = xc->merged_lse;
+        p.xc.parts_parity_stride = xc->parts_parity_stride;
+        p.xc.flags_parity_stride = xc->flags_parity_stride;
+        p.xc.n_ranks = xc->n_ranks;
+        p.xc.rank = xc->rank;
+        p.xc.phases = xc->phases & 3;
+    }
 
     cudaError_t e = launch_decode_f16(p, bt, d, items, st);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "decode_f16 launch");
@@ -291,6 +321,12 @@ int argus_b200_create(int device, size_t workspace_bytes, argus_b200_ctx** out) 
     c->device = device;
     c->num_sms = prop.multiProcessorCount;
     c->ws_bytes = workspace_bytes ? workspace_bytes : (size_t(64) << 20);
+    c->opt.decode_waves = argus::env_int("ARGUS_B200_DECODE_WAVES", 0);
+    c->opt.decode_min_chunk = argus::env_int("ARGUS_B200_DECODE_MIN_CHUNK", 0);
+    c->opt.decode_slots = argus::env_int("ARGUS_B200_DECODE_SLOTS", 0);
+    c->opt.kivi_waves = argus::env_int("ARGUS_B200_KIVI_WAVES", 0);
+    c->opt.kivi_slots = argus::env_int("ARGUS_B200_KIVI_SLOTS", 0);
+    c->opt.prefill_bf16_p = argus::env_int("ARGUS_B200_PREFILL_BF16_P", 2);
     c->n_tickets = 4096;
     e = cudaMalloc(&c->ws, c->ws_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->tickets, c->n_tickets * sizeof(int));
@@ -355,6 +391,76 @@ int argus_b200_attention_gen_paged(argus_b200_ctx* ctx, void* stream, const floa
     argus::PagedInfo pg{tables, page_tokens, page_stride};
     return argus::decode_f16_entry(c, static_cast<cudaStream_t>(stream), q, flat, n_seqs, out, num_heads_q, num_heads_kv,
                                    head_dim, ARGUS_B200_KV_F16, extras, &pg);
+}
+
+// Decode step = write the new token's K/V row, then attend over the sequence including it: what the engine's decode
+// layer does back to back (engine/src/layers/transformer_layer/forward_gen_fmt.rs:207,267-275). For F16 caches the
+// write happens inside the decode kernel (one launch); F32 caches take the KV write kernel first (two launches).
+int argus_b200_decode_step_batched(argus_b200_ctx* ctx, void* stream, const float* q, const float* k_new,
+                                   const float* v_new, const argus_b200_seq* seqs, const int64_t* capacity, int n_seqs,
+                                   float* out, int num_heads_q, int num_heads_kv, int head_dim, int kv_dtype,
+                                   const argus_b200_decode_extras* extras) {
+    Context* c = reinterpret_cast<Context*>(ctx);
+    if (!c) return ARGUS_B200_E_INVALID;
+    c->err[0] = 0;
+    if (!k_new || !v_new || !seqs || !capacity || n_seqs <= 0 || n_seqs > argus::kMaxBatch ||
+        ((reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new)) & 15)) {
+        c->set_error("decode_step: null or misaligned new rows, or more than %d sequences", argus::kMaxBatch);
+        return ARGUS_B200_E_INVALID;
+    }
+    argus_b200_seq after[argus::kMaxBatch];
+    for (int i = 0; i < n_seqs; ++i) {
+        if (!seqs[i].k || !seqs[i].v || seqs[i].seq_len < 0 || seqs[i].seq_len >= capacity[i]) {
+            c->set_error("decode_step: sequence %d: null cache or write position %lld outside capacity %lld", i,
+                         (long long)seqs[i].seq_len, (long long)capacity[i]);
+            return ARGUS_B200_E_INVALID;
+        }
+        after[i] = seqs[i];
+        after[i].seq_len = seqs[i].seq_len + 1;
+    }
+    if (kv_dtype != ARGUS_B200_KV_F16) {
+        const int rc = argus_b200_kv_scatter_batched(ctx, stream, k_new, v_new, seqs, capacity, n_seqs, kv_dtype, num_heads_kv,
+                                                     head_dim);
+        if (rc != ARGUS_B200_OK) return rc;
+        return argus::decode_f16_entry(c, static_cast<cudaStream_t>(stream), q, after, n_seqs, out, num_heads_q, num_heads_kv,
+                                       head_dim, kv_dtype, extras);
+    }
+    return argus::decode_f16_entry(c, static_cast<cudaStream_t>(stream), q, after, n_seqs, out, num_heads_q, num_heads_kv,
+                                   head_dim, kv_dtype, extras, nullptr, nullptr, k_new, v_new);
+}
+
+int argus_b200_decode_step(argus_b200_ctx* ctx, void* stream, const float* q, const float* k_new, const float* v_new,
+                           void* k_cache, void* v_cache, float* out, int num_heads_q, int num_heads_kv, int head_dim,
+                           int64_t cache_seq_len, int64_t capacity, int kv_dtype, int64_t head_stride, int64_t pos_stride,
+                           const argus_b200_decode_extras* extras) {
+    argus_b200_seq s;
+    s.k = k_cache;
+    s.v = v_cache;
+    s.seq_len = cache_seq_len;
+    s.head_stride = head_stride;
+    s.pos_stride = pos_stride;
+    return argus_b200_decode_step_batched(ctx, stream, q, k_new, v_new, &s, &capacity, 1, out, num_heads_q, num_heads_kv,
+                                          head_dim, kv_dtype, extras);
+}
+
+int argus_b200_attention_gen_sharded(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_shard,
+                                     const void* v_shard, float* out, int num_heads_q, int num_heads_kv, int head_dim,
+                                     int64_t shard_len, int kv_dtype, int64_t head_stride, int64_t pos_stride,
+                                     const argus_b200_exchange* exchange) {
+    Context* c = reinterpret_cast<Context*>(ctx);
+    if (!c) return ARGUS_B200_E_INVALID;
+    if (!exchange) {
+        c->set_error("attention_gen_sharded: null exchange descriptor");
+        return ARGUS_B200_E_INVALID;
+    }
+    argus_b200_seq s;
+    s.k = k_shard;
+    s.v = v_shard;
+    s.seq_len = shard_len;
+    s.head_stride = head_stride;
+    s.pos_stride = pos_stride;
+    return argus::decode_f16_entry(c, static_cast<cudaStream_t>(stream), q, &s, 1, out, num_heads_q, num_heads_kv, head_dim,
+                                   kv_dtype, nullptr, nullptr, exchange);
 }
 
 int argus_b200_attention_gen(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_cache,

@@ -20,6 +20,12 @@ struct Context {
     uint64_t launches = 0;
     size_t ws_tail_reserved = 0;   // bytes at the top of `ws` a composite call keeps for itself while it calls an entry
     char err[512] = {0};
+    // Tuning knobs, read from the environment ONCE at argus_b200_create (0 = the built-in choice).
+    struct Options {
+        int decode_waves = 0, decode_min_chunk = 0, decode_slots = 0;   // ARGUS_B200_DECODE_{WAVES,MIN_CHUNK,SLOTS}
+        int kivi_waves = 0, kivi_slots = 0;                             // ARGUS_B200_KIVI_{WAVES,SLOTS}
+        int prefill_bf16_p = 2;                                         // ARGUS_B200_PREFILL_BF16_P
+    } opt;
 
     void set_error(const char* fmt, ...);
     int cuda_fail(cudaError_t e, const char* what);
@@ -34,7 +40,8 @@ struct PagedInfo {   // paged form: seqs[i].k / .v are the page pools, strides a
 };
 int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_seq* seqs, int n_seqs, float* out,
                      int hq, int hkv, int d, int kv_dtype, const argus_b200_decode_extras* ex,
-                     const PagedInfo* paged = nullptr);
+                     const PagedInfo* paged = nullptr, const argus_b200_exchange* xc = nullptr,
+                     const float* k_new = nullptr, const float* v_new = nullptr);
 
 // cudaFuncSetAttribute applies to the current device only, so the "already raised" memo of a kernel's dynamic
 // shared-memory limit is kept per device (a process may hold one context per GPU).
@@ -49,6 +56,7 @@ inline cudaError_t ensure_dynamic_smem(const void* kernel, int bytes, bool (&don
     return e;
 }
 
+int env_int(const char* name, int dflt);
 void plan_splits(const int64_t* lens, int n, int hkv, int slots, int waves, int min_chunk, int32_t* chunk,
                  int32_t* nsplit);
 
@@ -93,7 +101,8 @@ cudaError_t launch_kv_scatter_rows(const float* k_src, const float* v_src, void*
                                    int n, bool dst_f16, int hkv, int d, cudaStream_t st);
 cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, long long i0, long long n_rows,
                                    long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
-                                   long long pos_stride_bytes, int first, int* status, cudaStream_t st);
+                                   long long pos_stride_bytes, int first, long long capacity, int* status,
+                                   cudaStream_t st);
 cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d, long long head_stride,
                                      long long pos_stride, const int* into_pos, const float* into_w, const int* from_start,
                                      const int* from_pos, const float* from_w, int n_merges, int do_k, int do_v,
@@ -102,7 +111,7 @@ cudaError_t launch_d2o_nearest(const void* k, bool f16, long long head_stride, l
                                const int* evict, int n_evict, const int* retain, int n_retain, float* norms,
                                unsigned long long* best, int* nearest, float* sim_out, cudaStream_t st);
 cudaError_t launch_pfa_reduce(const float* rows, float* sum_out, float* mean_out, int n_rows, int hq, long long prefix_len,
-                              cudaStream_t st);
+                              long long row0_pos, int window, cudaStream_t st);
 // lse_merge.cu
 cudaError_t launch_lse_merge(const float* parts, int n_parts, long long part_stride, int hq, int d, float* out,
                              float* lse_out, cudaStream_t st);

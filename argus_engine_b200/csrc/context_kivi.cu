@@ -98,10 +98,8 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
     // About 5/3 of the resident CTA slots (3 per SM for the Q4 head_dim-128 instantiation, 2 otherwise): planning 2 per
     // SM where 3 are resident left a third of the slots empty, and somewhat more CTAs than slots lets the block scheduler
     // even out the tail (185 -> 144 us on the benchmark shape). ARGUS_B200_KIVI_WAVES / _SLOTS override for experiments.
-    const char* w_s = getenv("ARGUS_B200_KIVI_WAVES");
-    const char* sl_s = getenv("ARGUS_B200_KIVI_SLOTS");
-    const int waves = (w_s && *w_s) ? std::max(1, atoi(w_s)) : 1;
-    const int slots_per_sm = (sl_s && *sl_s) ? std::max(1, atoi(sl_s)) : decode_kivi_plan_slots_per_sm(d, bits);
+    const int waves = ctx->opt.kivi_waves > 0 ? ctx->opt.kivi_waves : 1;
+    const int slots_per_sm = ctx->opt.kivi_slots > 0 ? ctx->opt.kivi_slots : decode_kivi_plan_slots_per_sm(d, bits);
     // Q4 at head_dim 128 has a second kernel, the tcgen05 form (one CTA per SM, tiles of 4 groups), selected by
     // ARGUS_B200_KIVI_TC=1. The mma.sync kernel stays the default: measured on the benchmark shape it is ~10 % faster.
     const char* tc_s = getenv("ARGUS_B200_KIVI_TC");   // read per call: tests switch between the two kernels
@@ -381,7 +379,7 @@ int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void* stream, const 
     cudaError_t e = argus::launch_prefill_tc(q16, k_cache, v_cache, out, dtype_mode == ARGUS_B200_PREFILL_BF16,
                                              dtype_mode == ARGUS_B200_PREFILL_F32Q_F16KV, batch_size, seq_len,
                                              cache_seq_len, n_heads_q, n_heads_kv, cache_seq_len, pos_stride, head_stride,
-                                             batch_stride, getenv("ARGUS_B200_PREFILL_BF16_P") ? atoi(getenv("ARGUS_B200_PREFILL_BF16_P")) : 2, c->status, st);
+                                             batch_stride, c->opt.prefill_bf16_p, c->status, st);
     if (e == cudaErrorNotSupported) {
         c->set_error("flash_attention_prefill: the driver does not export cuTensorMapEncodeTiled");
         return ARGUS_B200_E_UNSUPPORTED;

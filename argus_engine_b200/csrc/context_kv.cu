@@ -88,15 +88,16 @@ extern "C" int argus_b200_kv_scatter_batched(argus_b200_ctx* c, void* stream, co
 }
 
 extern "C" int argus_b200_kv_compact(argus_b200_ctx* c, void* stream, void* k, void* v, int kv_dtype, int num_heads_kv,
-                                     int head_dim, int64_t head_stride, int64_t pos_stride, const int32_t* keep_dev,
-                                     int64_t n_keep, int64_t write_start, int head) {
+                                     int head_dim, int64_t capacity, int64_t head_stride, int64_t pos_stride,
+                                     const int32_t* keep_dev, int64_t n_keep, int64_t write_start, int head) {
     Context* ctx = reinterpret_cast<Context*>(c);
     if (!ctx) return ARGUS_B200_E_INVALID;
     ctx->err[0] = 0;
     const int eb = elt_bytes(kv_dtype);
     if (!k || !v || eb < 0 || num_heads_kv <= 0 || head_dim <= 0 || n_keep < 0 || write_start < 0 || head < -1 ||
-        head >= num_heads_kv || (n_keep > 0 && !keep_dev)) {
-        ctx->set_error("kv_compact: null pointer, bad dtype or head index %d (of %d)", head, num_heads_kv);
+        head >= num_heads_kv || (n_keep > 0 && !keep_dev) || capacity <= 0 || write_start + n_keep > capacity) {
+        ctx->set_error("kv_compact: null pointer, bad dtype, head index %d (of %d) or %lld rows from %lld beyond capacity %lld",
+                       head, num_heads_kv, (long long)n_keep, (long long)write_start, (long long)capacity);
         return ARGUS_B200_E_INVALID;
     }
     if (n_keep == 0) return ARGUS_B200_OK;   // compact_keep_positions returns early on an empty list
@@ -120,7 +121,7 @@ extern "C" int argus_b200_kv_compact(argus_b200_ctx* c, void* stream, void* k, v
             void* cache = which == 0 ? k : v;
             for (int first = 1; first >= 0; --first) {
                 cudaError_t e = launch_kv_compact_pass(cache, ctx->ws, keep_dev, i0, n, write_start, head0, n_heads,
-                                                       (int)row_bytes, head_stride * eb, pos_stride * eb, first,
+                                                       (int)row_bytes, head_stride * eb, pos_stride * eb, first, capacity,
                                                        ctx->status, st);
                 if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_compact launch");
                 ctx->launches += 1;
@@ -233,7 +234,8 @@ extern "C" int argus_b200_prefill_attention_scores(argus_b200_ctx* c, void* stre
                                   num_heads_q, num_heads_kv, head_dim, kv_dtype, &ex);
         if (rc != ARGUS_B200_OK) return rc;
         float* mean = (per_row && !per_row_per_head) ? per_row + (size_t)r0 * prefix : nullptr;
-        cudaError_t e = launch_pfa_reduce(rows, sum_out, mean, nb, num_heads_q, prefix, st);
+        cudaError_t e = launch_pfa_reduce(rows, sum_out, mean, nb, num_heads_q, prefix, (long long)q_start_pos + qwin_start + r0,
+                                          window, st);
         if (e != cudaSuccess) return ctx->cuda_fail(e, "prefill_attention_scores reduce launch");
         ctx->launches += (sum_out || mean) ? 1 : 0;
     }

@@ -18,6 +18,95 @@ struct EpilogueSmem {
     static constexpr int BYTES = WARP_MERGE_B > SPLIT_MERGE_B ? WARP_MERGE_B : SPLIT_MERGE_B;
 };
 
+// Flag words of the peer exchange are written and read with release / acquire semantics at system scope.
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Sequence-sharded decode, run by every thread of the CTA that completed KV head `kv` after it has written the head
+// group's normalised rows and their natural-log lse into this rank's OWN slot of its receive buffer:
+//   push  - copy the g rows + lse into slot `rank` of every other rank's receive buffer with plain peer stores (no
+//           multicast, no bulk copy), fence at system scope, then raise flag[rank][head] = step on every rank;
+//   merge - wait, with an iteration limit, for flag[s][head] >= step of every rank s in this rank's own flag array
+//           and merge the n_ranks rows of each head (same algebra as the split merge above, natural-log lse).
+// Only data of this CTA's own heads is waited for, so no CTA of a launch depends on another CTA of the same launch
+// and ranks only depend on pushes, which never wait. A wait that runs out zeroes the heads' output and sets the
+// status word to 3. Requires Hq % 4 == 0 and parity strides that are multiples of 4 (16-byte rows).
+template <int D, int WARPS>
+__device__ __forceinline__ void peer_exchange_tail(const DecodeParams& p, int kv, int step, long long poff, long long foff) {
+    constexpr int NT = WARPS * 32;
+    const PeerExchange& x = p.xc;
+    const int hq = p.hq, g = p.group, h0 = kv * g;
+    const long long part_len = (long long)hq * D + hq;
+    __shared__ int xc_ok;
+    if (threadIdx.x == 0) xc_ok = 1;
+    __syncthreads();   // the rows and lse written by this CTA are visible to all its threads
+    if (x.phases & 1) {
+        const float* own = x.parts[x.rank] + poff + x.rank * part_len;
+        const int n4 = g * D / 4;
+        for (int s = 0; s < x.n_ranks; ++s) {
+            if (s == x.rank) continue;
+            float* dst = x.parts[s] + poff + x.rank * part_len;
+            for (int e = threadIdx.x; e < n4; e += NT)
+                reinterpret_cast<float4*>(dst + (long long)h0 * D)[e] = __ldcg(reinterpret_cast<const float4*>(own + (long long)h0 * D) + e);
+            if (threadIdx.x < g) dst[(long long)hq * D + h0 + threadIdx.x] = __ldcg(own + (long long)hq * D + h0 + threadIdx.x);
+        }
+        __threadfence_system();
+        __syncthreads();
+        for (int i = threadIdx.x; i < x.n_ranks * g; i += NT) {
+            __threadfence_system();
+            st_release_sys(x.flags[i / g] + foff + x.rank * hq + h0 + (i % g), step);
+        }
+    }
+    if (x.phases & 2) {
+        for (int i = threadIdx.x; i < x.n_ranks * g; i += NT) {
+            const int* f = x.flags[x.rank] + foff + (i / g) * hq + h0 + (i % g);
+            bool ok = false;
+            for (int it = 0; it < (1 << 21); ++it) {   // about a second before giving up
+                if (ld_acquire_sys(f) >= step) {
+                    ok = true;
+                    break;
+                }
+                if (it > 2048) __nanosleep(256);
+            }
+            __threadfence_system();
+            if (!ok) {
+                xc_ok = 0;
+                if (p.status != nullptr) atomicExch(p.status, 3);
+            }
+        }
+        __syncthreads();
+        const bool ok_all = xc_ok != 0;
+        const float* parts = x.parts[x.rank] + poff;
+        for (int e = threadIdx.x; e < g * D; e += NT) {
+            const int h = h0 + e / D, c = e % D;
+            float M = -INFINITY;
+            for (int s = 0; s < x.n_ranks; ++s) {
+                const float l = __ldcv(parts + s * part_len + (long long)hq * D + h);
+                if (isfinite(l) && l > M) M = l;
+            }
+            float W = 0.f, acc = 0.f;
+            for (int s = 0; s < x.n_ranks; ++s) {
+                const float l = __ldcv(parts + s * part_len + (long long)hq * D + h);
+                if (isfinite(l)) {
+                    const float w = expf(l - M);
+                    W += w;
+                    acc += w * __ldcv(parts + s * part_len + (long long)h * D + c);
+                }
+            }
+            p.out[(long long)h * D + c] = (ok_all && W > 0.f) ? acc / W : 0.f;
+            if (c == 0 && x.merged_lse != nullptr) x.merged_lse[h] = (ok_all && W > 0.f) ? M + logf(W) : -INFINITY;
+        }
+    }
+    __syncthreads();   // every thread has read the step counter's old value (the caller did) and is done with it
+    if (threadIdx.x == 0) x.step_ctr[kv] = step;
+}
+
 // Precondition: every warp has stored its un-normalised O tile at smem[O_OFF] as [warp][8][D] and its
 // (running max, sum) at smem[ML_OFF] as [warp][8], followed by __syncthreads().
 // item  = index of this CTA's partial, item0 = partial of split 0 of the same (sequence, KV head);
@@ -29,6 +118,21 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
     float* sm_o = reinterpret_cast<float*>(smem + EpilogueSmem<D, WARPS>::O_OFF);
     float2* sm_ml = reinterpret_cast<float2*>(smem + EpilogueSmem<D, WARPS>::ML_OFF);
     int* sm_flag = reinterpret_cast<int*>(smem + EpilogueSmem<D, WARPS>::FLAG_OFF);
+    // Sharded decode: the completing CTA writes the final rows into its own slot of the receive buffer (the buffer set
+    // follows the parity of the step number kept in device memory), then pushes and merges (peer_exchange_tail).
+    const bool xchg = p.xc.n_ranks > 0;
+    float* out_base = p.out;
+    float* lse_base = p.lse;
+    int xc_step = 0;
+    long long xc_poff = 0, xc_foff = 0;
+    auto bind_exchange = [&]() {
+        xc_step = __ldcg(p.xc.step_ctr + kv) + 1;
+        xc_poff = (xc_step & 1) ? p.xc.parts_parity_stride : 0;
+        xc_foff = (xc_step & 1) ? p.xc.flags_parity_stride : 0;
+        out_base = p.xc.parts[p.xc.rank] + xc_poff + p.xc.rank * ((long long)p.hq * D + p.hq);
+        lse_base = out_base + (long long)p.hq * D;
+    };
+    if (xchg && n_splits == 1) bind_exchange();
     for (int e = threadIdx.x; e < p.group * D; e += WARPS * 32) {
         const int h = e / D, d = e % D;
         float M = -INFINITY;
@@ -45,10 +149,10 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
         }
         if (n_splits == 1) {
             const int64_t oh = (int64_t)b * p.hq + kv * p.group + h;
-            p.out[oh * D + d] = (L > 0.f) ? acc / L : 0.f;
+            out_base[oh * D + d] = (L > 0.f) ? acc / L : 0.f;
             if (d == 0) {
                 const float l2 = (L > 0.f) ? M + log2f(L) : -INFINITY;
-                if (p.lse != nullptr) p.lse[oh] = l2 * 0.6931471805599453f;
+                if (lse_base != nullptr) lse_base[oh] = l2 * 0.6931471805599453f;
                 if (p.lse2 != nullptr) p.lse2[oh] = l2;
             }
         } else {
@@ -56,7 +160,10 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
             if (d == 0) p.part_ml[item * 8 + h] = make_float2(M, L);
         }
     }
-    if (n_splits == 1) return;
+    if (n_splits == 1) {
+        if (xchg) peer_exchange_tail<D, WARPS>(p, kv, xc_step, xc_poff, xc_foff);
+        return;
+    }
 
     // ── ticket: the last split of this (sequence, KV head) merges all of them ──
     __threadfence();
@@ -68,6 +175,7 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
     __syncthreads();
     if (*sm_flag == 0) return;
     __threadfence();
+    if (xchg) bind_exchange();
 
     // All (max, sum) pairs of this (sequence, KV head) come into shared memory once; everything else
     // is computed from there. The planner keeps n_splits <= kMaxSplits.
@@ -136,15 +244,16 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
         const float2 ML = sm_ML[h];
         const float inv = (ML.y > 0.f) ? 1.0f / ML.y : 0.f;
         const int64_t oh = (int64_t)b * p.hq + kv * p.group + h;
-        *reinterpret_cast<float4*>(p.out + oh * D + d) =
+        *reinterpret_cast<float4*>(out_base + oh * D + d) =
             make_float4(acc[k].x * inv, acc[k].y * inv, acc[k].z * inv, acc[k].w * inv);
         if (d == 0) {
             const float l2 = (ML.y > 0.f) ? ML.x + log2f(ML.y) : -INFINITY;
-            if (p.lse != nullptr) p.lse[oh] = l2 * 0.6931471805599453f;
+            if (lse_base != nullptr) lse_base[oh] = l2 * 0.6931471805599453f;
             if (p.lse2 != nullptr) p.lse2[oh] = l2;
         }
     }
     if (threadIdx.x == 0) p.tickets[b * p.hkv + kv] = 0;   // ready for the next call
+    if (xchg) peer_exchange_tail<D, WARPS>(p, kv, xc_step, xc_poff, xc_foff);
 }
 
 }  // namespace argus

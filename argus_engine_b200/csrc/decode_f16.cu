@@ -89,6 +89,22 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
         }
     };
 
+    // Decode step: the new token is position T-1. Only the last split reads it, so the CTA of that split rounds the
+    // F32 row to F16 (nearest even, as the engine's KV write kernel does) and stores it before any of its copies is
+    // issued; the barrier orders the store before the other threads' reads of the row.
+    if (!PAGED && p.k_new != nullptr && split == n_splits - 1 && T > 0) {
+        if (threadIdx.x < D / 2) {
+            const int64_t src = ((int64_t)b * p.hkv + kv) * D + 2 * threadIdx.x;
+            const int64_t dst = (int64_t)(T - 1) * pos_stride + 2 * threadIdx.x;
+            const float2 kx = *reinterpret_cast<const float2*>(p.k_new + src);
+            const float2 vx = *reinterpret_cast<const float2*>(p.v_new + src);
+            *reinterpret_cast<__half2*>(const_cast<__half*>(kbase) + dst) = __floats2half2_rn(kx.x, kx.y);
+            *reinterpret_cast<__half2*>(const_cast<__half*>(vbase) + dst) = __floats2half2_rn(vx.x, vx.y);
+        }
+        __threadfence();
+        __syncthreads();
+    }
+
     // ── prologue: start the ring, then fetch q while the copies fly ──
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -165,8 +181,8 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
             for (int i = 0; i < 2; ++i) {
                 const int tok = tokb + n * 8 + qlane * 2 + i;
                 float x = c[n][i] + c[n][i + 2];
-                if (tok >= t1) x = -INFINITY;
-                else if (logit_row != nullptr) logit_row[tok] = x;
+                if (tok >= t1 || x != x) x = -INFINITY;   // a NaN logit is skipped, as the CPU backends' guard does
+                if (tok < t1 && logit_row != nullptr) logit_row[tok] = x;
                 s[n][i] = x;
                 tile_max = fmaxf(tile_max, x);
             }

@@ -45,6 +45,20 @@ struct KiviBatch {
     int32_t res_is_f16;
 };
 
+// Sequence-sharded decode (one sequence, one KV slice per GPU): the CTA that completes a KV head pushes the head
+// group's normalised rows and lse into slot `rank` of every rank's receive buffer, raises the flags, and (phase 2)
+// waits for all ranks' flags in its own memory and merges. n_ranks == 0 switches all of it off.
+constexpr int kMaxRanks = 16;
+struct PeerExchange {
+    float* parts[kMaxRanks];        // receive buffer [n_ranks][Hq*D+Hq] of every rank (own entry = local memory)
+    int* flags[kMaxRanks];          // flag array [n_ranks][Hq] of every rank
+    int* step_ctr;                  // [Hkv] step counters in this rank's memory; the completing CTA of a KV head bumps its own
+    float* merged_lse;              // [Hq] natural-log lse of the merged result, nullable
+    long long parts_parity_stride;  // floats between the even-step and the odd-step receive buffers
+    long long flags_parity_stride;  // ints between the even-step and the odd-step flag arrays
+    int n_ranks, rank, phases;      // phases: 1 = push, 2 = wait + merge, 3 = both
+};
+
 struct DecodeParams {
     const float* q;   // [B][Hq][D]
     float* out;       // [B][Hq][D]
@@ -60,6 +74,11 @@ struct DecodeParams {
     int64_t logit_stride;
     float* lse2;      // [B][Hq] log2-domain lse for the finalize kernel (nullable unless logits set)
     int* status;      // set to 1 by a kernel whose bounded wait ran out (nullable)
+    // decode step (write the new token's row, then attend): F32 rows [B][Hkv][D] that the CTA owning the last split of a
+    // (sequence, KV head) rounds to F16 and stores at position seq_len-1 before it starts reading (nullable)
+    const float* k_new;
+    const float* v_new;
+    PeerExchange xc;  // sequence-sharded decode only
 };
 
 // Finalize: p = exp2(logit - lse2) and its reductions over the GQA group.
@@ -75,8 +94,7 @@ struct FinalizeParams {
     int32_t seq_len[kMaxBatch];
 };
 
-// Peer exchange + merge of a sequence-sharded decode (exchange_merge.cu).
-constexpr int kMaxRanks = 16;
+// Peer exchange + merge of a sequence-sharded decode as a kernel of its own (exchange_merge.cu).
 struct ExchangeParams {
     float* peer_parts[kMaxRanks];   // receive buffer [n_ranks][Hq*D+Hq] of every rank (own entry = local memory)
     int* peer_flags[kMaxRanks];     // flag array [n_ranks][Hq] of every rank

@@ -21,6 +21,15 @@
 
 namespace argus {
 
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __global__ void __launch_bounds__(128) exchange_merge_kernel(const __grid_constant__ ExchangeParams p) {
     const int h = blockIdx.x;
     const int d = p.d, hq = p.hq;
@@ -38,8 +47,10 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(const __grid_consta
         __threadfence_system();
         __syncthreads();
         if (threadIdx.x < p.n_ranks) {
-            volatile int* f = p.peer_flags[threadIdx.x] + foff + p.rank * hq + h;
-            *f = step;
+            // release in the thread that stores the flag: the rows stored by the other threads were fenced and
+            // ordered before this point by the barrier
+            __threadfence_system();
+            st_release_sys(p.peer_flags[threadIdx.x] + foff + p.rank * hq + h, step);
         }
     }
     if (!(p.phases & 2)) return;
@@ -47,12 +58,13 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(const __grid_consta
     if (threadIdx.x == 0) ok_all = 1;
     __syncthreads();
     if (threadIdx.x < p.n_ranks) {
-        volatile int* f = p.peer_flags[p.rank] + foff + threadIdx.x * hq + h;
+        const int* f = p.peer_flags[p.rank] + foff + threadIdx.x * hq + h;
         bool ok = false;
         for (int it = 0; it < (1 << 21); ++it) {
-            if (*f >= step) { ok = true; break; }
+            if (ld_acquire_sys(f) >= step) { ok = true; break; }
             __nanosleep(64);
         }
+        __threadfence_system();   // acquire in the polling thread, before the barrier hands the rows to the others
         if (!ok) {
             ok_all = 0;
             if (p.status != nullptr) atomicExch(p.status, 3);

@@ -119,13 +119,13 @@ cudaError_t launch_kv_scatter_rows(const float* k_src, const float* v_src, void*
 //   * otherwise a destination may be another row's source: the first launch gathers the rows into scratch, the
 //     second writes them (all reads precede all writes).
 // Rows already in place are skipped. An entry that is not above its predecessor or that would move a row to the
-// right is skipped and sets *status = 2; the contents of the cache are then unspecified.
+// right, or that lies at or beyond `capacity`, is skipped and sets *status = 2; the contents of the cache are then unspecified.
 // first = 1: direct copy or cache -> scratch; 0: scratch -> cache. Scratch layout [heads][rows of the chunk][row_vecs].
 __global__ void __launch_bounds__(256) kv_compact_kernel(uint4* __restrict__ cache, uint4* __restrict__ scratch,
                                                          const int* __restrict__ keep, long long i0, long long n_rows,
                                                          long long write_start, int head0, int n_heads, int row_vecs,
                                                          long long head_stride_v, long long pos_stride_v, int first,
-                                                         int* status) {
+                                                         long long capacity, int* status) {
     const bool direct = (long long)keep[i0] - (write_start + i0) >= n_rows;   // the same answer in every thread
     if (direct && !first) return;
     // blockIdx.y = head of the pass; a chunk has at most 32768 rows, so 32-bit index arithmetic is enough
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(256) kv_compact_kernel(uint4* __restrict__ cac
     const long long i = i0 + r;
     const long long src = keep[i], dst = write_start + i;
     if (src == dst) return;
-    if (src < dst || (i > 0 && keep[i - 1] >= src)) {
+    if (src < dst || src >= capacity || (i > 0 && keep[i - 1] >= src)) {   // the reference's slice index would panic
         if (status != nullptr && v == 0 && hh == 0) atomicExch(status, 2);
         return;
     }
@@ -150,46 +150,56 @@ __global__ void __launch_bounds__(256) kv_compact_kernel(uint4* __restrict__ cac
 
 cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, long long i0, long long n_rows,
                                    long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
-                                   long long pos_stride_bytes, int first, int* status, cudaStream_t st) {
+                                   long long pos_stride_bytes, int first, long long capacity, int* status,
+                                   cudaStream_t st) {
     const int row_vecs = row_bytes / 16;
     const long long per_head = n_rows * row_vecs;
     if (per_head <= 0 || n_heads <= 0) return cudaSuccess;
     if (per_head > 0x7fffffffLL || n_heads > 65535) return cudaErrorInvalidValue;
     kv_compact_kernel<<<dim3((unsigned)((per_head + 255) / 256), (unsigned)n_heads), 256, 0, st>>>(
         static_cast<uint4*>(cache), static_cast<uint4*>(scratch), keep, i0, n_rows, write_start, head0, n_heads, row_vecs,
-        head_stride_bytes / 16, pos_stride_bytes / 16, first, status);
+        head_stride_bytes / 16, pos_stride_bytes / 16, first, capacity, status);
     return cudaGetLastError();
 }
 
 // ───────── prefill attention scores: accumulate the per-row probabilities ─────────
-// rows [n_rows][Hq][prefix_len] are the probabilities of n_rows consecutive query rows. sum_out[h][t] += sum over
-// rows in ascending row order; mean_out[row][t] += rows[row][h][t] * (1/Hq) in ascending head order: the reference's
-// loop orders (head outer, row inner), element by element.
+// rows [n_rows][Hq][prefix_len] are the probabilities of n_rows consecutive query rows; row r sits at absolute position
+// p = row0_pos + r and sees keys lo..=p (lo = 0, or max(0, p - (window-1)) with a sliding window). Only those entries are
+// read - the reference adds keys lo..=p and nothing else - so whatever a reused or uninitialised per-row buffer holds
+// outside a row's range never reaches the sums. sum_out[h][t] += sum over rows in ascending row order;
+// mean_out[row][t] += rows[row][h][t] * (1/Hq) in ascending head order: the reference's loop orders, element by element.
 __global__ void __launch_bounds__(256) pfa_reduce_kernel(const float* __restrict__ rows, float* __restrict__ sum_out,
                                                          float* __restrict__ mean_out, int n_rows, int hq,
-                                                         long long prefix_len, float inv_heads) {
+                                                         long long prefix_len, float inv_heads, long long row0_pos,
+                                                         int window) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n_sum = sum_out ? (long long)hq * prefix_len : 0;
     if (idx < n_sum) {
+        const long long t = idx % prefix_len;
         float acc = sum_out[idx];
-        for (int r = 0; r < n_rows; ++r) acc = __fadd_rn(acc, rows[(long long)r * hq * prefix_len + idx]);
+        for (int r = 0; r < n_rows; ++r) {
+            const long long p = row0_pos + r, lo = window > 0 ? max(0LL, p - (window - 1)) : 0LL;
+            if (t >= lo && t <= p) acc = __fadd_rn(acc, rows[(long long)r * hq * prefix_len + idx]);
+        }
         sum_out[idx] = acc;
         return;
     }
     const long long j = idx - n_sum;
     if (mean_out == nullptr || j >= (long long)n_rows * prefix_len) return;
     const long long r = j / prefix_len, t = j % prefix_len;
+    const long long p = row0_pos + r, lo = window > 0 ? max(0LL, p - (window - 1)) : 0LL;
+    if (t < lo || t > p) return;
     float acc = mean_out[j];
     for (int h = 0; h < hq; ++h) acc = __fadd_rn(acc, __fmul_rn(rows[(r * hq + h) * prefix_len + t], inv_heads));
     mean_out[j] = acc;
 }
 
 cudaError_t launch_pfa_reduce(const float* rows, float* sum_out, float* mean_out, int n_rows, int hq, long long prefix_len,
-                              cudaStream_t st) {
+                              long long row0_pos, int window, cudaStream_t st) {
     const long long total = (sum_out ? (long long)hq * prefix_len : 0) + (mean_out ? (long long)n_rows * prefix_len : 0);
     if (total <= 0 || n_rows <= 0) return cudaSuccess;
     pfa_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(rows, sum_out, mean_out, n_rows, hq, prefix_len,
-                                                                       1.0f / (float)hq);
+                                                                       1.0f / (float)hq, row0_pos, window);
     return cudaGetLastError();
 }
 

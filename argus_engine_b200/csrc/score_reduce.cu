@@ -4,9 +4,13 @@
 // (crates/argus-extension-api/src/lib.rs:2938-2948; the kernels they replace are
 // kernel_score_fused_reduce{,_per_layer}, crates/techniques/attn-score/src/score_reduce.cu:13-91).
 // Policy, unchanged: per token, head sum and GQA group mean per layer, MAX across layers (from 0),
-// cumulative = cumulative*decay_factor + step. Sums run over heads in ascending order in F32, exactly as
-// the reference does, so the result is bit-identical to it for the same score buffer; the keep-set
-// selection that reads these buffers therefore sees the same numbers.
+// cumulative = cumulative*decay_factor + step. Sums run over heads in ascending order in F32 and the decay is a
+// rounded product followed by a rounded sum, exactly as the reference's CPU producer does it (AttnScoreProducer:
+// multiply at begin_step, add at end_step; crates/techniques/attn-score/src/lib.rs:175-359), so the result is
+// bit-identical to the CPU producer for the same score buffer and the keep-set selection that reads these
+// buffers sees the same numbers. The reference's CUDA kernel, built with nvcc's default contraction, fuses the
+// product and the sum into one FMA: with a decay factor whose product is inexact (0.9, not 1.0 or 0.5) it can
+// differ from the CPU producer, and from this kernel, by one ulp.
 //
 // One thread per token (loads of a (layer, head) row are coalesced across the warp); the head loop is
 // unrolled so that eight row loads are in flight per thread, and there is no 16-KV-head limit because the

@@ -44,7 +44,8 @@ class ShardedDecoder:
         self.part_len = num_heads_q * head_dim + num_heads_q
         self.part = torch.zeros(self.part_len, dtype=torch.float32, device=device)
         self.parts = torch.zeros(self.world, self.part_len, dtype=torch.float32, device=device)
-        self.exchange_fn = None   # set by make_gpu_decoder(..., fused=True): replaces gather + merge
+        self.exchange_fn = None     # set by make_gpu_decoder(..., fused="two_kernels"): replaces gather + merge
+        self.fused_step_fn = None   # set by make_gpu_decoder(..., fused=True): replaces the whole step
 
     def capture(self, q: torch.Tensor, out: torch.Tensor):
         """Record one step (kernel, gather, merge) on static tensors into a CUDA graph and return it; replaying it
@@ -62,6 +63,9 @@ class ShardedDecoder:
             return None
 
     def step(self, q: torch.Tensor, out: torch.Tensor) -> None:
+        if self.fused_step_fn is not None:   # decode, peer push, wait and merge in one launch
+            self.fused_step_fn(q, out)
+            return
         self.partial_fn(q, self.part)
         if self.exchange_fn is not None:
             self.exchange_fn(self.part, out)
@@ -98,10 +102,13 @@ class PeerBuffers:
 
 
 def make_gpu_decoder(be, k_shard: torch.Tensor, v_shard: torch.Tensor, shard_len: int, num_heads_q: int,
-                     num_heads_kv: int, head_dim: int, group=None, fused: bool = False) -> ShardedDecoder:
-    """ShardedDecoder over the CUDA kernels of `be` (a B200Backend) for an F16 HeadMajor shard. With `fused` the
-    all-gather and the merge become one kernel that stores the partial into every rank's receive buffer over
-    NVLink peer pointers and merges when all flags have arrived (argus_b200_exchange_merge)."""
+                     num_heads_kv: int, head_dim: int, group=None, fused=False) -> ShardedDecoder:
+    """ShardedDecoder over the CUDA kernels of `be` (a B200Backend) for an F16 HeadMajor shard.
+    fused=False: decode kernel, ONE NCCL all-gather into each rank's own memory, merge kernel.
+    fused=True: ONE launch per step (argus_b200_attention_gen_sharded): the CTA of the decode kernel that completes a
+    KV head stores the head group's (o, lse) rows into every rank's receive buffer over NVLink peer pointers, waits
+    (bounded) for the other ranks' rows of those heads and merges them. The step number lives in device memory.
+    fused="two_kernels": decode kernel, then argus_b200_exchange_merge (push + wait + merge as a kernel of its own)."""
     from .backend import DecodeExtras
 
     hq, d = num_heads_q, head_dim
@@ -114,7 +121,18 @@ def make_gpu_decoder(be, k_shard: torch.Tensor, v_shard: torch.Tensor, shard_len
         be.lse_merge(parts, hq, d, out)
 
     dec = ShardedDecoder(hq, d, partial_fn, merge_fn, k_shard.device, group)
-    if fused and dec.world > 1:
+    if fused is True and dec.world > 1:
+        peers = PeerBuffers(hq, d, group)
+        counters = torch.zeros(num_heads_kv, dtype=torch.int32, device=k_shard.device)
+
+        def fused_step_fn(q, out):
+            be.attention_gen_sharded(q, k_shard, v_shard, out, hq, num_heads_kv, d, shard_len, peers.peer_parts,
+                                     peers.peer_flags, peers.rank, counters, peers.parts_stride, peers.flags_stride)
+
+        dec.fused_step_fn = fused_step_fn
+        dec._peers = peers   # keep the symmetric allocation alive
+        dec._counters = counters
+    elif fused and dec.world > 1:
         peers = PeerBuffers(hq, d, group)
         step_dev = torch.zeros(1, dtype=torch.int32, device=k_shard.device)
 

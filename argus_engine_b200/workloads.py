@@ -63,6 +63,50 @@ def config2(batch: int = 16, lo: int = 1024, hi: int = 8192) -> DecodeCase:
     return DecodeCase(q, k, v, lens, 32, 8, 128)
 
 
+# ── long-context decode sharded by sequence: Hq=64, Hkv=8, D=128, T=2^20, seed 4 ──
+C5_T, C5_HQ, C5_HKV, C5_D, C5_SEED = 1 << 20, 64, 8, 128, 4
+C5_BLOCK = 1 << 16   # tokens per independently seeded block
+
+
+def config5_q() -> np.ndarray:
+    """q [64,128] float32: the first draw of PCG64(4)."""
+    return _rng(C5_SEED).standard_normal((C5_HQ, C5_D), dtype=np.float32)
+
+
+def config5_block(which: int, head: int, block: int) -> np.ndarray:
+    """Tokens [block*65536, (block+1)*65536) of one KV head of K (which=0) or V (which=1): [65536,128] float16 drawn
+    from its own stream PCG64(SeedSequence([4, which, head, block])). Independent streams per (tensor, head, block) let
+    every rank of a sharded run draw exactly its slice, in parallel, and let a checker redraw one head alone."""
+    rng = np.random.Generator(np.random.PCG64(np.random.SeedSequence([C5_SEED, which, head, block])))
+    return rng.standard_normal((C5_BLOCK, C5_D), dtype=np.float32).astype(np.float16)
+
+
+def config5_slice(lo: int, hi: int, heads=None, threads: int = 0):
+    """K and V [len(heads), hi-lo, 128] float16 (HeadMajor) for tokens [lo, hi) of the listed KV heads (default all 8).
+    Blocks are drawn on a thread pool (numpy's generators release the GIL)."""
+    from concurrent.futures import ThreadPoolExecutor
+    import os
+
+    heads = list(range(C5_HKV)) if heads is None else list(heads)
+    n = max(0, hi - lo)
+    k = np.empty((len(heads), n, C5_D), dtype=np.float16)
+    v = np.empty((len(heads), n, C5_D), dtype=np.float16)
+    if n == 0:
+        return k, v
+    jobs = [(w, i, h, b) for w in (0, 1) for i, h in enumerate(heads) for b in range(lo // C5_BLOCK, (hi - 1) // C5_BLOCK + 1)]
+
+    def run(job):
+        w, i, h, b = job
+        blk = config5_block(w, h, b)
+        t0, t1 = max(lo, b * C5_BLOCK), min(hi, (b + 1) * C5_BLOCK)
+        (k if w == 0 else v)[i, t0 - lo:t1 - lo] = blk[t0 - b * C5_BLOCK:t1 - b * C5_BLOCK]
+
+    workers = threads or min(32, len(os.sched_getaffinity(0)))
+    with ThreadPoolExecutor(max_workers=max(1, workers)) as ex:
+        list(ex.map(run, jobs))
+    return k, v
+
+
 @dataclass
 class KiviSource:
     """Un-quantised source tensors of a KIVI configuration: per sequence K and V [T,Hkv,D] float32 in token

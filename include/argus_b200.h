@@ -113,6 +113,25 @@ ARGUS_B200_API int argus_b200_attention_gen_batched(argus_b200_ctx* ctx, void* s
                                      int num_heads_q, int num_heads_kv, int head_dim, int kv_dtype,
                                      const argus_b200_decode_extras* extras);
 
+/* One decode step of the engine's attention layer in one call: the new token's K/V row is written into the cache and
+ * the query attends over the sequence INCLUDING it - the pair of calls the engine issues back to back
+ * (engine/src/layers/transformer_layer/forward_gen_fmt.rs:207 KV write, :267-275 attention; kernels
+ * kv_scatter_f32_to_f16, engine/src/backend/cuda_pc/kernels.cu:305-340, + attention_gen_f16kv_naive, :471-540).
+ * k_new / v_new: F32 device rows [n_seqs][Hkv][D] (16-byte aligned), stored at position seqs[b].seq_len - the length
+ * BEFORE the write, which must be below capacity[b] - rounded to F16 nearest-even exactly like argus_b200_kv_scatter;
+ * the attention then runs over seq_len + 1 positions. With F16 caches both happen in ONE launch (the CTA that owns the
+ * end of a sequence stores the row before it reads); F32 caches take the KV write kernel first. The caller advances
+ * its sequence length afterwards. `seqs` and `capacity` are HOST arrays read during the call. */
+ARGUS_B200_API int argus_b200_decode_step_batched(argus_b200_ctx* ctx, void* stream, const float* q, const float* k_new,
+                                                  const float* v_new, const argus_b200_seq* seqs, const int64_t* capacity,
+                                                  int n_seqs, float* out, int num_heads_q, int num_heads_kv, int head_dim,
+                                                  int kv_dtype, const argus_b200_decode_extras* extras);
+ARGUS_B200_API int argus_b200_decode_step(argus_b200_ctx* ctx, void* stream, const float* q, const float* k_new,
+                                          const float* v_new, void* k_cache, void* v_cache, float* out, int num_heads_q,
+                                          int num_heads_kv, int head_dim, int64_t cache_seq_len, int64_t capacity,
+                                          int kv_dtype, int64_t head_stride, int64_t pos_stride,
+                                          const argus_b200_decode_extras* extras);
+
 /* The same over PAGED F16 caches (the paged layout option of a KVCacheFormat for batched serving; no counterpart in
  * the reference, whose caches are contiguous per sequence): K and V live in page pools; token t of sequence b is row
  * t % page_tokens of page seqs[b].page_table[t / page_tokens], and element (page, kv_head, row, c) sits at
@@ -238,7 +257,9 @@ typedef struct argus_b200_score_reduce_args {
 } argus_b200_score_reduce_args;
 
 /* reduce — kernel_score_fused_reduce (crates/techniques/attn-score/src/score_reduce.cu:13-64); no
- * 16-KV-head limit. */
+ * 16-KV-head limit. Bit-identical to the CPU producer (AttnScoreProducer, crates/techniques/attn-score/src/lib.rs:
+ * 175-359: decay as a rounded product, then a rounded sum); the reference's CUDA kernel contracts the two into one
+ * FMA and can differ by one ulp when importance*decay_factor is inexact. */
 ARGUS_B200_API int argus_b200_score_reduce(argus_b200_ctx* ctx, const argus_b200_score_reduce_args* args);
 /* reduce_per_layer — kernel_score_fused_reduce_per_layer (score_reduce.cu:66-91). */
 ARGUS_B200_API int argus_b200_score_reduce_per_layer(argus_b200_ctx* ctx, const argus_b200_score_reduce_args* args);
@@ -291,6 +312,38 @@ ARGUS_B200_API int argus_b200_exchange_merge(argus_b200_ctx* ctx, void* stream, 
                                              float* lse_out, int phases);
 ARGUS_B200_API int argus_b200_step_increment(argus_b200_ctx* ctx, void* stream, int* step_dev);
 
+/* The whole step of a sequence-sharded decode in ONE launch: argus_b200_attention_gen over this rank's slice of the KV
+ * sequence, whose split-merge epilogue also does the exchange. No counterpart in the reference (single device; the
+ * algebra is the chunk merge of engine/src/backend/cpu/neon.rs:1028-1125). The CTA that completes a KV head writes the
+ * head group's normalised rows and natural-log lse into slot `rank` of every rank's receive buffer with plain NVLink
+ * peer stores (no multicast, no bulk copy on peer memory), raises flag[rank][head] to the step number there, then
+ * waits - with an iteration limit - for the flags of all ranks in its OWN flag array and writes the merged rows to
+ * `out` [Hq][D] (and `merged_lse` [Hq] if set). Buffers as for argus_b200_exchange_merge: peer_parts[s] / peer_flags[s]
+ * are addresses valid on this GPU of rank s's receive buffer (two sets of [n_ranks][Hq*D+Hq] floats, `parts_parity_stride`
+ * floats apart) and flag array (two sets of [n_ranks][Hq] ints), zero-initialised once. The step number lives in device
+ * memory: `step_counters` is an int[Hkv] array of this rank, zero-initialised once, bumped by the kernel itself (one
+ * counter per KV head), so the call replays from a CUDA graph and every rank must issue the same number of calls. Odd
+ * steps use the second buffer set, so a fast rank's next push cannot overwrite what a slow rank still merges.
+ * phases: 3 normally; 1 = push only (then argus_b200_exchange_merge with phases = 2 and the host's step number does the
+ * wait + merge: the form single-GPU tests use, where no kernel may wait for a later launch). Hq must be a multiple
+ * of 4; a shard may be empty (shard_len 0: lse = -inf, skipped by the merge). A wait that runs out zeroes the heads'
+ * output and sets the status word to 3 (argus_b200_check_status). */
+typedef struct argus_b200_exchange {
+    float* const* peer_parts;
+    int* const* peer_flags;
+    int* step_counters;
+    float* merged_lse;
+    int64_t parts_parity_stride;
+    int64_t flags_parity_stride;
+    int n_ranks;
+    int rank;
+    int phases;
+} argus_b200_exchange;
+ARGUS_B200_API int argus_b200_attention_gen_sharded(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_shard,
+                                                    const void* v_shard, float* out, int num_heads_q, int num_heads_kv,
+                                                    int head_dim, int64_t shard_len, int kv_dtype, int64_t head_stride,
+                                                    int64_t pos_stride, const argus_b200_exchange* exchange);
+
 /* Blocks until `stream` is idle and returns the status word the kernels set when one of their bounded
  * waits ran out (0 = clean). The word is cleared by the call. */
 ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
@@ -308,8 +361,9 @@ ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
  *
  * argus_b200_kv_compact replaces KVCache::compact_keep_positions and compact_keep_positions_for_head
  * (engine/src/kv/kv_cache.rs:1266-1352), which exist on the CPU only: position write_start+i receives position
- * keep[i] for i < n_keep, in place. keep_dev is a DEVICE array, ascending, with keep[i] >= write_start+i (an entry
- * that breaks this is skipped and sets the status word to 2, see argus_b200_check_status; the cache contents are
+ * keep[i] for i < n_keep, in place. keep_dev is a DEVICE array, ascending, with keep[i] >= write_start+i and keep[i] < capacity (the
+ * cache's row count; the reference's slice indexing would panic beyond it; an entry
+ * that breaks any of this is skipped and sets the status word to 2, see argus_b200_check_status; the cache contents are
  * then unspecified). head = -1 moves
  * every KV head, head >= 0 only that one. Like the reference, the call does not touch the sequence length: the
  * caller sets it to write_start + n_keep. Rows move in ascending chunks, through the context's scratch where a
@@ -333,8 +387,9 @@ ARGUS_B200_API int argus_b200_kv_scatter_batched(argus_b200_ctx* ctx, void* stre
                                                  const float* v_src, const argus_b200_seq* seqs, const int64_t* capacity,
                                                  int n_seqs, int dst_dtype, int num_heads_kv, int head_dim);
 ARGUS_B200_API int argus_b200_kv_compact(argus_b200_ctx* ctx, void* stream, void* k, void* v, int kv_dtype,
-                                         int num_heads_kv, int head_dim, int64_t head_stride, int64_t pos_stride,
-                                         const int32_t* keep_dev, int64_t n_keep, int64_t write_start, int head);
+                                         int num_heads_kv, int head_dim, int64_t capacity, int64_t head_stride,
+                                         int64_t pos_stride, const int32_t* keep_dev, int64_t n_keep, int64_t write_start,
+                                         int head);
 ARGUS_B200_API int argus_b200_kv_weighted_merge(argus_b200_ctx* ctx, void* stream, void* k, void* v, int kv_dtype,
                                                 int num_heads_kv, int head_dim, int64_t head_stride, int64_t pos_stride,
                                                 const int32_t* into_pos, const float* into_weight,

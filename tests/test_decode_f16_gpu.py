@@ -213,3 +213,97 @@ def test_paged_cache_is_bit_identical_to_contiguous(be, d, page_tokens):
     for i in range(B):
         want, _ = _oracle(case, i)
         np.testing.assert_allclose(out_p[i].cpu().numpy(), want, atol=OUT_ATOL, rtol=OUT_RTOL)
+
+
+@pytest.mark.parametrize("seq_major", [False, True])
+def test_decode_step_writes_the_row_and_attends(be, seq_major):
+    """argus_b200_decode_step_batched = KV write + attention in one launch: caches and outputs are bit-identical to
+    argus_b200_kv_scatter_batched followed by argus_b200_attention_gen_batched, and the output matches the oracle run
+    on the F16-rounded new rows. Lengths cover an empty cache, a row that opens a new 16-token tile and ragged ends."""
+    hq, hkv, d, cap_extra = 32, 8, 128, 40
+    lens = [0, 15, 16, 1000, 4099]            # lengths BEFORE the step
+    case = wl.decode_case(77, [t + 1 for t in lens], hq, hkv, d, cap_extra=cap_extra)
+    rng = np.random.Generator(np.random.PCG64(78))
+    k_new = rng.standard_normal((len(lens), hkv, d), dtype=np.float32)
+    v_new = rng.standard_normal((len(lens), hkv, d), dtype=np.float32)
+
+    def caches():
+        ks, vs = [], []
+        for i in range(len(lens)):
+            k, v = case.k[i].copy(), case.v[i].copy()
+            k[:, lens[i]:] = np.nan   # the new row's slot and everything behind it hold garbage before the step
+            v[:, lens[i]:] = np.nan
+            if seq_major:
+                k, v = (np.ascontiguousarray(a.transpose(1, 0, 2)) for a in (k, v))
+            ks.append(_dev(k))
+            vs.append(_dev(v))
+        return ks, vs
+
+    q = _dev(case.q)
+    ks1, vs1 = caches()
+    out1 = torch.full((len(lens), hq, d), float("nan"), device="cuda")
+    launches0 = be.launch_count
+    be.decode_step_batched(q, _dev(k_new), _dev(v_new), ks1, vs1, lens, out1, hq, hkv, d)
+    assert be.launch_count - launches0 == 1
+    ks2, vs2 = caches()
+    out2 = torch.full((len(lens), hq, d), float("nan"), device="cuda")
+    if seq_major:   # the batched KV write takes HeadMajor caches: write through a transposed view of the same memory
+        for i in range(len(lens)):
+            ks2[i][lens[i]] = _dev(k_new[i]).to(torch.float16)
+            vs2[i][lens[i]] = _dev(v_new[i]).to(torch.float16)
+    else:
+        be.kv_scatter_batched(_dev(k_new), _dev(v_new), ks2, vs2, lens)
+    be.attention_gen_batched(q, ks2, vs2, [t + 1 for t in lens], out2, hq, hkv, d)
+    torch.cuda.synchronize()
+    assert be.check_status() == 0
+    assert torch.equal(out1, out2)
+    for i, t in enumerate(lens):
+        a, b = (ks1[i], ks2[i]), (vs1[i], vs2[i])
+        for x, y in (a, b):
+            rows_x = x[: t + 1] if seq_major else x[:, : t + 1]
+            rows_y = y[: t + 1] if seq_major else y[:, : t + 1]
+            assert torch.equal(rows_x.view(torch.int16), rows_y.view(torch.int16))
+        kk = case.k[i].copy()
+        vv = case.v[i].copy()
+        kk[:, t] = k_new[i].astype(np.float16)
+        vv[:, t] = v_new[i].astype(np.float16)
+        want, _ = orc.attention_gen(case.q[i], kk.view(np.uint16), vv.view(np.uint16), hq, hkv, d, t + 1)
+        np.testing.assert_allclose(out1[i].cpu().numpy(), want, atol=OUT_ATOL, rtol=OUT_RTOL)
+
+
+def test_nan_logit_is_skipped_like_the_cpu_guard(be):
+    """What a NaN in the K cache does. The reference's CPU backends turn NaN logits into -inf, i.e. skip the position
+    (engine/src/backend/cpu/common.rs:555-584); its CUDA kernel (engine/src/backend/cuda_pc/kernels.cu:471-540) and its
+    AVX2 arm have no guard and return NaN rows. This kernel follows the CPU guard for NaN logits: the heads that read the
+    NaN row equal the guarded oracle, the exported probability of that position is 0, other KV heads are untouched.
+    (The guard's second half, a uniform distribution when NO finite logit is left, is not reproduced: such a head
+    returns zeros and lse = -inf, checked below with a NaN in q.)"""
+    from argus_engine_b200 import DecodeExtras
+
+    hq, hkv, d, T = 8, 2, 64, 300
+    case = wl.decode_case(5, [T], hq, hkv, d)
+    k = case.k[0].copy()
+    k[1, 17, 3] = np.nan
+    out = torch.zeros(hq, d, device="cuda")
+    sc = torch.zeros(hq, T, device="cuda")
+    be.attention_gen(_dev(case.q[0]), _dev(k), _dev(case.v[0]), out, hq, hkv, d, T, scores_out=sc)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    guarded, guarded_p = orc.attention_gen(case.q[0], k.view(np.uint16), case.v[0].view(np.uint16), hq, hkv, d, T,
+                                           want_scores=True, guards=True)
+    assert np.isfinite(guarded).all()
+    np.testing.assert_allclose(got, guarded, atol=OUT_ATOL, rtol=OUT_RTOL)
+    np.testing.assert_allclose(sc.cpu().numpy(), guarded_p, atol=P_ATOL, rtol=P_RTOL)
+    g = hq // hkv
+    assert (sc[g:, 17] == 0).all()
+    unguarded, _ = orc.attention_gen(case.q[0], k.view(np.uint16), case.v[0].view(np.uint16), hq, hkv, d, T)
+    assert np.isnan(unguarded[g:]).all()                # the unguarded arms return NaN rows here
+    q = case.q[0].copy()
+    q[5, 0] = np.nan                                    # every logit of query head 5 is NaN: nothing finite is left
+    lse = torch.zeros(hq, device="cuda")
+    be.attention_gen(_dev(q), _dev(case.k[0]), _dev(case.v[0]), out, hq, hkv, d, T, extras=DecodeExtras(lse=lse))
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(out[5]) == 0 and torch.isneginf(lse[5])
+    want, _ = orc.attention_gen(case.q[0], case.k[0].view(np.uint16), case.v[0].view(np.uint16), hq, hkv, d, T)
+    keep = [h for h in range(hq) if h != 5]
+    np.testing.assert_allclose(out.cpu().numpy()[keep], want[keep], atol=OUT_ATOL, rtol=OUT_RTOL)

@@ -1,6 +1,8 @@
-"""The benchmark configurations at their FULL sizes (BASELINE configs[1], [2], [4]) through the C ABI: against the
-CPU oracle where it finishes in seconds, and through size-independent properties of the domain (a split/sharded
-result equals the unsplit one, probabilities sum to one, a merge of partials equals the whole)."""
+"""The benchmarked workloads at their FULL sizes through the C ABI (batched F16 decode B=16, one-million-token decode,
+KIVI Q4 decode B=8 x 32768 with the H2O vector, BF16 causal prefill B=4 x 4096): against the CPU oracle where it
+finishes in seconds, and through size-independent properties of the domain (a split/sharded result equals the unsplit
+one, probabilities sum to one, a merge of partials equals the whole, an attention output lies in the convex hull of
+the visible V rows)."""
 import numpy as np
 import pytest
 import torch
@@ -27,8 +29,9 @@ def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def test_config2_full_batch_vs_oracle(be):
-    """configs[1] as benchmarked: 16 sequences of 1024..8192 tokens in ONE launch, every sequence against the oracle."""
+def test_batched_decode_full_batch_vs_oracle(be):
+    """The batched decode as benchmarked (B=16, Hq=32, Hkv=8, D=128, lengths U[1024,8192], seed 1): 16 sequences in ONE
+    launch, every sequence against the oracle."""
     case = wl.config2()
     B = len(case.lens)
     out = torch.full((B, 32, 128), float("nan"), device="cuda")
@@ -41,8 +44,8 @@ def test_config2_full_batch_vs_oracle(be):
     assert be.check_status() == 0
 
 
-def test_config5_one_million_tokens(be):
-    """configs[4]: Hq=64, Hkv=8, D=128, T=2^20 on one GPU (4.3 GB of K/V). (1) the 8 query heads of one KV head against
+def test_one_million_token_decode(be):
+    """The long-context decode shape: Hq=64, Hkv=8, D=128, T=2^20 on one GPU (4.3 GB of K/V). (1) the 8 query heads of one KV head against
     the oracle run on that head's 1M rows; (2) the result equals the (o, lse) merge of 8 sequence shards, each decoded
     on its own - the algebra the multi-GPU path relies on; (3) the lse equals the oracle's log-sum-exp."""
     from argus_engine_b200 import DecodeExtras
@@ -83,8 +86,8 @@ def test_config5_one_million_tokens(be):
     np.testing.assert_allclose(mlse.cpu().numpy(), ex.lse.cpu().numpy(), atol=1e-4)
 
 
-def test_config3_full_length_sequence(be):
-    """configs[2], one of its eight sequences at full length (T=32768: 255 flushes + 128 residual tokens, Q4) packed by
+def test_kivi_full_length_sequence(be):
+    """The KIVI Q4 workload, one of its eight sequences at full length (T=32768: 255 flushes + 128 residual tokens) packed by
     the device container: the decode output and the fused H2O group-mean vector against the oracle on the same bytes;
     the vector sums to one per KV head (each of its g rows is a distribution)."""
     from argus_engine_b200 import DecodeExtras
@@ -109,3 +112,66 @@ def test_config3_full_length_sequence(be):
     got = ex.head_scores[0].cpu().numpy()
     np.testing.assert_allclose(got, sh.reshape(hkv, T), atol=P_ATOL, rtol=P_RTOL)
     np.testing.assert_allclose(got.sum(1), 1.0, atol=1e-4)
+
+
+def test_kivi_full_batch_as_benchmarked(be):
+    """The KIVI Q4 decode exactly as the benchmark launches it: B=8 sequences of 32768 tokens (seed 2, 1 % of the K
+    channels scaled by 8), F16 residual window, ONE launch with the fused [8, 8, 32768] group-mean vector. Two of the
+    eight sequences against the oracle on the same packed bytes (output and vector); for all eight every KV head's
+    vector sums to one and every output row lies inside the range of the dequantised V values."""
+    from argus_engine_b200 import DecodeExtras
+    from argus_engine_b200.kivi_cache import KiviDeviceCache
+
+    src = wl.config3_source()
+    B, T, hq, hkv, d = len(src.k), src.k[0].shape[0], 32, 8, 128
+    seqs = []
+    for i in range(B):
+        cache = KiviDeviceCache(be, hkv, d, T, 128, 4)
+        cache.update(_dev(src.k[i]), _dev(src.v[i]))
+        seqs.append(cache.seq(res_f16=True))
+    out = torch.full((B, hq, d), float("nan"), device="cuda")
+    ex = DecodeExtras(head_scores=torch.zeros(B, hkv, T, device="cuda"), score_stride=T)
+    be.kivi_attention_batched(_dev(src.q), seqs, out, hq, hkv, d, 128, 4, 1 / np.sqrt(d), res_f16=True, extras=ex)
+    torch.cuda.synchronize()
+    assert be.check_status() == 0
+    got, got_s = out.cpu().numpy(), ex.head_scores.cpu().numpy()
+    np.testing.assert_allclose(got_s.sum(-1), 1.0, atol=1e-4)
+    vmax = max(float(np.abs(v).max()) for v in src.v)
+    assert np.isfinite(got).all() and np.abs(got).max() <= vmax * 1.07 + 1e-3   # Q4 blocks stay within their group's range
+    for i in (0, B - 1):
+        qk, qv, rk, rv, qt, rt = seqs[i]
+        vk, vv = orc.kivi_assemble_view(qk.cpu().numpy(), qv.cpu().numpy(), rk.float().cpu().numpy(), rv.float().cpu().numpy(),
+                                        hkv, d, 128, 4, qt, rt)
+        want, want_p = orc.attention_gen(src.q[i], vk, vv, hq, hkv, d, T, head_major=False, want_scores=True, avx2=True)
+        np.testing.assert_allclose(got[i], want, atol=OUT_ATOL, rtol=OUT_RTOL)
+        sh = np.zeros(hkv * T, dtype=np.float32)
+        orc.score_accumulate_layer(want_p, T, hq, hkv, T, np.zeros(T, dtype=np.float32), sh)
+        np.testing.assert_allclose(got_s[i], sh.reshape(hkv, T), atol=P_ATOL, rtol=P_RTOL)
+
+
+def test_prefill_full_size_bf16(be):
+    """The causal prefill at its benchmarked size: B=4, S=4096, Hq=32, Hkv=8, D=128, BF16 in and out, seed 3, drawn by the
+    seeded host generator. Four (batch, head) pairs - first and last batch, first and last head group - against the
+    oracle's tiled F32 prefill on the BF16-rounded inputs (all 4096 rows each), compared after rounding the oracle to
+    BF16; every output row of every pair lies in the convex hull of its visible V rows (|o| <= running max |v|), and row 0
+    of every head equals V row 0 exactly."""
+    B, S, hq, hkv, d = 4, 4096, 32, 8, 128
+    case = wl.config4(B, S)
+    q = _dev(case.q).to(torch.bfloat16)
+    k = _dev(case.k).to(torch.bfloat16)
+    v = _dev(case.v).to(torch.bfloat16)
+    out = torch.full((B, S, hq, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert be.flash_attention_prefill(q, k, v, out, hq, hkv, S, S, d, S, B, True)
+    torch.cuda.synchronize()
+    assert be.check_status() == 0
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    g = hq // hkv
+    hull = np.maximum.accumulate(np.abs(case.v), axis=2)           # [B, Hkv, S, D]: running max |v| over visible keys
+    bound = hull.transpose(0, 2, 1, 3).repeat(g, axis=2)            # [B, S, Hq, D]
+    assert (np.abs(got) <= bound * (1 + 2.0 ** -7) + 1e-6).all()
+    np.testing.assert_array_equal(got[:, 0], case.v[:, :, 0].repeat(g, axis=1))
+    for bh in (0, hq - 1, 2 * hq + 13, (B - 1) * hq + hq - 1):
+        want = orc.flash_prefill(case.q, case.k, case.v, hq, hkv, S, S, d, S, bh_range=(bh, bh + 1))
+        b, h = divmod(bh, hq)
+        np.testing.assert_allclose(got[b, :, h], wl._round_bf16(want[b, :, h]), atol=OUT_ATOL, rtol=OUT_RTOL + 2.0 ** -8)

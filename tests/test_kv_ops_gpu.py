@@ -110,6 +110,11 @@ def test_kv_compact_in_chunks_and_edge_lists(be):
     assert small.check_status() == 0 and torch.equal(kd, before)
     small.kv_compact(kd, vd, torch.tensor([0, 1, 2], dtype=torch.int32, device="cuda"), 5)   # would move right
     assert small.check_status() == 2 and torch.equal(kd, before)
+    # a source position at or beyond the cache's row count: the reference's slice index would panic; here the entry is
+    # skipped (nothing is read out of bounds), the status word says so, and the other entries of the list still move
+    small.kv_compact(kd, vd, torch.tensor([10, 20, cap, cap + 7], dtype=torch.int32, device="cuda"), 0)
+    assert small.check_status() == 2
+    assert torch.equal(kd[:, 0], before[:, 10]) and torch.equal(kd[:, 1], before[:, 20]) and torch.equal(kd[:, 2:], before[:, 2:])
 
 
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
@@ -177,6 +182,31 @@ def test_prefill_attention_scores_vs_reference_restatement(be, hq, hkv, d, S, q_
     flat = sum_out.sum(0).cpu().numpy()
     heavy = max(1, T // 8)
     assert orc.keep_top_k(T, 2, 4, heavy, flat) == orc.keep_top_k(T, 2, 4, heavy, want_sum.sum(0)) or T < 16
+
+
+@pytest.mark.parametrize("window", [0, 16])
+def test_prefill_attention_scores_ignores_stale_per_row_contents(be, window):
+    """The per-row buffer arrives full of NaN (a reused or uninitialised buffer). The reference assigns keys lo..=p of
+    each row and adds only those into the sums, so entries outside a row's range must never reach sum_out."""
+    rng = np.random.default_rng(3 + window)
+    hq, hkv, d, S, q_start, qw = 8, 2, 128, 40, 60, 12
+    T = q_start + S
+    q = (rng.standard_normal((S, hq, d)) * 0.8).astype(np.float32)
+    k = rng.standard_normal((hkv, T, d)).astype(np.float16)
+    v = rng.standard_normal((hkv, T, d)).astype(np.float16)
+    want_sum, want_rows, _ = orc.prefill_attention_scores(q, k, hkv, q_start, qw, T, window or None)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    sum_out = torch.zeros(hq, T, device="cuda")
+    rows = torch.full((qw, hq, T), float("nan"), device="cuda")
+    be.prefill_attention_scores(dev(q), dev(k), dev(v), T, q_start, qw, sum_out=sum_out, per_row=rows, window=window)
+    assert be.check_status() == 0
+    np.testing.assert_allclose(sum_out.cpu().numpy(), want_sum, atol=1e-6, rtol=1e-2)
+    got = rows.cpu().numpy()
+    for r in range(qw):
+        p = q_start + S - qw + r
+        lo = max(0, p - (window - 1)) if window else 0
+        np.testing.assert_allclose(got[r, :, lo:p + 1], want_rows[r, :, lo:p + 1], atol=1e-7, rtol=1e-2)
+        assert np.isnan(got[r, :, p + 1:]).all() and np.isnan(got[r, :, :lo]).all()   # left as found
 
 
 @pytest.mark.parametrize("window", [4, 64, 1000])

@@ -72,9 +72,9 @@ def test_prefill_causal_uniform(be):
     np.testing.assert_allclose(got[0, :, 2], want, atol=2e-3, rtol=1e-2)
 
 
-def test_prefill_config4_reduced(be):
-    """configs[3] at reduced size (B=1, S=1024, Hq=32, Hkv=8, D=128, BF16, seed 3) against the oracle, and the
-    full-size property: each output row lies in the convex hull of the visible V rows (|o| <= max |v|)."""
+def test_prefill_bf16_llama_shape_reduced(be):
+    """The benchmarked prefill shape at reduced size (B=1, S=1024, Hq=32, Hkv=8, D=128, BF16, seed 3) against the oracle
+    (the full size is covered in tests/test_full_size_gpu.py)."""
     case = wl.prefill_case(3, 1, 1024, 1024, 32, 8, 128, dtype="bf16")
     want = orc.flash_prefill(case.q, case.k, case.v, 32, 8, 1024, 1024, 128, 1024)
     ok, got = _run(be, case, "bf16")

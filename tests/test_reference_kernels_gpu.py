@@ -88,6 +88,15 @@ def test_score_reduce_matches_reference_kernel(be):
     torch.cuda.synchronize()
     for g, w in zip(got, want):   # decay 0.5 is exact in either rounding order, so the results are bit-identical
         assert torch.equal(g, w)
+    # A non-dyadic decay: this library rounds the product and the sum separately, like the CPU producer; the reference
+    # kernel as nvcc builds it by default contracts them into one fused multiply-add, so the two may differ by an ulp.
+    m.launch("kernel_score_fused_reduce", grid, (64, 1, 1), 0,
+             [ref.ptr(s), ref.ptr(want[0]), ref.ptr(want[1]), C.c_float(0.9), C.c_int(L), C.c_int(hq), C.c_int(hkv), C.c_int(T),
+              C.c_int(max_seq), C.c_int(max_seq)])
+    assert be.score_reduce(s, got[0], got[1], 0.9, L, hq, hkv, T, max_seq, max_seq) == 0
+    torch.cuda.synchronize()
+    for g, w in zip(got[:2], want[:2]):
+        assert torch.allclose(g, w, rtol=3e-7, atol=0)
 
 
 @pytest.mark.parametrize("S,T", [(256, 256), (100, 300)])
