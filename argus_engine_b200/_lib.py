@@ -89,6 +89,7 @@ def load_library() -> C.CDLL:
     lib = C.CDLL(LIB_PATH)
     vp, i32, i64 = C.c_void_p, C.c_int, C.c_int64
     lib.argus_b200_create.argtypes = [i32, C.c_size_t, C.POINTER(vp)]
+    lib.argus_b200_create_in_context.argtypes = [vp, i32, C.c_size_t, C.POINTER(vp)]
     lib.argus_b200_destroy.argtypes = [vp]
     lib.argus_b200_destroy.restype = None
     lib.argus_b200_last_error.argtypes = [vp]
@@ -129,6 +130,11 @@ def load_library() -> C.CDLL:
     lib.argus_b200_attention_gen_paged.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i64, i64, i64, vp]
     lib.argus_b200_kv_compact.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, i64, i64, i32]
     lib.argus_b200_kv_weighted_merge.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, vp, vp, vp, vp, vp, i32, i32]
+    lib.argus_b200_kv_snapshot_prefix.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, vp, C.c_size_t]
+    lib.argus_b200_kv_restore_prefix.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, vp, C.c_size_t]
+    lib.argus_b200_kv_make_resident.argtypes = [vp, vp, vp, C.c_size_t]
+    lib.argus_b200_kv_alloc.argtypes = [vp, C.c_size_t, i32, C.POINTER(vp)]
+    lib.argus_b200_kv_free.argtypes = [vp, vp]
     lib.argus_b200_attention_gen_static.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64]
     lib.argus_b200_static_scratch_bytes.restype = C.c_size_t
     lib.argus_b200_static_last_error.restype = C.c_char_p

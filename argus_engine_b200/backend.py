@@ -36,14 +36,19 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 class B200Backend:
     """One per device; owns the library context (split-KV scratch)."""
 
-    def __init__(self, device: int = 0, workspace_bytes: int = 0):
+    def __init__(self, device: int = 0, workspace_bytes: int = 0, cu_context: Optional[int] = None):
+        """cu_context: a raw CUcontext to create the library context in (argus_b200_create_in_context, the route the
+        engine's plugin factory takes); None binds the device's primary context."""
         self._lib = load_library()
         if not torch.cuda.is_available():
             raise RuntimeError("argus_engine_b200 needs a CUDA device (there is no CPU fallback)")
         torch.cuda.set_device(device)
         torch.cuda.init()
         h = C.c_void_p()
-        rc = self._lib.argus_b200_create(device, workspace_bytes, C.byref(h))
+        if cu_context is not None:
+            rc = self._lib.argus_b200_create_in_context(C.c_void_p(cu_context), device, workspace_bytes, C.byref(h))
+        else:
+            rc = self._lib.argus_b200_create(device, workspace_bytes, C.byref(h))
         if rc != 0:
             raise ArgusB200Error(rc, "argus_b200_create failed (is this an sm_100 device?)")
         self._h = h
@@ -370,6 +375,43 @@ class B200Backend:
         self._check(self._lib.argus_b200_prefill_attention_scores(
             self._h, self._stream(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), dt, hq, k_cache.shape[0], d, S,
             cache_seq_len, hs, ps, q_start_pos, q_window, window, _ptr(sum_out), _ptr(per_row), int(per_row_per_head)))
+
+    def _prefix_layout(self, k_cache: torch.Tensor, num_heads_kv: int):
+        hs, ps, head_major = self.kv_strides(k_cache, num_heads_kv)
+        d = k_cache.shape[-1]
+        cap = k_cache.shape[-2] if head_major else k_cache.shape[-3]
+        dt = KV_F16 if k_cache.dtype == torch.float16 else KV_F32
+        return dt, d, cap, hs, ps
+
+    def kv_snapshot_prefix(self, k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads_kv: int, token_count: int,
+                           dst: torch.Tensor) -> None:
+        """SnapshotRestore::snapshot_prefix payload of one layer: K bytes [Hkv, token_count, D] then V bytes into `dst`
+        (a uint8 tensor of exactly that size, on the device or in pinned host memory)."""
+        dt, d, cap, hs, ps = self._prefix_layout(k_cache, num_heads_kv)
+        self._check(self._lib.argus_b200_kv_snapshot_prefix(self._h, self._stream(), k_cache.data_ptr(), v_cache.data_ptr(), dt,
+                                                            num_heads_kv, d, cap, hs, ps, token_count, dst.data_ptr(),
+                                                            dst.numel() * dst.element_size()))
+
+    def kv_restore_prefix(self, k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads_kv: int, token_count: int,
+                          src: torch.Tensor) -> None:
+        """SnapshotRestore::restore_prefix: the inverse of kv_snapshot_prefix into a cache of any capacity >= token_count."""
+        dt, d, cap, hs, ps = self._prefix_layout(k_cache, num_heads_kv)
+        self._check(self._lib.argus_b200_kv_restore_prefix(self._h, self._stream(), k_cache.data_ptr(), v_cache.data_ptr(), dt,
+                                                           num_heads_kv, d, cap, hs, ps, token_count, src.data_ptr(),
+                                                           src.numel() * src.element_size()))
+
+    def kv_alloc(self, nbytes: int, managed: bool) -> int:
+        """Raw KV allocation (managed = what the engine's CUDA backend uses). Returns the address."""
+        out = C.c_void_p()
+        self._check(self._lib.argus_b200_kv_alloc(self._h, nbytes, int(managed), C.byref(out)))
+        return int(out.value)
+
+    def kv_free(self, ptr: int) -> None:
+        self._check(self._lib.argus_b200_kv_free(self._h, C.c_void_p(ptr)))
+
+    def kv_make_resident(self, ptr: int, nbytes: int) -> None:
+        """Preferred location = this device + prefetch, for a managed KV buffer (no-op for device memory)."""
+        self._check(self._lib.argus_b200_kv_make_resident(self._h, self._stream(), C.c_void_p(ptr), nbytes))
 
     def check_status(self) -> int:
         """Synchronises the current stream; non-zero if a kernel's bounded wait ran out since the last check."""

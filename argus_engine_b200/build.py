@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libargus_b200.so")
-SOURCES = ["context.cu", "context_kivi.cu", "decode_f16.cu", "decode_kivi.cu", "decode_kivi_tc.cu", "kivi_ops.cu", "score_reduce.cu", "prefill_sm100.cu", "decode_f16_static.cu", "lse_merge.cu", "kv_cast.cu", "exchange_merge.cu", "kv_ops.cu", "context_kv.cu"]
+SOURCES = ["context.cu", "context_kivi.cu", "decode_f16.cu", "decode_kivi.cu", "kivi_ops.cu", "score_reduce.cu", "prefill_sm100.cu", "decode_f16_static.cu", "lse_merge.cu", "kv_cast.cu", "exchange_merge.cu", "kv_ops.cu", "context_kv.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -173,7 +173,13 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
     const int waves = ctx->opt.decode_waves > 0 ? ctx->opt.decode_waves : 1;
     const int min_chunk = ctx->opt.decode_min_chunk > 0 ? ctx->opt.decode_min_chunk : 2 * decode_f16_cta_tokens(d);
     int32_t nsplit[kMaxBatch];
-    const int slots_per_sm = ctx->opt.decode_slots > 0 ? ctx->opt.decode_slots : 2;
+    // Two CTAs per SM, except for one long sequence (at least 4096 tokens per CTA even then): one CTA of four warps per
+    // SM keeps enough bytes in flight and streams a little faster (1M tokens: 601 us against 620 us; 128K: 87.3 / 88.4),
+    // and halves the split partials the last CTA of a KV head has to merge.
+    int64_t total_len = 0;
+    for (int i = 0; i < n_seqs; ++i) total_len += lens[i];
+    const bool one_long = n_seqs == 1 && total_len * hkv >= (int64_t)ctx->num_sms * 4096;
+    const int slots_per_sm = ctx->opt.decode_slots > 0 ? ctx->opt.decode_slots : (one_long ? 1 : 2);
     plan_splits(lens, n_seqs, hkv, ctx->num_sms * slots_per_sm, waves, min_chunk, bt.chunk, nsplit);
     int items = 0;
     for (int i = 0; i < n_seqs; ++i) {
@@ -308,13 +314,35 @@ extern "C" {
 int argus_b200_version(void) { return 1; }
 int argus_b200_sm_arch(void) { return 100; }
 
-int argus_b200_create(int device, size_t workspace_bytes, argus_b200_ctx** out) {
-    if (!out) return ARGUS_B200_E_INVALID;
-    *out = nullptr;
-    cudaError_t e = cudaSetDevice(device);
-    if (e != cudaSuccess) return ARGUS_B200_E_CUDA;
+// cuCtxPushCurrent / cuCtxPopCurrent through the runtime's driver entry-point lookup (no link against libcuda).
+typedef int (*CtxPushFn)(void*);
+typedef int (*CtxPopFn)(void**);
+static bool ctx_push(void* cu_context) {
+    static CtxPushFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuCtxPushCurrent", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<CtxPushFn>(sym);
+    }
+    return fn && fn(cu_context) == 0;
+}
+static void ctx_pop() {
+    static CtxPopFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuCtxPopCurrent", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<CtxPopFn>(sym);
+    }
+    void* old = nullptr;
+    if (fn) fn(&old);
+}
+
+// Allocations and device queries of a new context; the CUDA context they land in is whatever is current.
+static int create_in_current(int device, size_t workspace_bytes, argus_b200_ctx** out) {
     cudaDeviceProp prop;
-    e = cudaGetDeviceProperties(&prop, device);
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
     if (e != cudaSuccess) return ARGUS_B200_E_CUDA;
     if (prop.major != 10) return ARGUS_B200_E_UNSUPPORTED;   // sm_100a code only
     Context* c = new Context();
@@ -344,12 +372,33 @@ int argus_b200_create(int device, size_t workspace_bytes, argus_b200_ctx** out) 
     return ARGUS_B200_OK;
 }
 
+int argus_b200_create(int device, size_t workspace_bytes, argus_b200_ctx** out) {
+    if (!out) return ARGUS_B200_E_INVALID;
+    *out = nullptr;
+    cudaError_t e = cudaSetDevice(device);   // binds the device's primary context
+    if (e != cudaSuccess) return ARGUS_B200_E_CUDA;
+    return create_in_current(device, workspace_bytes, out);
+}
+
+int argus_b200_create_in_context(void* cu_context, int device, size_t workspace_bytes, argus_b200_ctx** out) {
+    if (!out) return ARGUS_B200_E_INVALID;
+    *out = nullptr;
+    if (!cu_context) return ARGUS_B200_E_INVALID;
+    if (!ctx_push(cu_context)) return ARGUS_B200_E_CUDA;   // the caller's context: borrowed, never destroyed
+    const int rc = create_in_current(device, workspace_bytes, out);
+    if (rc == ARGUS_B200_OK) reinterpret_cast<Context*>(*out)->cu_context = cu_context;
+    ctx_pop();
+    return rc;
+}
+
 void argus_b200_destroy(argus_b200_ctx* ctx) {
     Context* c = reinterpret_cast<Context*>(ctx);
     if (!c) return;
+    const bool pushed = c->cu_context != nullptr && ctx_push(c->cu_context);
     cudaFree(c->ws);
     cudaFree(c->tickets);
     cudaFree(c->status);
+    if (pushed) ctx_pop();
     delete c;
 }
 

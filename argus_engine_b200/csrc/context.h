@@ -11,6 +11,7 @@ namespace argus {
 
 struct Context {
     int device = 0;
+    void* cu_context = nullptr;   // the caller's CUcontext when created through argus_b200_create_in_context (borrowed)
     int num_sms = 148;
     uint8_t* ws = nullptr;      // scratch: partials, log-sum-exp, logit scratch
     size_t ws_bytes = 0;
@@ -103,6 +104,8 @@ cudaError_t launch_kv_compact_pass(void* cache, void* scratch, const int* keep, 
                                    long long write_start, int head0, int n_heads, int row_bytes, long long head_stride_bytes,
                                    long long pos_stride_bytes, int first, long long capacity, int* status,
                                    cudaStream_t st);
+cudaError_t launch_kv_prefix_rows(void* cache, void* packed, long long n_tok, int hkv, int row_bytes,
+                                  long long head_stride_bytes, long long pos_stride_bytes, int to_packed, cudaStream_t st);
 cudaError_t launch_kv_weighted_merge(void* k, void* v, bool f16, int hkv, int d, long long head_stride,
                                      long long pos_stride, const int* into_pos, const float* into_w, const int* from_start,
                                      const int* from_pos, const float* from_w, int n_merges, int do_k, int do_v,
@@ -120,7 +123,4 @@ cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int h
                                cudaStream_t st);
 int decode_kivi_ctas_per_sm(int head_dim, int bits);
 int decode_kivi_plan_slots_per_sm(int head_dim, int bits);
-// decode_kivi_tc.cu: Q4, head_dim 128, tcgen05 form; packed splits are planned in tiles of 4 groups, one CTA per SM
-cudaError_t launch_decode_kivi_tc(const DecodeParams& p, const KiviBatch& bt, int n_items, cudaStream_t st);
-
 }  // namespace argus

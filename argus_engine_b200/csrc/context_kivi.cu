@@ -54,7 +54,6 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
     bt.res_chunk = 128;
     int64_t qlens[kMaxBatch];
     int64_t max_len = 0, max_res = 0;
-    bool res_aligned = true;   // the tcgen05 kernel reads residual rows as 16-byte vectors
     for (int i = 0; i < n_seqs; ++i) {
         const argus_b200_kivi_seq& s = seqs[i];
         if (s.q_tokens < 0 || s.res_tokens < 0 || s.q_tokens % res_cap != 0 || s.res_tokens > res_cap ||
@@ -71,8 +70,6 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
             ctx->set_error("kivi attention: sequence %d: residual pointers are null", i);
             return ARGUS_B200_E_INVALID;
         }
-        if (s.res_tokens > 0 && ((reinterpret_cast<uintptr_t>(s.res_k) | reinterpret_cast<uintptr_t>(s.res_v)) & 15))
-            res_aligned = false;
         bt.qk[i] = static_cast<const uint8_t*>(s.qk);
         bt.qv[i] = static_cast<const uint8_t*>(s.qv);
         bt.res_k[i] = s.res_k;
@@ -100,24 +97,16 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
     // even out the tail (185 -> 144 us on the benchmark shape). ARGUS_B200_KIVI_WAVES / _SLOTS override for experiments.
     const int waves = ctx->opt.kivi_waves > 0 ? ctx->opt.kivi_waves : 1;
     const int slots_per_sm = ctx->opt.kivi_slots > 0 ? ctx->opt.kivi_slots : decode_kivi_plan_slots_per_sm(d, bits);
-    // Q4 at head_dim 128 has a second kernel, the tcgen05 form (one CTA per SM, tiles of 4 groups), selected by
-    // ARGUS_B200_KIVI_TC=1. The mma.sync kernel stays the default: measured on the benchmark shape it is ~10 % faster.
-    const char* tc_s = getenv("ARGUS_B200_KIVI_TC");   // read per call: tests switch between the two kernels
-    const int tc_env = (tc_s && *tc_s) ? atoi(tc_s) : 0;
-    const bool use_tc = tc_env != 0 && bits == 4 && d == 128 && res_aligned;
-    if (use_tc) plan_splits(qlens, n_seqs, hkv, ctx->num_sms, waves, 4 * 32 * 2, chunk, nsplit);
-    else plan_splits(qlens, n_seqs, hkv, ctx->num_sms * slots_per_sm, waves, 4 * 32 * 2, chunk, nsplit);
+    plan_splits(qlens, n_seqs, hkv, ctx->num_sms * slots_per_sm, waves, 4 * 32 * 2, chunk, nsplit);
     int items = 0;
     for (int i = 0; i < n_seqs; ++i) {
         const int groups = (int)(qlens[i] / 32);
         int cg = std::max(1, (chunk[i] + 31) / 32);
-        if (use_tc) cg = (cg + 3) / 4 * 4;
         int nq = groups > 0 ? (groups + cg - 1) / cg : 0;
         const int nr = (int)((bt.res_tokens[i] + bt.res_chunk - 1) / bt.res_chunk);
         if (nq + nr == 0) nq = 1;   // empty sequence: one empty split writes zeros and lse = -inf
         bt.chunk_groups[i] = cg;
         bt.n_qsplits[i] = nq;
-        bt.q_start[i + 1] = bt.q_start[i] + nq;
         bt.item_start[i] = items;
         items += nq + nr;
         if (nq + nr > kMaxSplits) {
@@ -166,7 +155,7 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
     p.lse2 = lse2;
     p.status = ctx->status;
 
-    cudaError_t e = use_tc ? launch_decode_kivi_tc(p, bt, items, st) : launch_decode_kivi(p, bt, d, bits, items, st);
+    cudaError_t e = launch_decode_kivi(p, bt, d, bits, items, st);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "decode_kivi launch");
     ctx->launches += 1;
 

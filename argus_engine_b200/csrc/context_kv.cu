@@ -131,6 +131,114 @@ extern "C" int argus_b200_kv_compact(argus_b200_ctx* c, void* stream, void* k, v
     return ARGUS_B200_OK;
 }
 
+// Payload of one layer of the session prefix cache: K bytes [Hkv][token_count][D] then V bytes, the packed form of
+// extract_packed_bytes / scatter_packed_bytes (engine/src/kv/standard_format.rs:1657-1790). The reference reads the
+// whole buffer (capacity rows per head) back to the host and packs there; here only the prefix rows move.
+static int prefix_payload(Context* ctx, cudaStream_t st, void* k, void* v, int kv_dtype, int hkv, int d, int64_t capacity,
+                          int64_t head_stride, int64_t pos_stride, int64_t token_count, void* buf, size_t buf_bytes,
+                          bool to_packed, const char* who) {
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    const int eb = elt_bytes(kv_dtype);
+    if (!k || !v || !buf || eb < 0 || hkv <= 0 || d <= 0 || token_count < 0 || capacity <= 0 || token_count > capacity) {
+        ctx->set_error("%s: null pointer, bad dtype or token_count %lld beyond capacity %lld", who, (long long)token_count,
+                       (long long)capacity);
+        return ARGUS_B200_E_INVALID;
+    }
+    const size_t half = (size_t)hkv * token_count * d * eb;
+    if (buf_bytes != 2 * half) {
+        ctx->set_error("%s: the payload of %lld tokens is %zu bytes, the buffer has %zu", who, (long long)token_count, 2 * half,
+                       buf_bytes);
+        return ARGUS_B200_E_INVALID;
+    }
+    if (token_count == 0) return ARGUS_B200_OK;
+    uint8_t* pk = static_cast<uint8_t*>(buf);
+    const size_t row = (size_t)d * eb;
+    cudaError_t e = cudaSuccess;
+    if (pos_stride == d) {
+        // rows of a head are contiguous: one pitched copy per tensor (device, pinned or pageable host on the packed side)
+        const size_t width = (size_t)token_count * row, pitch = (size_t)head_stride * eb;
+        if (to_packed) {
+            e = cudaMemcpy2DAsync(pk, width, k, pitch, width, hkv, cudaMemcpyDefault, st);
+            if (e == cudaSuccess) e = cudaMemcpy2DAsync(pk + half, width, v, pitch, width, hkv, cudaMemcpyDefault, st);
+        } else {
+            e = cudaMemcpy2DAsync(k, pitch, pk, width, width, hkv, cudaMemcpyDefault, st);
+            if (e == cudaSuccess) e = cudaMemcpy2DAsync(v, pitch, pk + half, width, width, hkv, cudaMemcpyDefault, st);
+        }
+        if (e != cudaSuccess) return ctx->cuda_fail(e, who);
+        return ARGUS_B200_OK;
+    }
+    if (!rows_are_vector_aligned(k, v, head_stride, pos_stride, d, eb) || (reinterpret_cast<uintptr_t>(buf) & 15) || (half & 15)) {
+        ctx->set_error("%s: strided rows need 16-byte aligned pointers, rows and pitches", who);
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    e = launch_kv_prefix_rows(k, pk, token_count, hkv, (int)row, head_stride * eb, pos_stride * eb, to_packed ? 1 : 0, st);
+    if (e == cudaSuccess)
+        e = launch_kv_prefix_rows(v, pk + half, token_count, hkv, (int)row, head_stride * eb, pos_stride * eb, to_packed ? 1 : 0, st);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, who);
+    ctx->launches += 2;
+    return ARGUS_B200_OK;
+}
+
+extern "C" int argus_b200_kv_snapshot_prefix(argus_b200_ctx* c, void* stream, const void* k, const void* v, int kv_dtype,
+                                             int num_heads_kv, int head_dim, int64_t capacity, int64_t head_stride,
+                                             int64_t pos_stride, int64_t token_count, void* dst, size_t dst_bytes) {
+    return prefix_payload(reinterpret_cast<Context*>(c), static_cast<cudaStream_t>(stream), const_cast<void*>(k),
+                          const_cast<void*>(v), kv_dtype, num_heads_kv, head_dim, capacity, head_stride, pos_stride, token_count,
+                          dst, dst_bytes, true, "kv_snapshot_prefix");
+}
+
+extern "C" int argus_b200_kv_restore_prefix(argus_b200_ctx* c, void* stream, void* k, void* v, int kv_dtype, int num_heads_kv,
+                                            int head_dim, int64_t capacity, int64_t head_stride, int64_t pos_stride,
+                                            int64_t token_count, const void* src, size_t src_bytes) {
+    return prefix_payload(reinterpret_cast<Context*>(c), static_cast<cudaStream_t>(stream), k, v, kv_dtype, num_heads_kv,
+                          head_dim, capacity, head_stride, pos_stride, token_count, const_cast<void*>(src), src_bytes, false,
+                          "kv_restore_prefix");
+}
+
+// KV residency. The engine's CUDA backend allocates KV buffers as managed memory and lets the driver migrate pages on
+// first touch (engine/src/backend/cuda_pc/memory.rs:1-44); a decode kernel that faults pages in while it streams runs
+// far below the device-memory rate. argus_b200_kv_make_resident states the preferred location once and prefetches.
+extern "C" int argus_b200_kv_make_resident(argus_b200_ctx* c, void* stream, const void* ptr, size_t bytes) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    ctx->err[0] = 0;
+    if (!ptr || bytes == 0) {
+        ctx->set_error("kv_make_resident: null pointer or zero size");
+        return ARGUS_B200_E_INVALID;
+    }
+    cudaPointerAttributes at;
+    cudaError_t e = cudaPointerGetAttributes(&at, ptr);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_make_resident: pointer attributes");
+    if (at.type == cudaMemoryTypeDevice) return ARGUS_B200_OK;   // already where the kernels want it
+    if (at.type != cudaMemoryTypeManaged) {
+        ctx->set_error("kv_make_resident: the range is neither device nor managed memory");
+        return ARGUS_B200_E_UNSUPPORTED;
+    }
+    e = cudaMemAdvise(ptr, bytes, cudaMemAdviseSetPreferredLocation, ctx->device);
+    if (e == cudaSuccess) e = cudaMemPrefetchAsync(ptr, bytes, ctx->device, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_make_resident: advise / prefetch");
+    return ARGUS_B200_OK;
+}
+
+extern "C" int argus_b200_kv_alloc(argus_b200_ctx* c, size_t bytes, int managed, void** out) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx || !out || bytes == 0) return ARGUS_B200_E_INVALID;
+    *out = nullptr;
+    cudaError_t e = managed ? cudaMallocManaged(out, bytes, cudaMemAttachGlobal) : cudaMalloc(out, bytes);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_alloc");
+    return ARGUS_B200_OK;
+}
+
+extern "C" int argus_b200_kv_free(argus_b200_ctx* c, void* ptr) {
+    Context* ctx = reinterpret_cast<Context*>(c);
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    if (!ptr) return ARGUS_B200_OK;
+    cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "kv_free");
+    return ARGUS_B200_OK;
+}
+
 extern "C" int argus_b200_kv_weighted_merge(argus_b200_ctx* c, void* stream, void* k, void* v, int kv_dtype,
                                             int num_heads_kv, int head_dim, int64_t head_stride, int64_t pos_stride,
                                             const int32_t* into_pos, const float* into_weight, const int32_t* from_start,

@@ -111,7 +111,8 @@ __device__ __forceinline__ void peer_exchange_tail(const DecodeParams& p, int kv
 // (running max, sum) at smem[ML_OFF] as [warp][8], followed by __syncthreads().
 // item  = index of this CTA's partial, item0 = partial of split 0 of the same (sequence, KV head);
 // consecutive splits are p.hkv partials apart.
-template <int D, int WARPS>
+// UNR = split partials each thread keeps in flight per float4 slice in the final merge (registers: 4*UNR per slice).
+template <int D, int WARPS, int UNR = 16>
 __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParams& p, int b, int kv, int64_t item,
                                                 int64_t item0, int n_splits) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -206,7 +207,8 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
     }
     __syncthreads();
     // out = sum_s f_s * O_s / L with splits in ascending order (fixed order => run-to-run identical bits).
-    // Each thread owns float4 slices of the [group][D] tile and keeps 8 loads per slice in flight.
+    // Each thread owns float4 slices of the [group][D] tile and keeps UNR loads per slice in flight: this CTA is the
+    // last one of its KV head, so every round trip to L2 here is at the end of the kernel's critical path.
     constexpr int V4 = (8 * D / 4) / (WARPS * 32);   // float4 slices per thread at the full group of 8
     float4 acc[V4];
 #pragma unroll
@@ -214,13 +216,13 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
     const int n_vec = p.group * D / 4;
     const float4* po = reinterpret_cast<const float4*>(p.part_o + item0 * 8 * D);
     const int64_t sstride = (int64_t)p.hkv * 8 * D / 4;
-    for (int s0 = 0; s0 < n_splits; s0 += 8) {
-        float4 v[V4][8];
+    for (int s0 = 0; s0 < n_splits; s0 += UNR) {
+        float4 v[V4][UNR];
 #pragma unroll
         for (int k = 0; k < V4; ++k) {
             const int e = threadIdx.x + k * WARPS * 32;
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
+            for (int u = 0; u < UNR; ++u)
                 v[k][u] = (e < n_vec && s0 + u < n_splits) ? __ldcg(po + (s0 + u) * sstride + e)
                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -229,7 +231,7 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
             const int e = threadIdx.x + k * WARPS * 32;
             const int h = (e * 4) / D;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < UNR; ++u) {
                 const float f = (e < n_vec && s0 + u < n_splits) ? sm_pm[(s0 + u) * 8 + h].x : 0.f;
                 acc[k].x += f * v[k][u].x; acc[k].y += f * v[k][u].y;
                 acc[k].z += f * v[k][u].z; acc[k].w += f * v[k][u].w;

@@ -39,7 +39,6 @@ struct KiviBatch {
     int32_t chunk_groups[kMaxBatch];
     int32_t n_qsplits[kMaxBatch];
     int32_t item_start[kMaxBatch + 1];
-    int32_t q_start[kMaxBatch + 1];   // prefix sum of n_qsplits (the tcgen05 kernel lists all packed splits first)
     int32_t res_cap;
     int32_t res_chunk;
     int32_t res_is_f16;

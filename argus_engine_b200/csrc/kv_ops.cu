@@ -110,6 +110,32 @@ cudaError_t launch_kv_scatter_rows(const float* k_src, const float* v_src, void*
     return cudaGetLastError();
 }
 
+// ───────── prefix snapshot payload: strided cache rows <-> packed [Hkv][token_count][D] bytes ─────────
+// to_packed = 1: packed[(h*n_tok + t)*row_vecs + v] = cache[h*head_stride + t*pos_stride + v]; 0: the other way round.
+// Used where the rows of a head are not contiguous in the cache (SeqMajor); the HeadMajor case is a pitched copy.
+__global__ void __launch_bounds__(256) kv_prefix_rows_kernel(uint4* __restrict__ cache, uint4* __restrict__ packed,
+                                                             long long n_tok, int hkv, int row_vecs,
+                                                             long long head_stride_v, long long pos_stride_v, int to_packed) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tok * hkv * row_vecs) return;
+    const int v = (int)(idx % row_vecs);
+    const long long t = (idx / row_vecs) % n_tok;
+    const int h = (int)(idx / (row_vecs * n_tok));
+    uint4* c = cache + h * head_stride_v + t * pos_stride_v + v;
+    if (to_packed) packed[idx] = *c;
+    else *c = packed[idx];
+}
+
+cudaError_t launch_kv_prefix_rows(void* cache, void* packed, long long n_tok, int hkv, int row_bytes,
+                                  long long head_stride_bytes, long long pos_stride_bytes, int to_packed, cudaStream_t st) {
+    const long long total = n_tok * hkv * (row_bytes / 16);
+    if (total <= 0) return cudaSuccess;
+    kv_prefix_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<uint4*>(cache), static_cast<uint4*>(packed),
+                                                                         n_tok, hkv, row_bytes / 16, head_stride_bytes / 16,
+                                                                         pos_stride_bytes / 16, to_packed);
+    return cudaGetLastError();
+}
+
 // ───────── keep-set compaction ─────────
 // The move is in place and to the left (keep[i] >= write_start + i), and the distance keep[i] - (write_start + i)
 // never shrinks along an ascending list. Rows are moved chunk after chunk in ascending order, so that a later

@@ -1,5 +1,5 @@
 """Seeded synthetic inputs with the shapes, dtypes and value distributions of the five benchmark
-configurations. BASELINE names no public dataset; these stand in for it. All draws use
+configurations. No public dataset belongs to them; these stand in for one. All draws use
 ``numpy.random.Generator(PCG64(seed)).standard_normal(float32)`` in the stated order, so the CPU oracle and
 the GPU path see bit-identical inputs.
 """

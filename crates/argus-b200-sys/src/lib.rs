@@ -45,12 +45,80 @@ pub struct ArgusB200DecodeExtras {
     pub score_stride: i64,
 }
 
+/// `argus_b200_kivi_seq`: one KIVI-packed sequence of a batched call.
+#[repr(C)]
+pub struct ArgusB200KiviSeq {
+    pub qk: *const c_void,
+    pub qv: *const c_void,
+    pub res_k: *const c_void,
+    pub res_v: *const c_void,
+    pub q_tokens: i64,
+    pub res_tokens: i64,
+}
+
+/// `argus_b200_exchange`: peer buffers of a sequence-sharded decode step.
+#[repr(C)]
+pub struct ArgusB200Exchange {
+    pub peer_parts: *const *mut f32,
+    pub peer_flags: *const *mut c_int,
+    pub step_counters: *mut c_int,
+    pub merged_lse: *mut f32,
+    pub parts_parity_stride: i64,
+    pub flags_parity_stride: i64,
+    pub n_ranks: c_int,
+    pub rank: c_int,
+    pub phases: c_int,
+}
+
+pub const ARGUS_B200_KV_F32: c_int = 0;
 pub const ARGUS_B200_KV_F16: c_int = 1;
 pub const ARGUS_B200_E_UNSUPPORTED: c_int = -2;
 
 extern "C" {
     pub fn argus_b200_create(device: c_int, workspace_bytes: usize, out: *mut *mut ArgusB200Ctx) -> c_int;
+    pub fn argus_b200_create_in_context(
+        cu_context: *mut c_void, device: c_int, workspace_bytes: usize, out: *mut *mut ArgusB200Ctx,
+    ) -> c_int;
     pub fn argus_b200_destroy(ctx: *mut ArgusB200Ctx);
+    pub fn argus_b200_version() -> c_int;
+    pub fn argus_b200_sm_arch() -> c_int;
+    pub fn argus_b200_launch_count(ctx: *const ArgusB200Ctx) -> u64;
+    pub fn argus_b200_check_status(ctx: *mut ArgusB200Ctx, stream: *mut c_void) -> c_int;
+    pub fn argus_b200_attention_gen_batched(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, seqs: *const ArgusB200Seq, n_seqs: c_int,
+        out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, kv_dtype: c_int,
+        extras: *const ArgusB200DecodeExtras,
+    ) -> c_int;
+    pub fn argus_b200_decode_step(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, k_new: *const f32, v_new: *const f32,
+        k_cache: *mut c_void, v_cache: *mut c_void, out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int,
+        head_dim: c_int, cache_seq_len: i64, capacity: i64, kv_dtype: c_int, head_stride: i64, pos_stride: i64,
+        extras: *const ArgusB200DecodeExtras,
+    ) -> c_int;
+    pub fn argus_b200_decode_step_batched(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, k_new: *const f32, v_new: *const f32,
+        seqs: *const ArgusB200Seq, capacity: *const i64, n_seqs: c_int, out: *mut f32, num_heads_q: c_int,
+        num_heads_kv: c_int, head_dim: c_int, kv_dtype: c_int, extras: *const ArgusB200DecodeExtras,
+    ) -> c_int;
+    pub fn argus_b200_kivi_attention_batched(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, seqs: *const ArgusB200KiviSeq, n_seqs: c_int,
+        out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, res_cap: c_int, bits: c_int,
+        res_dtype: c_int, scale: f32, extras: *const ArgusB200DecodeExtras,
+    ) -> c_int;
+    pub fn argus_b200_exchange_merge(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, local_part: *const f32, peer_parts: *const *mut f32,
+        peer_flags: *const *mut c_int, n_ranks: c_int, rank: c_int, step: c_int, step_dev: *const c_int,
+        parts_parity_stride: i64, flags_parity_stride: i64, num_heads_q: c_int, head_dim: c_int, out: *mut f32,
+        lse_out: *mut f32, phases: c_int,
+    ) -> c_int;
+    pub fn argus_b200_step_increment(ctx: *mut ArgusB200Ctx, stream: *mut c_void, step_dev: *mut c_int) -> c_int;
+    pub fn argus_b200_attention_gen_sharded(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, k_shard: *const c_void, v_shard: *const c_void,
+        out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, shard_len: i64, kv_dtype: c_int,
+        head_stride: i64, pos_stride: i64, exchange: *const ArgusB200Exchange,
+    ) -> c_int;
+    pub fn argus_b200_static_scratch_bytes() -> usize;
+    pub fn argus_b200_static_last_error() -> *const c_char;
     pub fn argus_b200_last_error(ctx: *const ArgusB200Ctx) -> *const c_char;
     pub fn argus_b200_attention_gen(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, k_cache: *const c_void, v_cache: *const c_void,
@@ -90,9 +158,22 @@ extern "C" {
     ) -> c_int;
     pub fn argus_b200_kv_compact(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, k: *mut c_void, v: *mut c_void, kv_dtype: c_int,
-        num_heads_kv: c_int, head_dim: c_int, head_stride: i64, pos_stride: i64, keep_dev: *const i32, n_keep: i64,
-        write_start: i64, head: c_int,
+        num_heads_kv: c_int, head_dim: c_int, capacity: i64, head_stride: i64, pos_stride: i64, keep_dev: *const i32,
+        n_keep: i64, write_start: i64, head: c_int,
     ) -> c_int;
+    pub fn argus_b200_kv_snapshot_prefix(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, k: *const c_void, v: *const c_void, kv_dtype: c_int,
+        num_heads_kv: c_int, head_dim: c_int, capacity: i64, head_stride: i64, pos_stride: i64, token_count: i64,
+        dst: *mut c_void, dst_bytes: usize,
+    ) -> c_int;
+    pub fn argus_b200_kv_restore_prefix(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, k: *mut c_void, v: *mut c_void, kv_dtype: c_int,
+        num_heads_kv: c_int, head_dim: c_int, capacity: i64, head_stride: i64, pos_stride: i64, token_count: i64,
+        src: *const c_void, src_bytes: usize,
+    ) -> c_int;
+    pub fn argus_b200_kv_make_resident(ctx: *mut ArgusB200Ctx, stream: *mut c_void, ptr: *const c_void, bytes: usize) -> c_int;
+    pub fn argus_b200_kv_alloc(ctx: *mut ArgusB200Ctx, bytes: usize, managed: c_int, out: *mut *mut c_void) -> c_int;
+    pub fn argus_b200_kv_free(ctx: *mut ArgusB200Ctx, ptr: *mut c_void) -> c_int;
     pub fn argus_b200_kv_weighted_merge(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, k: *mut c_void, v: *mut c_void, kv_dtype: c_int,
         num_heads_kv: c_int, head_dim: c_int, head_stride: i64, pos_stride: i64, into_pos: *const i32,
@@ -129,12 +210,18 @@ unsafe impl Send for B200Context {}
 unsafe impl Sync for B200Context {}
 
 impl B200Context {
-    pub fn new(device: i32) -> Result<Self, String> {
+    /// `cu_context` is the raw `CUcontext` the engine lends to a plugin factory (`CudaQuantAttnMakeArgs.cu_context`):
+    /// the library pushes it for its allocations and pops it again; it is borrowed and never destroyed, the same
+    /// contract as `CudaContext::from_raw_context` in crates/techniques/kivi/src/gpu_kivi_cuda.rs:387-399.
+    pub fn new(cu_context: *mut c_void, device: i32) -> Result<Self, String> {
+        if cu_context.is_null() {
+            return Err("null cu_context".to_string());
+        }
         let mut p = std::ptr::null_mut();
-        // SAFETY: plain FFI call; the caller's CUDA context is current and is only borrowed.
-        let rc = unsafe { argus_b200_create(device, 0, &mut p) };
+        // SAFETY: plain FFI call; the context handle stays owned by the engine.
+        let rc = unsafe { argus_b200_create_in_context(cu_context, device, 0, &mut p) };
         if rc != 0 || p.is_null() {
-            return Err(format!("argus_b200_create failed: {rc}"));
+            return Err(format!("argus_b200_create_in_context failed: {rc}"));
         }
         Ok(Self(p))
     }
@@ -182,7 +269,7 @@ fn make_quant_attn(args: &CudaQuantAttnMakeArgs) -> Result<Box<dyn CudaQuantAttn
     if args.cc_major != 10 {
         return Err(format!("argus-b200 needs an sm_100 device, got sm_{}{}", args.cc_major, args.cc_minor));
     }
-    Ok(Box::new(B200QuantAttn(B200Context::new(args.cu_device)?)))
+    Ok(Box::new(B200QuantAttn(B200Context::new(args.cu_context, args.cu_device)?)))
 }
 
 /// Registered beside (not instead of) the JIT plugin: selected with `--backend-cap kivi_b200`.
@@ -204,7 +291,7 @@ impl CudaScoreReduceBackend for B200ScoreReduce {
 }
 
 fn make_score_reduce(args: &CudaScoreReduceMakeArgs) -> Result<Box<dyn CudaScoreReduceBackend>, String> {
-    Ok(Box::new(B200ScoreReduce(B200Context::new(args.cu_device)?)))
+    Ok(Box::new(B200ScoreReduce(B200Context::new(args.cu_context, args.cu_device)?)))
 }
 
 #[distributed_slice(CUDA_SCORE_REDUCERS)]
@@ -217,3 +304,21 @@ const _: () = assert!(std::mem::size_of::<CudaQuantDequantFlushArgs>() == 72);
 const _: () = assert!(std::mem::size_of::<CudaQuantScatterResidualArgs>() == 64);
 const _: () = assert!(std::mem::size_of::<CudaScoreReduceArgs>() == 96);
 const _: () = assert!(std::mem::size_of::<ArgusB200DecodeExtras>() == 48);
+const _: () = assert!(std::mem::size_of::<ArgusB200Seq>() == 40);
+const _: () = assert!(std::mem::size_of::<ArgusB200KiviSeq>() == 48);
+const _: () = assert!(std::mem::size_of::<ArgusB200Exchange>() == 64);
+// Field offsets of the reference's PODs, as the C header's static_asserts state them.
+const _: () = assert!(std::mem::offset_of!(CudaQuantAttnArgs, scores_out) == 56);
+const _: () = assert!(std::mem::offset_of!(CudaQuantAttnArgs, scores_len) == 64);
+const _: () = assert!(std::mem::offset_of!(CudaQuantAttnArgs, num_heads_q) == 72);
+const _: () = assert!(std::mem::offset_of!(CudaQuantAttnArgs, scale) == 120);
+const _: () = assert!(std::mem::offset_of!(CudaQuantAttnArgs, bits) == 124);
+const _: () = assert!(std::mem::offset_of!(CudaQuantAttnGatherArgs, kv_heads) == 24);
+const _: () = assert!(std::mem::offset_of!(CudaQuantDequantFlushArgs, kv_heads) == 24);
+const _: () = assert!(std::mem::offset_of!(CudaQuantDequantFlushArgs, bits) == 64);
+const _: () = assert!(std::mem::offset_of!(CudaQuantDequantFlushArgs, is_key) == 65);
+const _: () = assert!(std::mem::offset_of!(CudaQuantScatterResidualArgs, kv_heads) == 24);
+const _: () = assert!(std::mem::offset_of!(CudaScoreReduceArgs, decay_factor) == 32);
+const _: () = assert!(std::mem::offset_of!(CudaScoreReduceArgs, n_layers) == 40);
+const _: () = assert!(std::mem::offset_of!(CudaScoreReduceArgs, layer_flat_importance) == 88);
+const _: () = assert!(std::mem::offset_of!(ArgusB200Exchange, n_ranks) == 48);

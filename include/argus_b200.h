@@ -52,6 +52,13 @@ typedef struct argus_b200_ctx argus_b200_ctx;
  * device, raises the shared-memory limits and allocates `workspace_bytes` of scratch (0 = default
  * 64 MiB). The caller's context is borrowed, never destroyed. */
 ARGUS_B200_API int argus_b200_create(int device, size_t workspace_bytes, argus_b200_ctx** out);
+/* The same inside the CALLER'S CUDA context instead of the device's primary one: `cu_context` is the raw CUcontext the
+ * engine's KV buffers live in - CudaQuantAttnMakeArgs.cu_context / cu_device (crates/argus-extension-api/src/lib.rs:
+ * 2985-2994), which the reference's plugin rebuilds with CudaContext::from_raw_context
+ * (crates/techniques/kivi/src/gpu_kivi_cuda.rs:387-399). It is pushed for the allocations and popped again, borrowed and
+ * never destroyed. Later calls on the context object must come from a thread that has this CUDA context current, as
+ * the engine's inference thread does. */
+ARGUS_B200_API int argus_b200_create_in_context(void* cu_context, int device, size_t workspace_bytes, argus_b200_ctx** out);
 ARGUS_B200_API void argus_b200_destroy(argus_b200_ctx* ctx);
 /* Text of the last failure on this context ("" if none). Owned by the context. */
 ARGUS_B200_API const char* argus_b200_last_error(const argus_b200_ctx* ctx);
@@ -395,6 +402,34 @@ ARGUS_B200_API int argus_b200_kv_weighted_merge(argus_b200_ctx* ctx, void* strea
                                                 const int32_t* into_pos, const float* into_weight,
                                                 const int32_t* from_start, const int32_t* from_pos,
                                                 const float* from_weight, int n_merges, int axis);
+
+/* ───────────── KV residency and the session prefix cache payload ─────────────
+ * argus_b200_kv_snapshot_prefix / _restore_prefix move the per-layer payload of the session prefix cache file
+ * ("ARGUSKV1" version 2, engine/src/session/prefix_cache.rs:1-30): for one layer, K bytes [Hkv][token_count][D] followed by
+ * V bytes in the cache's own element type - byte for byte what SnapshotRestore::snapshot_prefix produces through
+ * extract_packed_bytes and restore_prefix consumes through scatter_packed_bytes
+ * (engine/src/kv/standard_format.rs:1796-1838, :1657-1790). The reference reads all `capacity` rows of every head back to
+ * the host and packs on the CPU; here only the token_count prefix rows move. `dst` / `src` may be device memory or host
+ * memory (pinned for an asynchronous copy); its size must be exactly 2*Hkv*token_count*D*elt bytes. The file header (magic,
+ * hashes, token ids, logits) stays with the engine. Restoring does not touch rows at or beyond token_count, nor the
+ * sequence length, which the caller sets. The cache is addressed as in argus_b200_attention_gen (HeadMajor: one
+ * pitched copy per tensor; SeqMajor: a gather kernel, rows and pitches 16-byte aligned).
+ *
+ * argus_b200_kv_make_resident: the engine allocates KV buffers as managed memory (cuMemAllocManaged,
+ * engine/src/backend/cuda_pc/memory.rs:36-44) and leaves page placement to first touch. Called once per buffer (after
+ * allocation, or after the host wrote into it) this sets the device as the range's preferred location and prefetches
+ * it on `stream`, so that the decode kernels stream it at the device-memory rate. Device memory is accepted and left
+ * alone; any other kind of pointer returns ARGUS_B200_E_UNSUPPORTED. argus_b200_kv_alloc / _free are the matching
+ * allocator for hosts that want the library to own the choice (managed != 0: cudaMallocManaged, else cudaMalloc). */
+ARGUS_B200_API int argus_b200_kv_snapshot_prefix(argus_b200_ctx* ctx, void* stream, const void* k, const void* v, int kv_dtype,
+                                                 int num_heads_kv, int head_dim, int64_t capacity, int64_t head_stride,
+                                                 int64_t pos_stride, int64_t token_count, void* dst, size_t dst_bytes);
+ARGUS_B200_API int argus_b200_kv_restore_prefix(argus_b200_ctx* ctx, void* stream, void* k, void* v, int kv_dtype,
+                                                int num_heads_kv, int head_dim, int64_t capacity, int64_t head_stride,
+                                                int64_t pos_stride, int64_t token_count, const void* src, size_t src_bytes);
+ARGUS_B200_API int argus_b200_kv_make_resident(argus_b200_ctx* ctx, void* stream, const void* ptr, size_t bytes);
+ARGUS_B200_API int argus_b200_kv_alloc(argus_b200_ctx* ctx, size_t bytes, int managed, void** out);
+ARGUS_B200_API int argus_b200_kv_free(argus_b200_ctx* ctx, void* ptr);
 
 /* D2O Eq. 8, find_nearest_layer_wide_via with cosine_similarity (crates/techniques/d2o/src/lib.rs:187-255; CPU-only in
  * the reference): for each evicted position the retained position whose K row (all KV heads concatenated) has the

@@ -378,3 +378,74 @@ def d2o_find_nearest(k_cache, evict_pos, retain_pos):
         nearest[i] = best_pos
         sims[i] = f32(0.0) if best == -np.inf else best
     return nearest, sims
+
+
+# ── session prefix cache file ("ARGUSKV1", version 2) ──
+
+def extract_packed_bytes(cache: np.ndarray, token_count: int) -> bytes:
+    """extract_packed_bytes for F32 / F16 caches (engine/src/kv/standard_format.rs:1657-1701): HeadMajor [Hkv, cap, D] ->
+    the first token_count rows of every head, heads back to back."""
+    return np.ascontiguousarray(cache[:, :token_count, :]).tobytes()
+
+
+def prefix_cache_encode(model_hash: bytes, tokenizer_hash: bytes, token_ids, last_logits, format_id: int, kv_heads: int,
+                        head_dim: int, layer_payloads) -> bytes:
+    """save_prefix (engine/src/session/prefix_cache.rs:98-149): magic, version 2, header_len (fixed fields after it + the
+    token ids), model hash, format id, tokenizer hash, geometry, token ids, logits section, then the layers' payloads
+    (K bytes then V bytes each) in layer order. All integers little-endian u32, logits little-endian f32."""
+    import struct
+
+    assert len(model_hash) == 32 and len(tokenizer_hash) == 32
+    token_ids = list(token_ids)
+    header_len = (100 - 8 - 4 - 4) + 4 * len(token_ids)
+    buf = bytearray(b"ARGUSKV1")
+    buf += struct.pack("<II", 2, header_len)
+    buf += model_hash
+    buf += struct.pack("<I", format_id)
+    buf += tokenizer_hash
+    buf += struct.pack("<IIII", kv_heads, head_dim, len(layer_payloads), len(token_ids))
+    buf += struct.pack(f"<{len(token_ids)}I", *token_ids)
+    logits = np.asarray(last_logits, dtype="<f4")
+    buf += struct.pack("<I", logits.size) + logits.tobytes()
+    for payload in layer_payloads:
+        buf += payload
+    return bytes(buf)
+
+
+def prefix_cache_decode(raw: bytes, n_layers: int):
+    """The reading half of try_restore_prefix (engine/src/session/prefix_cache.rs:170-330) without the validation against
+    a running model: returns the header fields and the payload split evenly over the layers, or None for a file the
+    reference would invalidate by magic / version / truncation."""
+    import struct
+
+    if len(raw) < 100 or raw[:8] != b"ARGUSKV1":
+        return None
+    version, header_len = struct.unpack_from("<II", raw, 8)
+    if version != 2:
+        return None
+    off = 16
+    model_hash = raw[off:off + 32]
+    off += 32
+    (format_id,) = struct.unpack_from("<I", raw, off)
+    off += 4
+    tokenizer_hash = raw[off:off + 32]
+    off += 32
+    kv_heads, head_dim, saved_layers, token_count = struct.unpack_from("<IIII", raw, off)
+    off += 16
+    if saved_layers != n_layers or off + 4 * token_count > len(raw):
+        return None
+    token_ids = list(struct.unpack_from(f"<{token_count}I", raw, off))
+    off += 4 * token_count
+    (logits_len,) = struct.unpack_from("<I", raw, off)
+    off += 4
+    if off + 4 * logits_len > len(raw):
+        return None
+    logits = np.frombuffer(raw, dtype="<f4", count=logits_len, offset=off).copy()
+    off += 4 * logits_len
+    payload = raw[off:]
+    if n_layers and len(payload) % n_layers:
+        return None
+    per = len(payload) // max(n_layers, 1)
+    return {"model_hash": model_hash, "tokenizer_hash": tokenizer_hash, "format_id": format_id, "kv_heads": kv_heads,
+            "head_dim": head_dim, "token_ids": token_ids, "last_logits": logits, "header_len": header_len,
+            "layers": [payload[i * per:(i + 1) * per] for i in range(n_layers)]}

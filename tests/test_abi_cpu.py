@@ -55,3 +55,25 @@ def test_product_never_imports_the_oracle():
             text = open(os.path.join(pkg, fn)).read()
             assert not re.search(r"^\s*(from|import)\s+oracle", text, re.M), fn
             assert "libargus_oracle" not in text, fn
+
+
+def test_rust_ffi_crate_declares_every_export():
+    """crates/argus-b200-sys cannot be compiled where no Rust toolchain exists, so its completeness is checked as text:
+    every function the C header exports has a `pub fn` declaration in the crate's extern block."""
+    text = open(os.path.join(ROOT, "crates", "argus-b200-sys", "src", "lib.rs")).read()
+    declared = set(re.findall(r"pub fn (argus_b200_\w+)\s*\(", text))
+    missing = [n for n in _declared() if n not in declared]
+    assert not missing, f"missing from the Rust FFI crate: {missing}"
+
+
+def test_ctypes_offsets_match_the_guards_of_the_header_and_crate():
+    from argus_engine_b200 import _lib
+
+    qa = _lib.QuantAttnArgs
+    assert (qa.scores_out.offset, qa.scores_len.offset, qa.num_heads_q.offset, qa.scale.offset, qa.bits.offset) == (56, 64, 72, 120, 124)
+    assert _lib.QuantGatherArgs.kv_heads.offset == 24 and _lib.QuantScatterResidualArgs.kv_heads.offset == 24
+    df = _lib.QuantDequantFlushArgs
+    assert (df.kv_heads.offset, df.bits.offset, df.is_key.offset) == (24, 64, 65)
+    sr = _lib.ScoreReduceArgs
+    assert (sr.decay_factor.offset, sr.n_layers.offset, sr.layer_flat_importance.offset) == (32, 40, 88)
+    assert C.sizeof(_lib.ExchangeC) == 64 and _lib.ExchangeC.n_ranks.offset == 48

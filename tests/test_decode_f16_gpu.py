@@ -56,7 +56,7 @@ def _run_single(be, case, i=0, seq_major=False, scores_stride=None, host_scores=
 
 
 def test_config1_parity(be):
-    """BASELINE configs[0]: B=1, Hq=32, Hkv=8, D=64, T=2048, seed 0."""
+    """The single short decode of the benchmark set: B=1, Hq=32, Hkv=8, D=64, T=2048, seed 0."""
     case = wl.config1()
     want, _ = _oracle(case, 0)
     got, _, _ = _run_single(be, case)
@@ -101,7 +101,7 @@ def test_host_scores_blocking_readback(be):
 
 
 def test_batched_varlen_with_fused_group_scores(be):
-    """A scaled-down configs[1] (same head shape, lengths U[64,1500]) incl. an empty sequence."""
+    """The batched decode scaled down (Llama-3-8B head shape, lengths U[64,1500]) incl. an empty sequence."""
     from argus_engine_b200 import DecodeExtras
 
     lens = wl.config2_lengths(6, 64, 1500) + [0]
@@ -307,3 +307,27 @@ def test_nan_logit_is_skipped_like_the_cpu_guard(be):
     want, _ = orc.attention_gen(case.q[0], case.k[0].view(np.uint16), case.v[0].view(np.uint16), hq, hkv, d, T)
     keep = [h for h in range(hq) if h != 5]
     np.testing.assert_allclose(out.cpu().numpy()[keep], want[keep], atol=OUT_ATOL, rtol=OUT_RTOL)
+
+
+def test_context_created_inside_the_callers_cuda_context():
+    """argus_b200_create_in_context takes the raw CUcontext the engine lends to a plugin factory
+    (CudaQuantAttnMakeArgs.cu_context, crates/argus-extension-api/src/lib.rs:2985-2994): the context is pushed for the
+    allocations and popped again, and decode through the object works from a thread that has it current."""
+    import ctypes as C
+
+    from argus_engine_b200 import B200Backend
+
+    torch.zeros(1, device="cuda")
+    cu = C.CDLL("libcuda.so.1")
+    cur = C.c_void_p()
+    assert cu.cuCtxGetCurrent(C.byref(cur)) == 0 and cur.value
+    b = B200Backend(0, cu_context=cur.value)
+    after = C.c_void_p()
+    assert cu.cuCtxGetCurrent(C.byref(after)) == 0 and after.value == cur.value   # pushed and popped: nothing left behind
+    case = wl.decode_case(3, [700], 32, 8, 128)
+    want, _ = _oracle(case, 0)
+    got, _, _ = _run_single(b, case)
+    np.testing.assert_allclose(got, want, atol=OUT_ATOL, rtol=OUT_RTOL)
+    b.close()
+    with pytest.raises(Exception):
+        B200Backend(0, cu_context=0)

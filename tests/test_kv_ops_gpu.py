@@ -269,3 +269,78 @@ def test_d2o_nearest_empty_lists(be):
     assert pos.tolist()[0] == 5 and sim.tolist()[0] == 0.0                 # only itself to choose from
     pos, sim = be.d2o_nearest(k, none, ev)
     assert pos.numel() == 0
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("seq_major", [False, True])
+@pytest.mark.parametrize("host_side", ["device", "pinned"])
+def test_prefix_cache_payload_round_trip(be, dtype, seq_major, host_side):
+    """Session prefix cache (engine/src/session/prefix_cache.rs): the per-layer payload written from a device-resident
+    cache is byte-identical to what the reference's snapshot_prefix packs on the host; a two-layer ARGUSKV1 v2 file built
+    around it parses back; restoring the payload into a cache of another capacity reproduces the prefix rows bit for bit
+    and leaves the rows behind them alone."""
+    rng = np.random.default_rng(12)
+    hkv, cap, d, tc = 4, 300, 128, 173
+    layers = []
+    for layer in range(2):
+        k, v = _cache(rng, hkv, cap, d, dtype)
+        kd, vd = torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda()
+        if seq_major:   # the same values laid out [cap, Hkv, D]
+            kd, vd = kd.transpose(0, 1).contiguous(), vd.transpose(0, 1).contiguous()
+        nbytes = 2 * hkv * tc * d * k.itemsize
+        dst = torch.zeros(nbytes, dtype=torch.uint8, device="cuda") if host_side == "device" else torch.zeros(nbytes, dtype=torch.uint8).pin_memory()
+        be.kv_snapshot_prefix(kd, vd, hkv, tc, dst)
+        torch.cuda.synchronize()
+        want = orc.extract_packed_bytes(k, tc) + orc.extract_packed_bytes(v, tc)
+        assert bytes(dst.cpu().numpy()) == want
+        layers.append((k, v, want))
+    raw = orc.prefix_cache_encode(b"m" * 32, b"t" * 32, range(tc), [1.0, 2.0], 0, hkv, d, [p for _, _, p in layers])
+    parsed = orc.prefix_cache_decode(raw, 2)
+    assert parsed is not None and parsed["layers"] == [p for _, _, p in layers]
+    for (k, v, _), payload in zip(layers, parsed["layers"]):
+        cap2 = 256
+        filler = 3.0
+        k2 = torch.full((hkv, cap2, d), filler, dtype=torch.from_numpy(k).dtype, device="cuda")
+        v2 = torch.full_like(k2, filler)
+        if seq_major:
+            k2, v2 = k2.transpose(0, 1).contiguous(), v2.transpose(0, 1).contiguous()
+        src = torch.frombuffer(bytearray(payload), dtype=torch.uint8)
+        src = src.cuda() if host_side == "device" else src.pin_memory()
+        be.kv_restore_prefix(k2, v2, hkv, tc, src)
+        torch.cuda.synchronize()
+        k2h, v2h = (t.transpose(0, 1) if seq_major else t for t in (k2, v2))
+        assert np.array_equal(k2h[:, :tc].cpu().numpy().view(np.uint8), np.ascontiguousarray(k[:, :tc]).view(np.uint8))
+        assert np.array_equal(v2h[:, :tc].cpu().numpy().view(np.uint8), np.ascontiguousarray(v[:, :tc]).view(np.uint8))
+        assert (k2h[:, tc:] == filler).all() and (v2h[:, tc:] == filler).all()
+    assert be.check_status() == 0
+
+
+def test_managed_kv_buffers_are_made_resident_and_decoded(be):
+    """KV residency: the engine's CUDA backend allocates KV as managed memory (engine/src/backend/cuda_pc/memory.rs:36-44).
+    A managed buffer filled from the host, advised and prefetched once (argus_b200_kv_make_resident), decodes to the same
+    result as device memory; a device pointer is accepted as is, a host pointer is declined."""
+    import ctypes as C
+
+    from argus_engine_b200 import ArgusB200Error, workloads as wl
+
+    hq, hkv, d, T = 32, 8, 128, 6000
+    case = wl.decode_case(31, [T], hq, hkv, d)
+    nbytes = case.k[0].nbytes
+    ptrs = [be.kv_alloc(nbytes, managed=True) for _ in range(2)]
+    for ptr, arr in zip(ptrs, (case.k[0], case.v[0])):   # the host writes the pages, as a CPU-side cache fill would
+        C.memmove(ptr, arr.ctypes.data, nbytes)
+        be.kv_make_resident(ptr, nbytes)
+    q = torch.from_numpy(case.q[0]).cuda()
+    out = torch.zeros(hq, d, device="cuda")
+    rc = be._lib.argus_b200_attention_gen(be._h, be._stream(), q.data_ptr(), C.c_void_p(ptrs[0]), C.c_void_p(ptrs[1]), out.data_ptr(),
+                                          hq, hkv, d, T, 1, T * d, d, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    want, _ = orc.attention_gen(case.q[0], case.k[0].view(np.uint16), case.v[0].view(np.uint16), hq, hkv, d, T)
+    np.testing.assert_allclose(out.cpu().numpy(), want, atol=2e-3, rtol=1e-2)
+    be.kv_make_resident(q.data_ptr(), q.numel() * 4)          # device memory: nothing to do
+    host = torch.zeros(16)
+    with pytest.raises(ArgusB200Error):
+        be.kv_make_resident(host.data_ptr(), 64)
+    for ptr in ptrs:
+        be.kv_free(ptr)

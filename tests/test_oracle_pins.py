@@ -361,3 +361,25 @@ def test_d2o_find_nearest_reference_case():
     assert pos.tolist() == [0] and sim.tolist() == [0.0]
     pos, sim = orc.d2o_find_nearest(k, [0], [])
     assert pos.tolist() == [0] and sim.tolist() == [0.0]
+
+
+def test_prefix_cache_file_layout_pins():
+    """The byte layout stated in engine/src/session/prefix_cache.rs:1-30 and its FIXED_HEADER_BYTES = 100: the fixed
+    header is 100 bytes, header_len counts everything after the header_len field up to the end of the token ids, the
+    logits section sits between the token ids and the payload, and the payload is layer-major K then V."""
+    k0 = np.arange(2 * 5 * 4, dtype=np.float16).reshape(2, 5, 4)
+    v0 = -k0
+    pay = orc.extract_packed_bytes(k0, 3) + orc.extract_packed_bytes(v0, 3)
+    assert len(pay) == 2 * 2 * 3 * 4 * 2
+    assert np.array_equal(np.frombuffer(pay[:48], dtype=np.float16), np.concatenate([k0[0, :3].ravel(), k0[1, :3].ravel()]))
+    raw = orc.prefix_cache_encode(bytes(range(32)), bytes(range(32, 64)), [7, 8, 9], [0.5, -1.0], 3, 2, 4, [pay, pay])
+    assert raw[:8] == b"ARGUSKV1" and int.from_bytes(raw[8:12], "little") == 2
+    assert int.from_bytes(raw[12:16], "little") == 84 + 3 * 4                      # header_len
+    assert raw[16:48] == bytes(range(32)) and int.from_bytes(raw[48:52], "little") == 3
+    assert [int.from_bytes(raw[84 + 4 * i:88 + 4 * i], "little") for i in range(4)] == [2, 4, 2, 3]   # geometry, token_count
+    assert len(raw) == 100 + 12 + 4 + 8 + 2 * len(pay)
+    got = orc.prefix_cache_decode(raw, 2)
+    assert got["token_ids"] == [7, 8, 9] and got["layers"] == [pay, pay] and got["last_logits"].tolist() == [0.5, -1.0]
+    assert orc.prefix_cache_decode(b"ARGUSKV0" + raw[8:], 2) is None               # magic
+    assert orc.prefix_cache_decode(raw[:8] + (1).to_bytes(4, "little") + raw[12:], 2) is None   # version 1 files are invalid
+    assert orc.prefix_cache_decode(raw, 3) is None                                 # geometry mismatch

@@ -31,7 +31,7 @@ def _dev(a):
 @pytest.mark.parametrize("T,hq,hkv,d", [(2048, 32, 8, 64), (5000, 32, 8, 128), (777, 8, 2, 128)])
 def test_decode_matches_reference_kernel(be, T, hq, hkv, d):
     """attention_gen_f16kv_naive (engine/src/backend/cuda_pc/kernels.cu:471-540), incl. its score export.
-    The first shape is configs[0]."""
+    The first shape is the single short decode of the benchmark set (Hq=32, Hkv=8, D=64, T=2048)."""
     case = wl.decode_case(0, [T], hq, hkv, d)
     q, k, v = _dev(case.q[0]), _dev(case.k[0]), _dev(case.v[0])
     want, want_s = torch.zeros(hq, d, device="cuda"), torch.zeros(hq, T, device="cuda")

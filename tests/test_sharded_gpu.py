@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 def test_virtual_ranks_match_unsharded_oracle(T, N):
     from argus_engine_b200 import B200Backend, DecodeExtras
 
-    hq, hkv, d = 64, 8, 128                      # the Llama-3-70B attention shape of configs[4]
+    hq, hkv, d = 64, 8, 128                      # the Llama-3-70B attention shape of the long-context workload
     case = wl.decode_case(4, [T], hq, hkv, d)
     be = B200Backend(0)
     q = torch.from_numpy(case.q[0]).cuda()
