@@ -62,9 +62,8 @@ class KiviSeq(C.Structure):
 
 class ExchangeC(C.Structure):
     """argus_b200_exchange."""
-    _fields_ = [("peer_parts", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)), ("step_counters", C.c_void_p),
-                ("merged_lse", C.c_void_p), ("parts_parity_stride", C.c_int64), ("flags_parity_stride", C.c_int64),
-                ("n_ranks", C.c_int), ("rank", C.c_int), ("phases", C.c_int)]
+    _fields_ = [("peer_lines", C.POINTER(C.c_void_p)), ("step_counters", C.c_void_p), ("merged_lse", C.c_void_p),
+                ("parity_stride_lines", C.c_int64), ("n_ranks", C.c_int), ("rank", C.c_int), ("phases", C.c_int)]
 
 
 class ScoreReduceArgs(C.Structure):
@@ -117,9 +116,8 @@ def load_library() -> C.CDLL:
     lib.argus_b200_check_status.argtypes = [vp, vp]
     lib.argus_b200_flash_attention_prefill.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i32, i32, i32]
     lib.argus_b200_lse_merge.argtypes = [vp, vp, vp, i32, i64, i32, i32, vp, vp]
-    lib.argus_b200_exchange_merge.argtypes = [vp, vp, vp, C.POINTER(vp), C.POINTER(vp), i32, i32, i32, vp, i64, i64, i32, i32,
-                                              vp, vp, i32]
-    lib.argus_b200_step_increment.argtypes = [vp, vp, vp]
+    lib.argus_b200_exchange_wait_merge.argtypes = [vp, vp, vp, C.POINTER(ExchangeC), i32, i32, i32, i32, vp]
+    lib.argus_b200_exchange_lines_per_head.argtypes = [i32, i32, i32]
     lib.argus_b200_attention_gen_sharded.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i64, i64,
                                                      C.POINTER(ExchangeC)]
     lib.argus_b200_kv_scatter.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, i64]

@@ -268,39 +268,37 @@ class B200Backend:
                                                    parts.stride(0), num_heads_q, head_dim, out.data_ptr(),
                                                    _ptr(lse_out)))
 
-    def exchange_merge(self, local_part: torch.Tensor, peer_parts, peer_flags, rank: int, num_heads_q: int, head_dim: int,
-                       out: torch.Tensor, step: int = 0, step_dev: Optional[torch.Tensor] = None,
-                       parts_parity_stride: int = 0, flags_parity_stride: int = 0,
-                       lse_out: Optional[torch.Tensor] = None, phases: int = 3) -> None:
-        """Fused peer exchange + merge. peer_parts / peer_flags: device pointers (ints), one per rank, valid on this
-        GPU. Give the step number as `step` (host) or `step_dev` (int32 device tensor, see step_increment)."""
-        n = len(peer_parts)
-        pp = (C.c_void_p * n)(*peer_parts)
-        pf = (C.c_void_p * n)(*peer_flags)
-        self._check(self._lib.argus_b200_exchange_merge(
-            self._h, self._stream(), local_part.data_ptr(), pp, pf, n, rank, step, _ptr(step_dev), parts_parity_stride,
-            flags_parity_stride, num_heads_q, head_dim, out.data_ptr(), _ptr(lse_out), phases))
+    def exchange_lines_per_head(self, num_heads_q: int, num_heads_kv: int, head_dim: int) -> int:
+        return int(self._lib.argus_b200_exchange_lines_per_head(num_heads_q, num_heads_kv, head_dim))
+
+    def _exchange(self, peer_lines, rank, step_counters, parity_stride_lines, merged_lse, phases):
+        n = len(peer_lines)
+        pl = (C.c_void_p * n)(*peer_lines)
+        xc = ExchangeC(pl, _ptr(step_counters), _ptr(merged_lse), parity_stride_lines, n, rank, phases)
+        xc._keep = pl
+        return xc
 
     def attention_gen_sharded(self, q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, out: torch.Tensor,
-                              num_heads_q: int, num_heads_kv: int, head_dim: int, shard_len: int, peer_parts, peer_flags,
-                              rank: int, step_counters: torch.Tensor, parts_parity_stride: int, flags_parity_stride: int,
+                              num_heads_q: int, num_heads_kv: int, head_dim: int, shard_len: int, peer_lines, rank: int,
+                              step_counters: torch.Tensor, parity_stride_lines: int,
                               merged_lse: Optional[torch.Tensor] = None, phases: int = 3) -> None:
         """One launch per step of a sequence-sharded decode: split-KV decode over this rank's K/V slice whose epilogue
-        pushes the (o, lse) partial to every rank and merges. peer_parts / peer_flags: device addresses (ints), one per
-        rank; step_counters: int32 device tensor [Hkv], zero before the first step."""
-        n = len(peer_parts)
-        pp = (C.c_void_p * n)(*peer_parts)
-        pf = (C.c_void_p * n)(*peer_flags)
-        xc = ExchangeC(pp, pf, step_counters.data_ptr(), _ptr(merged_lse), parts_parity_stride, flags_parity_stride, n, rank,
-                       phases)
+        pushes the (o, lse) rows to every rank and merges. peer_lines: device addresses (ints) of every rank's receive
+        buffer; step_counters: int32 device tensor [Hkv], zero before the first step."""
+        xc = self._exchange(peer_lines, rank, step_counters, parity_stride_lines, merged_lse, phases)
         hs, ps, _ = self.kv_strides(k_shard, num_heads_kv)
         dt = KV_F16 if k_shard.dtype == torch.float16 else KV_F32
         self._check(self._lib.argus_b200_attention_gen_sharded(
             self._h, self._stream(), q.data_ptr(), k_shard.data_ptr(), v_shard.data_ptr(), out.data_ptr(), num_heads_q,
             num_heads_kv, head_dim, shard_len, dt, hs, ps, C.byref(xc)))
 
-    def step_increment(self, step_dev: torch.Tensor) -> None:
-        self._check(self._lib.argus_b200_step_increment(self._h, self._stream(), step_dev.data_ptr()))
+    def exchange_wait_merge(self, own_part: torch.Tensor, peer_lines, rank: int, step: int, parity_stride_lines: int,
+                            num_heads_q: int, num_heads_kv: int, head_dim: int, out: torch.Tensor,
+                            merged_lse: Optional[torch.Tensor] = None) -> None:
+        """The receiving half of the exchange as a launch of its own (after attention_gen_sharded with phases=1)."""
+        xc = self._exchange(peer_lines, rank, None, parity_stride_lines, merged_lse, 2)
+        self._check(self._lib.argus_b200_exchange_wait_merge(self._h, self._stream(), own_part.data_ptr(), C.byref(xc), step,
+                                                             num_heads_q, num_heads_kv, head_dim, out.data_ptr()))
 
     # ── KV write and eviction executors (HeadMajor [Hkv, cap, D] caches, F16 or F32) ──
     @staticmethod

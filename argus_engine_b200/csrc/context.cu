@@ -5,6 +5,7 @@
 // and the blocking score read-back — minus the run-time nvcc step, since kernels are ahead-of-time
 // sm_100a code, and with a split-KV plan instead of one CTA per query head.
 #include "context.h"
+#include "decode_epilogue.cuh"
 
 #include <cuda_runtime.h>
 #include <math.h>
@@ -157,15 +158,20 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
 
     if (xc) {
         // sequence-sharded form: one sequence, the (o, lse) partial goes to the peers from inside the kernel
-        if (n_seqs != 1 || paged || want_scores || (hq & 3) || xc->n_ranks <= 0 || xc->n_ranks > kMaxRanks || xc->rank < 0 ||
-            xc->rank >= xc->n_ranks || !xc->peer_parts || !xc->peer_flags || !xc->step_counters || (xc->phases & 3) == 0 ||
-            (xc->parts_parity_stride & 3) || (xc->flags_parity_stride < 0)) {
-            ctx->set_error("attention_gen_sharded: one contiguous sequence, Hq a multiple of 4, no score outputs, 1..%d ranks "
-                           "and parity strides that are multiples of 4 are required", kMaxRanks);
+        if (n_seqs != 1 || paged || want_scores || xc->n_ranks <= 0 || xc->n_ranks > kMaxRanks || xc->rank < 0 ||
+            xc->rank >= xc->n_ranks || !xc->peer_lines || !xc->step_counters || (xc->phases & 3) == 0 ||
+            xc->parity_stride_lines < (int64_t)xc->n_ranks * hkv * xc_lines_per_head(g, d)) {
+            ctx->set_error("attention_gen_sharded: one contiguous sequence, no score outputs, 1..%d ranks and a parity stride "
+                           "of at least n_ranks*Hkv*lines_per_head lines are required", kMaxRanks);
             return ARGUS_B200_E_INVALID;
         }
+        if (xc_smem_end(xc->n_ranks, g, d) > (size_t)decode_f16_smem_bytes(d)) {
+            ctx->set_error("attention_gen_sharded: %d ranks of %d query heads per KV head do not fit the kernel's shared memory",
+                           xc->n_ranks, g);
+            return ARGUS_B200_E_UNSUPPORTED;
+        }
         for (int s = 0; s < xc->n_ranks; ++s)
-            if (!xc->peer_parts[s] || !xc->peer_flags[s] || (reinterpret_cast<uintptr_t>(xc->peer_parts[s]) & 15)) {
+            if (!xc->peer_lines[s] || (reinterpret_cast<uintptr_t>(xc->peer_lines[s]) & 15)) {
                 ctx->set_error("attention_gen_sharded: receive buffer of rank %d is null or not 16-byte aligned", s);
                 return ARGUS_B200_E_INVALID;
             }
@@ -259,14 +265,10 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
     p.k_new = k_new;   // F16 contiguous caches only; the callers route the other cases through the KV write kernel
     p.v_new = v_new;
     if (xc) {
-        for (int s = 0; s < xc->n_ranks; ++s) {
-            p.xc.parts[s] = xc->peer_parts[s];
-            p.xc.flags[s] = xc->peer_flags[s];
-        }
+        for (int s = 0; s < xc->n_ranks; ++s) p.xc.lines[s] = xc->peer_lines[s];
         p.xc.step_ctr = xc->step_counters;
         p.xc.merged_lse = xc->merged_lse;
-        p.xc.parts_parity_stride = xc->parts_parity_stride;
-        p.xc.flags_parity_stride = xc->flags_parity_stride;
+        p.xc.parity_stride_lines = xc->parity_stride_lines;
         p.xc.n_ranks = xc->n_ranks;
         p.xc.rank = xc->rank;
         p.xc.phases = xc->phases & 3;
@@ -490,6 +492,11 @@ int argus_b200_decode_step(argus_b200_ctx* ctx, void* stream, const float* q, co
     s.pos_stride = pos_stride;
     return argus_b200_decode_step_batched(ctx, stream, q, k_new, v_new, &s, &capacity, 1, out, num_heads_q, num_heads_kv,
                                           head_dim, kv_dtype, extras);
+}
+
+int argus_b200_exchange_lines_per_head(int num_heads_q, int num_heads_kv, int head_dim) {
+    if (num_heads_q <= 0 || num_heads_kv <= 0 || num_heads_q % num_heads_kv != 0 || head_dim <= 0) return ARGUS_B200_E_INVALID;
+    return argus::xc_lines_per_head(num_heads_q / num_heads_kv, head_dim);
 }
 
 int argus_b200_attention_gen_sharded(argus_b200_ctx* ctx, void* stream, const float* q, const void* k_shard,

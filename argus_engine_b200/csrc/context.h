@@ -88,8 +88,8 @@ cudaError_t launch_prefill_tc(const void* q16, const void* k, const void* v, voi
                               int64_t kv_head_stride, int64_t kv_batch_stride, int p_mode, int* status, cudaStream_t st);
 cudaError_t launch_cast_f32_to_f16(const float* src, void* dst, long long n, cudaStream_t st);
 // exchange_merge.cu
-cudaError_t launch_exchange_merge(const ExchangeParams& p, cudaStream_t st);
-cudaError_t launch_step_increment(int* step, cudaStream_t st);
+cudaError_t launch_exchange_wait_merge(const ExchangeWaitParams& p, const float* own_rows, cudaStream_t st);
+int decode_f16_smem_bytes(int head_dim);
 // kv_cast.cu
 cudaError_t launch_kv_f32_to_f16(const float* src, void* dst, int hkv, long long T, int d, long long head_stride,
                                  long long pos_stride, cudaStream_t st);

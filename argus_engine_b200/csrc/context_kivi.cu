@@ -393,47 +393,34 @@ int argus_b200_lse_merge(argus_b200_ctx* ctx, void* stream, const float* parts, 
     return ARGUS_B200_OK;
 }
 
-int argus_b200_exchange_merge(argus_b200_ctx* ctx, void* stream, const float* local_part, float* const* peer_parts,
-                              int* const* peer_flags, int n_ranks, int rank, int step, const int* step_dev,
-                              int64_t parts_parity_stride, int64_t flags_parity_stride, int num_heads_q, int head_dim,
-                              float* out, float* lse_out, int phases) {
+int argus_b200_exchange_wait_merge(argus_b200_ctx* ctx, void* stream, const float* own_part, const argus_b200_exchange* xc,
+                                   int step, int num_heads_q, int num_heads_kv, int head_dim, float* out) {
     if (!ctx) return ARGUS_B200_E_INVALID;
-    if (!local_part || !peer_parts || !peer_flags || !out || n_ranks <= 0 || n_ranks > argus::kMaxRanks || rank < 0 ||
-        rank >= n_ranks || num_heads_q <= 0 || head_dim <= 0 || (step <= 0 && !step_dev) || (phases & 3) == 0) {
-        C_(ctx)->set_error("exchange_merge: bad arguments (n_ranks=%d rank=%d step=%d)", n_ranks, rank, step);
+    Context* c = C_(ctx);
+    c->err[0] = 0;
+    if (!own_part || !xc || !out || !xc->peer_lines || xc->n_ranks <= 0 || xc->n_ranks > argus::kMaxRanks || xc->rank < 0 ||
+        xc->rank >= xc->n_ranks || step <= 0 || num_heads_q <= 0 || num_heads_kv <= 0 || num_heads_q % num_heads_kv != 0 ||
+        head_dim <= 0 || !xc->peer_lines[xc->rank]) {
+        c->set_error("exchange_wait_merge: bad arguments (n_ranks=%d rank=%d step=%d)", xc ? xc->n_ranks : 0, xc ? xc->rank : 0,
+                     step);
         return ARGUS_B200_E_INVALID;
     }
-    argus::ExchangeParams p;
+    argus::ExchangeWaitParams p;
     memset(&p, 0, sizeof(p));
-    for (int s = 0; s < n_ranks; ++s) {
-        if (!peer_parts[s] || !peer_flags[s]) return ARGUS_B200_E_INVALID;
-        p.peer_parts[s] = peer_parts[s];
-        p.peer_flags[s] = peer_flags[s];
-    }
-    p.local_part = local_part;
+    for (int s = 0; s < xc->n_ranks; ++s) p.xc.lines[s] = xc->peer_lines[s];
+    p.xc.merged_lse = xc->merged_lse;
+    p.xc.parity_stride_lines = xc->parity_stride_lines;
+    p.xc.n_ranks = xc->n_ranks;
+    p.xc.rank = xc->rank;
     p.out = out;
-    p.lse_out = lse_out;
-    p.status = C_(ctx)->status;
-    p.n_ranks = n_ranks;
-    p.rank = rank;
-    p.step = step;
-    p.step_dev = step_dev;
-    p.parts_parity_stride = parts_parity_stride;
-    p.flags_parity_stride = flags_parity_stride;
+    p.status = c->status;
     p.hq = num_heads_q;
+    p.hkv = num_heads_kv;
     p.d = head_dim;
-    p.phases = phases;
-    cudaError_t e = argus::launch_exchange_merge(p, static_cast<cudaStream_t>(stream));
-    if (e != cudaSuccess) return C_(ctx)->cuda_fail(e, "exchange_merge launch");
-    C_(ctx)->launches += 1;
-    return ARGUS_B200_OK;
-}
-
-int argus_b200_step_increment(argus_b200_ctx* ctx, void* stream, int* step_dev) {
-    if (!ctx || !step_dev) return ARGUS_B200_E_INVALID;
-    cudaError_t e = argus::launch_step_increment(step_dev, static_cast<cudaStream_t>(stream));
-    if (e != cudaSuccess) return C_(ctx)->cuda_fail(e, "step_increment launch");
-    C_(ctx)->launches += 1;
+    p.step = step;
+    cudaError_t e = argus::launch_exchange_wait_merge(p, own_part, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return c->cuda_fail(e, "exchange_wait_merge launch");
+    c->launches += 1;
     return ARGUS_B200_OK;
 }
 

@@ -18,92 +18,125 @@ struct EpilogueSmem {
     static constexpr int BYTES = WARP_MERGE_B > SPLIT_MERGE_B ? WARP_MERGE_B : SPLIT_MERGE_B;
 };
 
-// Flag words of the peer exchange are written and read with release / acquire semantics at system scope.
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
+// Optional time stamps of the exchange tail (compiled in with -DARGUS_XC_PROFILE only): g_xc_prof[kv][stage] in ns.
+#ifdef ARGUS_XC_PROFILE
+__device__ unsigned long long g_xc_prof[64 * 8];
+#define XC_STAMP(i) { if (threadIdx.x == 0 && kv < 64) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_xc_prof[kv * 8 + (i)] = t_; } }
+#else
+#define XC_STAMP(i)
+#endif
 
-// Sequence-sharded decode, run by every thread of the CTA that completed KV head `kv` after it has written the head
-// group's normalised rows and their natural-log lse into this rank's OWN slot of its receive buffer:
-//   push  - copy the g rows + lse into slot `rank` of every other rank's receive buffer with plain peer stores (no
-//           multicast, no bulk copy), fence at system scope, then raise flag[rank][head] = step on every rank;
-//   merge - wait, with an iteration limit, for flag[s][head] >= step of every rank s in this rank's own flag array
-//           and merge the n_ranks rows of each head (same algebra as the split merge above, natural-log lse).
-// Only data of this CTA's own heads is waited for, so no CTA of a launch depends on another CTA of the same launch
-// and ranks only depend on pushes, which never wait. A wait that runs out zeroes the heads' output and sets the
-// status word to 3. Requires Hq % 4 == 0 and parity strides that are multiples of 4 (16-byte rows).
-template <int D, int WARPS>
-__device__ __forceinline__ void peer_exchange_tail(const DecodeParams& p, int kv, int step, long long poff, long long foff) {
-    constexpr int NT = WARPS * 32;
-    const PeerExchange& x = p.xc;
-    const int hq = p.hq, g = p.group, h0 = kv * g;
-    const long long part_len = (long long)hq * D + hq;
-    __shared__ int xc_ok;
-    if (threadIdx.x == 0) xc_ok = 1;
-    __syncthreads();   // the rows and lse written by this CTA are visible to all its threads
-    if (x.phases & 1) {
-        const float* own = x.parts[x.rank] + poff + x.rank * part_len;
-        const int n4 = g * D / 4;
-        for (int s = 0; s < x.n_ranks; ++s) {
-            if (s == x.rank) continue;
-            float* dst = x.parts[s] + poff + x.rank * part_len;
-            for (int e = threadIdx.x; e < n4; e += NT)
-                reinterpret_cast<float4*>(dst + (long long)h0 * D)[e] = __ldcg(reinterpret_cast<const float4*>(own + (long long)h0 * D) + e);
-            if (threadIdx.x < g) dst[(long long)hq * D + h0 + threadIdx.x] = __ldcg(own + (long long)hq * D + h0 + threadIdx.x);
-        }
-        __threadfence_system();
-        __syncthreads();
-        for (int i = threadIdx.x; i < x.n_ranks * g; i += NT) {
-            __threadfence_system();
-            st_release_sys(x.flags[i / g] + foff + x.rank * hq + h0 + (i % g), step);
+// ───────── sequence-sharded decode: exchange of the (o, lse) rows of one KV head's query heads ─────────
+// Every 16-byte line that crosses NVLink carries its own arrival flags: {float a, int step, float b, int step}. A peer
+// store of 8 aligned bytes becomes visible as a whole, so a reader that finds `step` in both flag words of a line has
+// both floats, with no fence on either side and no separate flag traffic: the latency of an exchange is one store
+// plus one NVLink crossing (measured on two B200s: about 5 us for the whole tail, against 33 us for "store rows,
+// fence at system scope, store flags, poll flags, read rows"). Flags are step numbers, so nothing is ever cleared: a
+// line of the buffer set that step n uses last held step n-2.
+//
+// The head group's data is the float sequence [g rows of D outputs | g natural-log lse values] = g*(D+1) floats,
+// two per line. Rank r's receive buffer holds, per buffer set, [n_ranks][Hkv][lines_per_head] lines.
+__host__ __device__ constexpr int xc_lines_per_head(int g, int d) { return (g * (d + 1) + 1) / 2; }
+// floats between two ranks' slots in the shared-memory region (a multiple of 4: the rows are written as float4)
+__host__ __device__ constexpr int xc_slot_floats(int g, int d) { return (g * (d + 1) + 3) & ~3; }
+
+// Push: `stage` holds this CTA's g*(D+1) floats (shared or global memory); they go to slot `rank` of every other rank.
+template <int NT>
+__device__ __forceinline__ void xc_push(const PeerExchange& x, const float* stage, int kv, int hkv, int g, int d, int step,
+                                        long long poff) {
+    const int nf = g * (d + 1), lph = xc_lines_per_head(g, d);
+    for (int s = 0; s < x.n_ranks; ++s) {
+        if (s == x.rank) continue;
+        int4* dst = static_cast<int4*>(x.lines[s]) + poff + ((long long)x.rank * hkv + kv) * lph;
+        for (int i = threadIdx.x; i < lph; i += NT) {
+            const float a = stage[2 * i], b = (2 * i + 1 < nf) ? stage[2 * i + 1] : 0.f;
+            // volatile: one 16-byte store, not to be split, merged or deferred by the compiler
+            asm volatile("st.volatile.global.v4.s32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "r"(__float_as_int(a)), "r"(step),
+                         "r"(__float_as_int(b)), "r"(step)
+                         : "memory");
         }
     }
-    if (x.phases & 2) {
-        for (int i = threadIdx.x; i < x.n_ranks * g; i += NT) {
-            const int* f = x.flags[x.rank] + foff + (i / g) * hq + h0 + (i % g);
+}
+
+// Wait + merge: collects the other ranks' lines of KV head `kv` from this rank's own receive buffer into `rows`
+// ([n_ranks][xc_slot_floats] floats of shared memory; slot `rank` is filled by the caller), every wait bounded, then merges:
+// M = max finite lse, w = exp(lse - M), out = sum w*o / sum w (engine/src/backend/cpu/neon.rs:1028-1125 in (o, lse)
+// form). Returns false, for every thread, when a line never arrived (the caller reports it; the output is zeroed).
+template <int NT>
+__device__ __forceinline__ bool xc_wait_merge(const PeerExchange& x, float* rows, int* ok_flag, int kv, int hq, int hkv, int g,
+                                              int d, int step, long long poff, float* out, float* merged_lse) {
+    const int nf = g * (d + 1), nfp = xc_slot_floats(g, d), lph = xc_lines_per_head(g, d), h0 = kv * g;
+    if (threadIdx.x == 0) *ok_flag = 1;
+    __syncthreads();
+    for (int s = 0; s < x.n_ranks; ++s) {
+        if (s == x.rank) continue;
+        const int4* src = static_cast<const int4*>(x.lines[x.rank]) + poff + ((long long)s * hkv + kv) * lph;
+        for (int i = threadIdx.x; i < lph; i += NT) {
+            int4 v;
             bool ok = false;
-            for (int it = 0; it < (1 << 21); ++it) {   // about a second before giving up
-                if (ld_acquire_sys(f) >= step) {
+            for (int it = 0; it < (1 << 20); ++it) {   // about a second before giving up
+                asm volatile("ld.volatile.global.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i) : "memory");
+                if (v.y == step && v.w == step) {
                     ok = true;
                     break;
                 }
-                if (it > 2048) __nanosleep(256);
+                if (it > 256) __nanosleep(it > 4096 ? 1000 : 100);
             }
-            __threadfence_system();
-            if (!ok) {
-                xc_ok = 0;
-                if (p.status != nullptr) atomicExch(p.status, 3);
-            }
-        }
-        __syncthreads();
-        const bool ok_all = xc_ok != 0;
-        const float* parts = x.parts[x.rank] + poff;
-        for (int e = threadIdx.x; e < g * D; e += NT) {
-            const int h = h0 + e / D, c = e % D;
-            float M = -INFINITY;
-            for (int s = 0; s < x.n_ranks; ++s) {
-                const float l = __ldcv(parts + s * part_len + (long long)hq * D + h);
-                if (isfinite(l) && l > M) M = l;
-            }
-            float W = 0.f, acc = 0.f;
-            for (int s = 0; s < x.n_ranks; ++s) {
-                const float l = __ldcv(parts + s * part_len + (long long)hq * D + h);
-                if (isfinite(l)) {
-                    const float w = expf(l - M);
-                    W += w;
-                    acc += w * __ldcv(parts + s * part_len + (long long)h * D + c);
-                }
-            }
-            p.out[(long long)h * D + c] = (ok_all && W > 0.f) ? acc / W : 0.f;
-            if (c == 0 && x.merged_lse != nullptr) x.merged_lse[h] = (ok_all && W > 0.f) ? M + logf(W) : -INFINITY;
+            if (!ok) *ok_flag = 0;
+            rows[s * nfp + 2 * i] = __int_as_float(v.x);
+            if (2 * i + 1 < nf) rows[s * nfp + 2 * i + 1] = __int_as_float(v.z);
         }
     }
+    __syncthreads();
+    const bool ok_all = *ok_flag != 0;
+    for (int e = threadIdx.x; e < g * d; e += NT) {
+        const int r = e / d;
+        float M = -INFINITY;
+        for (int s = 0; s < x.n_ranks; ++s) {
+            const float l = rows[s * nfp + g * d + r];
+            if (isfinite(l) && l > M) M = l;
+        }
+        float W = 0.f, acc = 0.f;
+        for (int s = 0; s < x.n_ranks; ++s) {
+            const float l = rows[s * nfp + g * d + r];
+            if (isfinite(l)) {
+                const float w = expf(l - M);
+                W += w;
+                acc += w * rows[s * nfp + e];
+            }
+        }
+        out[(long long)h0 * d + e] = (ok_all && W > 0.f) ? acc / W : 0.f;
+        if (e % d == 0 && merged_lse != nullptr) merged_lse[h0 + r] = (ok_all && W > 0.f) ? M + logf(W) : -INFINITY;
+    }
+    return ok_all;
+}
+
+// Shared-memory region of the exchange inside a decode CTA: behind the split-merge tables, [n_ranks][xc_slot_floats].
+constexpr int kXcSmemOff = kMaxSplits * 8 * 8 + 256;
+__host__ __device__ constexpr size_t xc_smem_end(int n_ranks, int g, int d) {
+    return (size_t)kXcSmemOff + (size_t)n_ranks * xc_slot_floats(g, d) * sizeof(float);
+}
+
+// Run by every thread of the CTA that completed KV head `kv`, after it has written the head group's normalised rows
+// and lse into slot `rank` of the shared-memory region. Only data of this CTA's own heads is waited for, so no CTA of a
+// launch depends on another CTA of the same launch, and ranks only depend on pushes, which never wait.
+template <int D, int WARPS>
+__device__ __forceinline__ void peer_exchange_tail(uint8_t* smem, const DecodeParams& p, int kv, int step, long long poff) {
+    constexpr int NT = WARPS * 32;
+    const PeerExchange& x = p.xc;
+    const int g = p.group, nfp = xc_slot_floats(g, D);
+    float* rows = reinterpret_cast<float*>(smem + kXcSmemOff);
+    __shared__ int xc_ok;
+    __syncthreads();   // the rows and lse written by this CTA are visible to all its threads
+    XC_STAMP(0)
+    if (x.phases & 1) xc_push<NT>(x, rows + x.rank * nfp, kv, p.hkv, g, D, step, poff);
+    XC_STAMP(1)
+    if (x.phases & 2) {
+        const bool ok = xc_wait_merge<NT>(x, rows, &xc_ok, kv, p.hq, p.hkv, g, D, step, poff, p.out, x.merged_lse);
+        if (!ok && threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, 3);
+    }
     __syncthreads();   // every thread has read the step counter's old value (the caller did) and is done with it
+    XC_STAMP(2)
     if (threadIdx.x == 0) x.step_ctr[kv] = step;
 }
 
@@ -119,19 +152,20 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
     float* sm_o = reinterpret_cast<float*>(smem + EpilogueSmem<D, WARPS>::O_OFF);
     float2* sm_ml = reinterpret_cast<float2*>(smem + EpilogueSmem<D, WARPS>::ML_OFF);
     int* sm_flag = reinterpret_cast<int*>(smem + EpilogueSmem<D, WARPS>::FLAG_OFF);
-    // Sharded decode: the completing CTA writes the final rows into its own slot of the receive buffer (the buffer set
-    // follows the parity of the step number kept in device memory), then pushes and merges (peer_exchange_tail).
+    // Sharded decode: the completing CTA writes the final rows and lse into slot `rank` of the exchange region in shared
+    // memory (rows [g][D], then [g] lse), then pushes and merges (peer_exchange_tail). The buffer set on the peers
+    // follows the parity of the step number kept in device memory.
     const bool xchg = p.xc.n_ranks > 0;
     float* out_base = p.out;
     float* lse_base = p.lse;
     int xc_step = 0;
-    long long xc_poff = 0, xc_foff = 0;
+    long long xc_poff = 0;
     auto bind_exchange = [&]() {
         xc_step = __ldcg(p.xc.step_ctr + kv) + 1;
-        xc_poff = (xc_step & 1) ? p.xc.parts_parity_stride : 0;
-        xc_foff = (xc_step & 1) ? p.xc.flags_parity_stride : 0;
-        out_base = p.xc.parts[p.xc.rank] + xc_poff + p.xc.rank * ((long long)p.hq * D + p.hq);
-        lse_base = out_base + (long long)p.hq * D;
+        xc_poff = (xc_step & 1) ? p.xc.parity_stride_lines : 0;
+        float* stage = reinterpret_cast<float*>(smem + kXcSmemOff) + p.xc.rank * xc_slot_floats(p.group, D);
+        out_base = stage - (long long)kv * p.group * D;            // indexed below with (kv*g + h)*D + d; b is 0 here
+        lse_base = stage + p.group * D - (long long)kv * p.group;   // indexed with kv*g + h
     };
     if (xchg && n_splits == 1) bind_exchange();
     for (int e = threadIdx.x; e < p.group * D; e += WARPS * 32) {
@@ -162,7 +196,7 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
         }
     }
     if (n_splits == 1) {
-        if (xchg) peer_exchange_tail<D, WARPS>(p, kv, xc_step, xc_poff, xc_foff);
+        if (xchg) peer_exchange_tail<D, WARPS>(smem, p, kv, xc_step, xc_poff);
         return;
     }
 
@@ -255,7 +289,7 @@ __device__ __forceinline__ void decode_epilogue(uint8_t* smem, const DecodeParam
         }
     }
     if (threadIdx.x == 0) p.tickets[b * p.hkv + kv] = 0;   // ready for the next call
-    if (xchg) peer_exchange_tail<D, WARPS>(p, kv, xc_step, xc_poff, xc_foff);
+    if (xchg) peer_exchange_tail<D, WARPS>(smem, p, kv, xc_step, xc_poff);
 }
 
 }  // namespace argus

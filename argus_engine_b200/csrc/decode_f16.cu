@@ -274,6 +274,7 @@ static cudaError_t launch_decode_f16_t(const DecodeParams& p, const DecodeBatch&
     return cudaGetLastError();
 }
 
+int decode_f16_smem_bytes(int head_dim) { return head_dim == 64 ? DecodeF16Cfg<64, 4, 4>::SMEM_B : DecodeF16Cfg<128, 4, 3>::SMEM_B; }
 int decode_f16_cta_tokens(int head_dim) { return head_dim == 64 ? DecodeF16Cfg<64, 4, 4>::CTA_TOK : DecodeF16Cfg<128, 4, 3>::CTA_TOK; }
 
 cudaError_t launch_decode_f16(const DecodeParams& p, const DecodeBatch& bt, int head_dim, int n_items, cudaStream_t st) {
@@ -293,5 +294,11 @@ cudaError_t launch_finalize_scores(const FinalizeParams& f, int max_len, cudaStr
     finalize_scores_kernel<<<grid, 256, 0, st>>>(f);
     return cudaGetLastError();
 }
+
+#ifdef ARGUS_XC_PROFILE
+extern "C" __attribute__((visibility("default"))) int argus_b200_debug_xc_profile(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_xc_prof, sizeof(g_xc_prof));
+}
+#endif
 
 }  // namespace argus

@@ -45,17 +45,15 @@ struct KiviBatch {
 };
 
 // Sequence-sharded decode (one sequence, one KV slice per GPU): the CTA that completes a KV head pushes the head
-// group's normalised rows and lse into slot `rank` of every rank's receive buffer, raises the flags, and (phase 2)
-// waits for all ranks' flags in its own memory and merges. n_ranks == 0 switches all of it off.
+// group's normalised rows and lse into slot `rank` of every rank's receive buffer and (phase 2) collects the other
+// ranks' rows from its own buffer and merges. n_ranks == 0 switches all of it off. Layout: decode_epilogue.cuh.
 constexpr int kMaxRanks = 16;
 struct PeerExchange {
-    float* parts[kMaxRanks];        // receive buffer [n_ranks][Hq*D+Hq] of every rank (own entry = local memory)
-    int* flags[kMaxRanks];          // flag array [n_ranks][Hq] of every rank
-    int* step_ctr;                  // [Hkv] step counters in this rank's memory; the completing CTA of a KV head bumps its own
-    float* merged_lse;              // [Hq] natural-log lse of the merged result, nullable
-    long long parts_parity_stride;  // floats between the even-step and the odd-step receive buffers
-    long long flags_parity_stride;  // ints between the even-step and the odd-step flag arrays
-    int n_ranks, rank, phases;      // phases: 1 = push, 2 = wait + merge, 3 = both
+    void* lines[kMaxRanks];          // receive buffer of every rank: 2 sets of [n_ranks][Hkv][lines_per_head] 16-byte lines
+    int* step_ctr;                   // [Hkv] step counters in this rank's memory; the completing CTA of a KV head bumps its own
+    float* merged_lse;               // [Hq] natural-log lse of the merged result, nullable
+    long long parity_stride_lines;   // lines between the even-step and the odd-step buffer set
+    int n_ranks, rank, phases;       // phases: 1 = push, 2 = wait + merge, 3 = both
 };
 
 struct DecodeParams {
@@ -93,18 +91,13 @@ struct FinalizeParams {
     int32_t seq_len[kMaxBatch];
 };
 
-// Peer exchange + merge of a sequence-sharded decode as a kernel of its own (exchange_merge.cu).
-struct ExchangeParams {
-    float* peer_parts[kMaxRanks];   // receive buffer [n_ranks][Hq*D+Hq] of every rank (own entry = local memory)
-    int* peer_flags[kMaxRanks];     // flag array [n_ranks][Hq] of every rank
-    const float* local_part;        // this rank's partial: [Hq][D] outputs, then [Hq] lse
-    float* out;                     // [Hq][D]
-    float* lse_out;                 // [Hq], nullable
+// Wait + merge of a sequence-sharded decode as a kernel of its own (exchange_merge.cu): the second half of the
+// exchange for callers that ran the decode with phases = 1.
+struct ExchangeWaitParams {
+    PeerExchange xc;
+    float* out;      // [Hq][D]
     int* status;
-    const int* step_dev;            // nullable: step number in device memory (CUDA-graph replay)
-    long long parts_parity_stride;  // floats between the even-step and the odd-step receive buffers
-    long long flags_parity_stride;  // ints between the even-step and the odd-step flag arrays
-    int n_ranks, rank, step, hq, d, phases;
+    int hq, hkv, d, step;
 };
 
 }  // namespace argus

@@ -349,6 +349,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // ───────── warps 2..3: V tile BF16 -> F16 in place (VCONV only), otherwise idle ─────────
         if constexpr (VCONV) {
             const int t64 = threadIdx.x - 64;   // 0..63
+            bool clamped = false;   // a finite BF16 value beyond the F16 range met the saturating conversion
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j % V_STAGES;
                 if (*abort_flag || !mbar_wait(b_vfull(s), (j / V_STAGES) & 1)) { fail(); break; }
@@ -362,6 +363,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         const float lo = __uint_as_float(e[k] << 16), hi = __uint_as_float(e[k] & 0xffff0000u);
                         uint32_t r;
                         asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+                        clamped |= fmaxf(fabsf(lo), fabsf(hi)) > 65504.0f;   // false for NaN; the BF16 infinities count too
                         e[k] = r;
                     }
                     tile[t64 + 64 * i] = w;
@@ -369,6 +371,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(b_vconv(s));
             }
+            // informational status 4, never over an error code already there
+            if (clamped && p.status != nullptr) atomicCAS(p.status, 0, 4);
         }
     } else {
         // ───────── softmax / correction / epilogue: one query row per thread ─────────

@@ -44,7 +44,6 @@ class ShardedDecoder:
         self.part_len = num_heads_q * head_dim + num_heads_q
         self.part = torch.zeros(self.part_len, dtype=torch.float32, device=device)
         self.parts = torch.zeros(self.world, self.part_len, dtype=torch.float32, device=device)
-        self.exchange_fn = None     # set by make_gpu_decoder(..., fused="two_kernels"): replaces gather + merge
         self.fused_step_fn = None   # set by make_gpu_decoder(..., fused=True): replaces the whole step
 
     def capture(self, q: torch.Tensor, out: torch.Tensor):
@@ -67,9 +66,6 @@ class ShardedDecoder:
             self.fused_step_fn(q, out)
             return
         self.partial_fn(q, self.part)
-        if self.exchange_fn is not None:
-            self.exchange_fn(self.part, out)
-            return
         if self.world > 1:
             dist.all_gather_into_tensor(self.parts.view(-1), self.part, group=self.group)
         else:
@@ -78,27 +74,24 @@ class ShardedDecoder:
 
 
 class PeerBuffers:
-    """Receive buffers and flags of the fused exchange, in memory every rank of the node can address
-    (torch symmetric memory over NVLink). Layout per rank, in 4-byte words: two sets (even / odd steps) of
-    parts [N][Hq*D+Hq] floats, then two sets of flags [N][Hq] ints, all zero-initialised."""
+    """Receive buffers of the in-kernel exchange, in memory every rank of the node can address (torch symmetric memory
+    over NVLink). Per rank: two sets (even / odd steps) of [N][Hkv][lines_per_head] 16-byte lines {float, step, float,
+    step}, zero-initialised; see argus_b200_attention_gen_sharded in the C header."""
 
-    def __init__(self, num_heads_q: int, head_dim: int, group=None):
+    def __init__(self, be, num_heads_q: int, num_heads_kv: int, head_dim: int, group=None):
         import torch.distributed._symmetric_memory as symm_mem
 
         group = group or dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        part_len = num_heads_q * head_dim + num_heads_q
-        self.parts_stride = self.world * part_len
-        self.flags_stride = self.world * num_heads_q
-        n_words = 2 * self.parts_stride + 2 * self.flags_stride
-        self.buf = symm_mem.empty(n_words, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        lph = be.exchange_lines_per_head(num_heads_q, num_heads_kv, head_dim)
+        self.parity_stride_lines = self.world * num_heads_kv * lph
+        n_words = 2 * self.parity_stride_lines * 4
+        self.buf = symm_mem.empty(n_words, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group.group_name)
         torch.cuda.synchronize()
         dist.barrier(group)
-        bases = [int(p) for p in self.handle.buffer_ptrs]
-        self.peer_parts = bases
-        self.peer_flags = [b + 4 * 2 * self.parts_stride for b in bases]
+        self.peer_lines = [int(p) for p in self.handle.buffer_ptrs]
 
 
 def make_gpu_decoder(be, k_shard: torch.Tensor, v_shard: torch.Tensor, shard_len: int, num_heads_q: int,
@@ -106,9 +99,8 @@ def make_gpu_decoder(be, k_shard: torch.Tensor, v_shard: torch.Tensor, shard_len
     """ShardedDecoder over the CUDA kernels of `be` (a B200Backend) for an F16 HeadMajor shard.
     fused=False: decode kernel, ONE NCCL all-gather into each rank's own memory, merge kernel.
     fused=True: ONE launch per step (argus_b200_attention_gen_sharded): the CTA of the decode kernel that completes a
-    KV head stores the head group's (o, lse) rows into every rank's receive buffer over NVLink peer pointers, waits
-    (bounded) for the other ranks' rows of those heads and merges them. The step number lives in device memory.
-    fused="two_kernels": decode kernel, then argus_b200_exchange_merge (push + wait + merge as a kernel of its own)."""
+    KV head stores the head group's (o, lse) rows into every rank's receive buffer over NVLink peer pointers, collects
+    (bounded) the other ranks' rows of those heads and merges them. The step number lives in device memory."""
     from .backend import DecodeExtras
 
     hq, d = num_heads_q, head_dim
@@ -121,26 +113,15 @@ def make_gpu_decoder(be, k_shard: torch.Tensor, v_shard: torch.Tensor, shard_len
         be.lse_merge(parts, hq, d, out)
 
     dec = ShardedDecoder(hq, d, partial_fn, merge_fn, k_shard.device, group)
-    if fused is True and dec.world > 1:
-        peers = PeerBuffers(hq, d, group)
+    if fused and dec.world > 1:
+        peers = PeerBuffers(be, hq, num_heads_kv, d, group)
         counters = torch.zeros(num_heads_kv, dtype=torch.int32, device=k_shard.device)
 
         def fused_step_fn(q, out):
-            be.attention_gen_sharded(q, k_shard, v_shard, out, hq, num_heads_kv, d, shard_len, peers.peer_parts,
-                                     peers.peer_flags, peers.rank, counters, peers.parts_stride, peers.flags_stride)
+            be.attention_gen_sharded(q, k_shard, v_shard, out, hq, num_heads_kv, d, shard_len, peers.peer_lines, peers.rank,
+                                     counters, peers.parity_stride_lines)
 
         dec.fused_step_fn = fused_step_fn
         dec._peers = peers   # keep the symmetric allocation alive
         dec._counters = counters
-    elif fused and dec.world > 1:
-        peers = PeerBuffers(hq, d, group)
-        step_dev = torch.zeros(1, dtype=torch.int32, device=k_shard.device)
-
-        def exchange_fn(part, out):
-            be.step_increment(step_dev)   # the step number lives on the device so that a CUDA graph can replay this
-            be.exchange_merge(part, peers.peer_parts, peers.peer_flags, peers.rank, hq, d, out, step_dev=step_dev,
-                              parts_parity_stride=peers.parts_stride, flags_parity_stride=peers.flags_stride)
-
-        dec.exchange_fn = exchange_fn
-        dec._peers = peers   # keep the symmetric allocation alive
     return dec

@@ -126,10 +126,13 @@ class ClockSampler(threading.Thread):
 
 # ───────────────────────────── headline workload: 1M-token decode, sharded by sequence ─────────────────────────────
 
+TOKENS_OVERRIDE = None   # --tokens: a shorter cache of the same shape, for profiler captures of a small case
+
+
 def c5_shape():
     from argus_engine_b200 import workloads as wl
 
-    return wl.C5_T, wl.C5_HQ, wl.C5_HKV, wl.C5_D
+    return (TOKENS_OVERRIDE or wl.C5_T), wl.C5_HQ, wl.C5_HKV, wl.C5_D
 
 
 def c5_bytes(tokens=None) -> int:
@@ -264,17 +267,15 @@ def headline_c5(be, dist, world, rank, args, peaks, sampler):
     exchange = "none (one GPU)"
     dec = None
     if world > 1:
-        mode = os.environ.get("ARGUS_B200_SHARDED_EXCHANGE", "fused")   # fused | two_kernels | nccl
-        fused = {"fused": True, "two_kernels": "two_kernels", "nccl": False}[mode]
+        fused = os.environ.get("ARGUS_B200_SHARDED_EXCHANGE", "fused") != "nccl"
         try:
             dec = make_gpu_decoder(be, k, v, n_local, hq, hkv, d, fused=fused)
         except Exception as e:   # symmetric memory unavailable: NCCL all-gather + merge kernel
             sys.stderr.write(f"[bench] peer buffers unavailable ({e}); using the NCCL gather\n")
             fused = False
             dec = make_gpu_decoder(be, k, v, n_local, hq, hkv, d)
-        exchange = {True: "peer push + wait + merge in the decode kernel's epilogue (one launch per step)",
-                    "two_kernels": "decode kernel, then one peer-exchange + merge kernel",
-                    False: "decode kernel, NCCL all-gather, merge kernel"}[fused]
+        exchange = ("flagged 16-byte lines pushed to the peers, collected and merged in the decode kernel's epilogue "
+                    "(one launch per step)" if fused else "decode kernel, NCCL all-gather, merge kernel")
         step = lambda: dec.step(q, out)   # noqa: E731
     else:
         step = lambda: be.attention_gen(q, k, v, out, hq, hkv, d, n_local)   # noqa: E731
@@ -886,7 +887,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--others", default="c2,c1,c3,c4,kv", help="comma list of further configurations to time at N=1 ('' = none)")
+    ap.add_argument("--tokens", type=int, default=0, help="cached tokens of the headline workload (default 2^20); a smaller "
+                    "multiple of 65536 gives the small case a profiler capture wants")
     args = ap.parse_args()
+    if args.tokens:
+        global TOKENS_OVERRIDE
+        TOKENS_OVERRIDE = int(args.tokens)
     if args.impl == "reference":
         if args.steps == 200:
             args.steps = 10

@@ -59,12 +59,10 @@ pub struct ArgusB200KiviSeq {
 /// `argus_b200_exchange`: peer buffers of a sequence-sharded decode step.
 #[repr(C)]
 pub struct ArgusB200Exchange {
-    pub peer_parts: *const *mut f32,
-    pub peer_flags: *const *mut c_int,
+    pub peer_lines: *const *mut c_void,
     pub step_counters: *mut c_int,
     pub merged_lse: *mut f32,
-    pub parts_parity_stride: i64,
-    pub flags_parity_stride: i64,
+    pub parity_stride_lines: i64,
     pub n_ranks: c_int,
     pub rank: c_int,
     pub phases: c_int,
@@ -105,13 +103,11 @@ extern "C" {
         out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, res_cap: c_int, bits: c_int,
         res_dtype: c_int, scale: f32, extras: *const ArgusB200DecodeExtras,
     ) -> c_int;
-    pub fn argus_b200_exchange_merge(
-        ctx: *mut ArgusB200Ctx, stream: *mut c_void, local_part: *const f32, peer_parts: *const *mut f32,
-        peer_flags: *const *mut c_int, n_ranks: c_int, rank: c_int, step: c_int, step_dev: *const c_int,
-        parts_parity_stride: i64, flags_parity_stride: i64, num_heads_q: c_int, head_dim: c_int, out: *mut f32,
-        lse_out: *mut f32, phases: c_int,
+    pub fn argus_b200_exchange_wait_merge(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, own_part: *const f32, exchange: *const ArgusB200Exchange, step: c_int,
+        num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, out: *mut f32,
     ) -> c_int;
-    pub fn argus_b200_step_increment(ctx: *mut ArgusB200Ctx, stream: *mut c_void, step_dev: *mut c_int) -> c_int;
+    pub fn argus_b200_exchange_lines_per_head(num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int) -> c_int;
     pub fn argus_b200_attention_gen_sharded(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, k_shard: *const c_void, v_shard: *const c_void,
         out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, shard_len: i64, kv_dtype: c_int,
@@ -306,7 +302,7 @@ const _: () = assert!(std::mem::size_of::<CudaScoreReduceArgs>() == 96);
 const _: () = assert!(std::mem::size_of::<ArgusB200DecodeExtras>() == 48);
 const _: () = assert!(std::mem::size_of::<ArgusB200Seq>() == 40);
 const _: () = assert!(std::mem::size_of::<ArgusB200KiviSeq>() == 48);
-const _: () = assert!(std::mem::size_of::<ArgusB200Exchange>() == 64);
+const _: () = assert!(std::mem::size_of::<ArgusB200Exchange>() == 48);
 // Field offsets of the reference's PODs, as the C header's static_asserts state them.
 const _: () = assert!(std::mem::offset_of!(CudaQuantAttnArgs, scores_out) == 56);
 const _: () = assert!(std::mem::offset_of!(CudaQuantAttnArgs, scores_len) == 64);
@@ -321,4 +317,4 @@ const _: () = assert!(std::mem::offset_of!(CudaQuantScatterResidualArgs, kv_head
 const _: () = assert!(std::mem::offset_of!(CudaScoreReduceArgs, decay_factor) == 32);
 const _: () = assert!(std::mem::offset_of!(CudaScoreReduceArgs, n_layers) == 40);
 const _: () = assert!(std::mem::offset_of!(CudaScoreReduceArgs, layer_flat_importance) == 88);
-const _: () = assert!(std::mem::offset_of!(ArgusB200Exchange, n_ranks) == 48);
+const _: () = assert!(std::mem::offset_of!(ArgusB200Exchange, n_ranks) == 32);

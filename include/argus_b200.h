@@ -283,7 +283,11 @@ ARGUS_B200_API int argus_b200_score_reduce_per_layer(argus_b200_ctx* ctx, const 
  * [batch][Hkv][kv_capacity][D] when is_head_major, else [batch][kv_capacity][Hkv][D]. Query row r sees keys
  * 0..=cache_seq_len-seq_len+r; scale = 1/sqrt(D). Returns ARGUS_B200_E_UNSUPPORTED for head_dim != 128
  * (the reference's `Ok(false)`: the caller keeps its own route). In the F32-Q mode Q is first rounded to
- * F16 into context scratch (batch*seq_len*Hq*D*2 bytes). */
+ * F16 into context scratch (batch*seq_len*Hq*D*2 bytes).
+ * In the BF16 mode V is multiplied as an F16 copy made tile by tile in shared memory (the probabilities need F16's 11
+ * bits to hold the 2e-3 tolerance, and both operands of one MMA share a type): exact for |v| <= 65504, clamped to
+ * +-65504 beyond. When that happens the status word reads 4 afterwards (argus_b200_check_status); the output is then
+ * computed from the clamped values. */
 ARGUS_B200_API int argus_b200_flash_attention_prefill(argus_b200_ctx* ctx, void* stream, const void* q,
                                                       const void* k_cache, const void* v_cache, void* out,
                                                       int n_heads_q, int n_heads_kv, int seq_len,
@@ -301,47 +305,33 @@ ARGUS_B200_API int argus_b200_lse_merge(argus_b200_ctx* ctx, void* stream, const
                                         int64_t part_stride, int num_heads_q, int head_dim, float* out,
                                         float* lse_out);
 
-/* The same merge with the exchange fused in: instead of an all-gather, CTA h of every rank stores row h of its
- * partial into slot `rank` of EVERY rank's receive buffer through NVLink peer pointers, raises a per-(rank, head)
- * flag there to `step`, waits (bounded) for the flags of all ranks in its own flag array and merges. No
- * counterpart in the reference (single device). peer_parts[s] / peer_flags[s] are device pointers valid on this
- * GPU to rank s's receive buffer [n_ranks][Hq*D+Hq] floats and flag array [n_ranks][Hq] ints (zero-initialised
- * once; e.g. a torch symmetric-memory allocation). The step number must grow by one per call on all ranks alike
- * (starting at 1): pass it as `step`, or keep it in device memory (`step_dev`, bumped on the stream by
- * argus_b200_step_increment) so that the call can be replayed from a CUDA graph. Odd steps use the buffers
- * `*_parity_stride` elements behind the even ones, so that a fast rank's next push cannot overwrite what a slow
- * rank still merges. phases: 3 normally; 1 (push only) and 2 (wait + merge only) exist for single-GPU tests.
- * n_ranks <= 16. A wait that runs out zeroes the output and sets the status word. */
-ARGUS_B200_API int argus_b200_exchange_merge(argus_b200_ctx* ctx, void* stream, const float* local_part,
-                                             float* const* peer_parts, int* const* peer_flags, int n_ranks, int rank,
-                                             int step, const int* step_dev, int64_t parts_parity_stride,
-                                             int64_t flags_parity_stride, int num_heads_q, int head_dim, float* out,
-                                             float* lse_out, int phases);
-ARGUS_B200_API int argus_b200_step_increment(argus_b200_ctx* ctx, void* stream, int* step_dev);
-
 /* The whole step of a sequence-sharded decode in ONE launch: argus_b200_attention_gen over this rank's slice of the KV
  * sequence, whose split-merge epilogue also does the exchange. No counterpart in the reference (single device; the
- * algebra is the chunk merge of engine/src/backend/cpu/neon.rs:1028-1125). The CTA that completes a KV head writes the
- * head group's normalised rows and natural-log lse into slot `rank` of every rank's receive buffer with plain NVLink
- * peer stores (no multicast, no bulk copy on peer memory), raises flag[rank][head] to the step number there, then
- * waits - with an iteration limit - for the flags of all ranks in its OWN flag array and writes the merged rows to
- * `out` [Hq][D] (and `merged_lse` [Hq] if set). Buffers as for argus_b200_exchange_merge: peer_parts[s] / peer_flags[s]
- * are addresses valid on this GPU of rank s's receive buffer (two sets of [n_ranks][Hq*D+Hq] floats, `parts_parity_stride`
- * floats apart) and flag array (two sets of [n_ranks][Hq] ints), zero-initialised once. The step number lives in device
- * memory: `step_counters` is an int[Hkv] array of this rank, zero-initialised once, bumped by the kernel itself (one
- * counter per KV head), so the call replays from a CUDA graph and every rank must issue the same number of calls. Odd
- * steps use the second buffer set, so a fast rank's next push cannot overwrite what a slow rank still merges.
- * phases: 3 normally; 1 = push only (then argus_b200_exchange_merge with phases = 2 and the host's step number does the
- * wait + merge: the form single-GPU tests use, where no kernel may wait for a later launch). Hq must be a multiple
- * of 4; a shard may be empty (shard_len 0: lse = -inf, skipped by the merge). A wait that runs out zeroes the heads'
- * output and sets the status word to 3 (argus_b200_check_status). */
+ * algebra is the chunk merge of engine/src/backend/cpu/neon.rs:1028-1125). The CTA that completes a KV head stores the
+ * head group's normalised rows and natural-log lse into slot `rank` of every other rank's receive buffer with plain
+ * NVLink peer stores (no multicast, no bulk copy on peer memory), then collects - every wait bounded - the other
+ * ranks' rows of those heads from its OWN receive buffer and writes the merged rows to `out` [Hq][D] (and `merged_lse`
+ * [Hq] if set).
+ *
+ * Wire format: 16-byte lines {float a, int step, float b, int step}. An aligned 8-byte peer store becomes visible as a
+ * whole, so a reader that finds the current step number in both flag words of a line has both floats: no fence, no
+ * separate flag traffic, latency of one store plus one NVLink crossing. A head group's g*(D+1) floats ([g][D] outputs,
+ * then [g] lse) take lines_per_head = ceil(g*(D+1)/2) lines; a receive buffer is two sets (even / odd steps,
+ * `parity_stride_lines` lines apart) of [n_ranks][Hkv][lines_per_head] lines, zero-initialised once (steps start at 1).
+ * peer_lines[s] is the address, valid on this GPU, of rank s's receive buffer (e.g. a torch symmetric-memory
+ * allocation). The step number lives in device memory: `step_counters` is an int[Hkv] array of this rank,
+ * zero-initialised once and bumped by the kernel itself (one counter per KV head), so the call replays from a CUDA
+ * graph; every rank must issue the same sequence of calls. Odd steps use the second buffer set, so a fast rank's next
+ * push cannot overwrite what a slow rank still reads. phases: 3 normally; 1 = push only, after which
+ * argus_b200_exchange_wait_merge (with the host's step number and this rank's own (o, lse) partial) does the second
+ * half: the form single-GPU tests use, where no kernel may wait for a later launch. A shard may be empty (shard_len 0:
+ * lse = -inf, skipped by the merge). A wait that runs out (about a second) zeroes the heads' output and sets the status
+ * word to 3 (argus_b200_check_status). */
 typedef struct argus_b200_exchange {
-    float* const* peer_parts;
-    int* const* peer_flags;
+    void* const* peer_lines;
     int* step_counters;
     float* merged_lse;
-    int64_t parts_parity_stride;
-    int64_t flags_parity_stride;
+    int64_t parity_stride_lines;
     int n_ranks;
     int rank;
     int phases;
@@ -350,9 +340,19 @@ ARGUS_B200_API int argus_b200_attention_gen_sharded(argus_b200_ctx* ctx, void* s
                                                     const void* v_shard, float* out, int num_heads_q, int num_heads_kv,
                                                     int head_dim, int64_t shard_len, int kv_dtype, int64_t head_stride,
                                                     int64_t pos_stride, const argus_b200_exchange* exchange);
+/* Lines one head group occupies in a receive buffer (see above). */
+ARGUS_B200_API int argus_b200_exchange_lines_per_head(int num_heads_q, int num_heads_kv, int head_dim);
+/* The receiving half alone: one CTA per KV head waits (bounded) for the other ranks' lines of step `step` in this rank's
+ * receive buffer and merges them with `own_part` ([Hq][D] outputs then [Hq] lse, as argus_b200_attention_gen with
+ * extras.lse writes them) into out [Hq][D]. `exchange->step_counters` and `phases` are ignored. */
+ARGUS_B200_API int argus_b200_exchange_wait_merge(argus_b200_ctx* ctx, void* stream, const float* own_part,
+                                                  const argus_b200_exchange* exchange, int step, int num_heads_q,
+                                                  int num_heads_kv, int head_dim, float* out);
 
-/* Blocks until `stream` is idle and returns the status word the kernels set when one of their bounded
- * waits ran out (0 = clean). The word is cleared by the call. */
+/* Blocks until `stream` is idle and returns the status word the kernels set (0 = clean) and clears it:
+ * 1 / 2 a bounded wait inside a decode / prefill kernel ran out (the call's output is not valid), 2 also: an invalid
+ * entry in a compaction list, 3 a rank's flags never arrived in a sharded step (those heads are zero),
+ * 4 a BF16 prefill clamped V values beyond the F16 range (informational, set only when no error is pending). */
 ARGUS_B200_API int argus_b200_check_status(argus_b200_ctx* ctx, void* stream);
 
 /* ───────────── KV write and eviction executors on a device-resident cache ─────────────

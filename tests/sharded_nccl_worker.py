@@ -23,8 +23,8 @@ k = torch.from_numpy(np.ascontiguousarray(case.k[0][:, lo:hi])).cuda()
 v = torch.from_numpy(np.ascontiguousarray(case.v[0][:, lo:hi])).cuda()
 want, _ = orc.attention_gen(case.q[0], case.k[0].view(np.uint16), case.v[0].view(np.uint16), hq, hkv, d, T)
 qd = torch.from_numpy(case.q[0]).cuda()
-# NCCL all-gather + merge; decode + stand-alone peer exchange kernel; the single-launch step (plain peer stores)
-for fused in (False, "two_kernels", True):
+# NCCL all-gather + merge, then the single-launch step (flagged lines pushed with plain peer stores)
+for fused in (False, True):
     dec = make_gpu_decoder(be, k, v, hi - lo, hq, hkv, d, fused=fused)
     for _ in range(3):           # several steps: the fused paths alternate their two buffer sets
         out = torch.full((hq, d), float("nan"), device="cuda")

@@ -76,4 +76,4 @@ def test_ctypes_offsets_match_the_guards_of_the_header_and_crate():
     assert (df.kv_heads.offset, df.bits.offset, df.is_key.offset) == (24, 64, 65)
     sr = _lib.ScoreReduceArgs
     assert (sr.decay_factor.offset, sr.n_layers.offset, sr.layer_flat_importance.offset) == (32, 40, 88)
-    assert C.sizeof(_lib.ExchangeC) == 64 and _lib.ExchangeC.n_ranks.offset == 48
+    assert C.sizeof(_lib.ExchangeC) == 48 and _lib.ExchangeC.n_ranks.offset == 32

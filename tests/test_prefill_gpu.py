@@ -86,3 +86,29 @@ def test_prefill_declines_other_head_dims(be):
     q = torch.zeros(1, 16, 4, 64, dtype=torch.bfloat16, device="cuda")
     k = torch.zeros(1, 2, 16, 64, dtype=torch.bfloat16, device="cuda")
     assert be.flash_attention_prefill(q, k, k, torch.zeros_like(q), 4, 2, 16, 16, 64, 16, 1, True) is False
+
+
+def test_bf16_v_beyond_f16_range_is_clamped_and_reported(be):
+    """BF16 inputs are served with an F16 copy of each V tile: exact up to |v| = 65504 (largest finite F16), clamped
+    beyond, and the clamp is reported through the status word (4). With a single key the output row IS the V row, so
+    the boundary shows directly."""
+    B, S, hq, hkv, d = 1, 128, 4, 1, 128
+    case = wl.prefill_case(5, B, S, S, hq, hkv, d, dtype="bf16")
+    case.k[:] = 0                      # uniform attention: row r is the mean of V rows 0..=r
+    case.v[:] = 0
+    case.v[0, 0, 0, 0] = 65280.0       # the largest BF16 value below 65504: representable in both types
+    case.v[0, 0, 0, 1] = -65280.0
+    ok, got = _run(be, case, "bf16")
+    assert ok and be.check_status() == 0
+    assert got[0, 0, 0, 0] == 65280.0 and got[0, 0, 0, 1] == -65280.0
+    case.v[0, 0, 0, 2] = 131072.0      # finite in BF16, beyond F16
+    tq = torch.bfloat16
+    q, k, v = _t(case.q, tq), _t(case.k, tq), _t(case.v, tq)
+    out = torch.zeros(B, S, hq, d, dtype=tq, device="cuda")
+    assert be.flash_attention_prefill(q, k, v, out, hq, hkv, S, S, d, S, B, True)
+    torch.cuda.synchronize()
+    assert be.check_status() == 4
+    o = out.float().cpu().numpy()
+    assert o[0, 0, 0, 2] == 65504.0 or o[0, 0, 0, 2] == 65536.0   # the clamped value, rounded to BF16 on output
+    assert o[0, 0, 0, 0] == 65280.0
+    assert be.check_status() == 0      # cleared by the read
