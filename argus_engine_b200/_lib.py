@@ -60,6 +60,11 @@ class KiviSeq(C.Structure):
                 ("q_tokens", C.c_int64), ("res_tokens", C.c_int64)]
 
 
+class KiviPagedSeq(C.Structure):
+    _fields_ = [("flush_pages", C.c_void_p), ("res_k", C.c_void_p), ("res_v", C.c_void_p),
+                ("q_tokens", C.c_int64), ("res_tokens", C.c_int64)]
+
+
 class ExchangeC(C.Structure):
     """argus_b200_exchange."""
     _fields_ = [("peer_lines", C.POINTER(C.c_void_p)), ("step_counters", C.c_void_p), ("merged_lse", C.c_void_p),
@@ -111,6 +116,8 @@ def load_library() -> C.CDLL:
     lib.argus_b200_kivi_flush_pack.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i64]
     lib.argus_b200_kivi_attention_batched.argtypes = [vp, vp, vp, C.POINTER(KiviSeq), i32, vp, i32, i32, i32, i32, i32,
                                                       i32, C.c_float, C.POINTER(DecodeExtrasC)]
+    lib.argus_b200_kivi_attention_paged.argtypes = [vp, vp, vp, vp, vp, C.POINTER(KiviPagedSeq), i32, vp, i32, i32, i32,
+                                                    i32, i32, i32, C.c_float, C.POINTER(DecodeExtrasC)]
     lib.argus_b200_score_reduce.argtypes = [vp, C.POINTER(ScoreReduceArgs)]
     lib.argus_b200_score_reduce_per_layer.argtypes = [vp, C.POINTER(ScoreReduceArgs)]
     lib.argus_b200_check_status.argtypes = [vp, vp]

@@ -12,8 +12,8 @@ from typing import Optional, Sequence
 
 import torch
 
-from ._lib import (ArgusB200Error, DecodeExtrasC, ExchangeC, KiviSeq, QuantAttnArgs, QuantDequantFlushArgs, QuantGatherArgs,
-                   QuantScatterResidualArgs, PagedSeq, ScoreReduceArgs, Seq, load_library)
+from ._lib import (ArgusB200Error, DecodeExtrasC, ExchangeC, KiviPagedSeq, KiviSeq, QuantAttnArgs, QuantDequantFlushArgs,
+                   QuantGatherArgs, QuantScatterResidualArgs, PagedSeq, ScoreReduceArgs, Seq, load_library)
 
 KV_F32, KV_F16 = 0, 1
 
@@ -241,6 +241,19 @@ class B200Backend:
         self._check(self._lib.argus_b200_kivi_attention_batched(
             self._h, self._stream(), q.data_ptr(), arr, n, out.data_ptr(), num_heads_q, num_heads_kv, head_dim, res_cap,
             bits, KV_F16 if res_f16 else KV_F32, float(scale), self._extras(extras)))
+
+    def kivi_attention_paged(self, q, qk_pool, qv_pool, seqs, out, num_heads_q, num_heads_kv, head_dim, res_cap, bits,
+                             scale, res_f16: bool = False, extras: Optional[DecodeExtras] = None) -> None:
+        """seqs: list of (flush_pages int32 device tensor, res_k, res_v, q_tokens, res_tokens); a page of the two pools
+        holds one flush of res_cap tokens for all KV heads."""
+        n = len(seqs)
+        arr = (KiviPagedSeq * n)()
+        for i, (pages, rk, rv, qt, rt) in enumerate(seqs):
+            arr[i] = KiviPagedSeq(_ptr(pages), _ptr(rk), _ptr(rv), int(qt), int(rt))
+        self._check(self._lib.argus_b200_kivi_attention_paged(
+            self._h, self._stream(), q.data_ptr(), qk_pool.data_ptr(), qv_pool.data_ptr(), arr, n, out.data_ptr(),
+            num_heads_q, num_heads_kv, head_dim, res_cap, bits, KV_F16 if res_f16 else KV_F32, float(scale),
+            self._extras(extras)))
 
     # ── CudaScoreReduceBackend (crates/argus-extension-api/src/lib.rs:2938-2948) ──
     def _reduce_args(self, score_buf, importance, head_importance, decay_factor, n_layers, n_heads_q, n_kv_heads,

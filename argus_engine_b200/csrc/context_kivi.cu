@@ -31,7 +31,7 @@ static int block_bytes(int bits) { return bits == 2 ? 12 : bits == 4 ? 20 : bits
 
 int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_kivi_seq* seqs, int n_seqs, float* out,
                int hq, int hkv, int d, int res_cap, int bits, int res_dtype, float scale,
-               const argus_b200_decode_extras* ex) {
+               const argus_b200_decode_extras* ex, const int32_t* const* flush_pages) {
     if (!ctx) return ARGUS_B200_E_INVALID;
     ctx->err[0] = 0;
     if (!q || !seqs || !out || n_seqs <= 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || n_seqs > kMaxBatch) {
@@ -74,6 +74,13 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
         bt.qv[i] = static_cast<const uint8_t*>(s.qv);
         bt.res_k[i] = s.res_k;
         bt.res_v[i] = s.res_v;
+        if (flush_pages) {
+            if (s.q_tokens > 0 && !flush_pages[i]) {
+                ctx->set_error("kivi attention: sequence %d: page table is null", i);
+                return ARGUS_B200_E_INVALID;
+            }
+            bt.flush_pages[i] = flush_pages[i];
+        }
         bt.q_tokens[i] = (int32_t)s.q_tokens;
         bt.res_tokens[i] = (int32_t)s.res_tokens;
         qlens[i] = s.q_tokens;
@@ -203,7 +210,31 @@ int argus_b200_kivi_attention_batched(argus_b200_ctx* ctx, void* stream, const f
                                       int res_cap, int bits, int res_dtype, float scale,
                                       const argus_b200_decode_extras* extras) {
     return argus::kivi_entry(C_(ctx), static_cast<cudaStream_t>(stream), q, seqs, n_seqs, out, num_heads_q, num_heads_kv,
-                             head_dim, res_cap, bits, res_dtype, scale, extras);
+                             head_dim, res_cap, bits, res_dtype, scale, extras, nullptr);
+}
+
+int argus_b200_kivi_attention_paged(argus_b200_ctx* ctx, void* stream, const float* q, const void* qk_pool,
+                                    const void* qv_pool, const argus_b200_kivi_paged_seq* seqs, int n_seqs, float* out,
+                                    int num_heads_q, int num_heads_kv, int head_dim, int res_cap, int bits,
+                                    int res_dtype, float scale, const argus_b200_decode_extras* extras) {
+    if (!ctx) return ARGUS_B200_E_INVALID;
+    if (!seqs || n_seqs <= 0 || n_seqs > argus::kMaxBatch) {
+        C_(ctx)->set_error("kivi paged attention: null sequence table or more than %d sequences", argus::kMaxBatch);
+        return ARGUS_B200_E_INVALID;
+    }
+    argus_b200_kivi_seq flat[argus::kMaxBatch];
+    const int32_t* tables[argus::kMaxBatch];
+    for (int i = 0; i < n_seqs; ++i) {
+        flat[i].qk = qk_pool;
+        flat[i].qv = qv_pool;
+        flat[i].res_k = seqs[i].res_k;
+        flat[i].res_v = seqs[i].res_v;
+        flat[i].q_tokens = seqs[i].q_tokens;
+        flat[i].res_tokens = seqs[i].res_tokens;
+        tables[i] = seqs[i].flush_pages;
+    }
+    return argus::kivi_entry(C_(ctx), static_cast<cudaStream_t>(stream), q, flat, n_seqs, out, num_heads_q, num_heads_kv,
+                             head_dim, res_cap, bits, res_dtype, scale, extras, tables);
 }
 
 int argus_b200_kivi_attention_gen_quant(argus_b200_ctx* ctx, const argus_b200_quant_attn_args* a) {
@@ -228,7 +259,8 @@ int argus_b200_kivi_attention_gen_quant(argus_b200_ctx* ctx, const argus_b200_qu
     }
     return argus::kivi_entry(C_(ctx), static_cast<cudaStream_t>(a->cu_stream), reinterpret_cast<const float*>(a->q_mem),
                              &s, 1, reinterpret_cast<float*>(a->out_mem), (int)a->num_heads_q, (int)a->num_heads_kv,
-                             (int)a->head_dim, (int)a->res_cap, a->bits, ARGUS_B200_KV_F32, a->scale, want ? &ex : nullptr);
+                             (int)a->head_dim, (int)a->res_cap, a->bits, ARGUS_B200_KV_F32, a->scale, want ? &ex : nullptr,
+                             nullptr);
 }
 
 int argus_b200_kivi_gather_update_quant(argus_b200_ctx* ctx, const argus_b200_quant_gather_args* a) {

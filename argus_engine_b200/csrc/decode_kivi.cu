@@ -209,6 +209,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
     const int my_tiles = warp < n_tiles ? (n_tiles - warp + WARPS - 1) / WARPS : 0;
     const uint8_t* qk = bt.qk[b];
     const uint8_t* qv = bt.qv[b];
+    const int32_t* pages = bt.flush_pages[b];
 
     uint8_t* ring = smem + warp * STAGES * STAGE_B;
     uint2* kh = reinterpret_cast<uint2*>(smem + Cfg::RING_B) + warp * (Cfg::KH_N + Cfg::VH_N);
@@ -224,7 +225,9 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
 
     auto issue = [&](int j, int slot) {   // lane 0 only
         const int gidx = g0 + warp + j * WARPS;
-        const int f = gidx / gpf, gif = gidx - f * gpf;
+        int f = gidx / gpf;
+        const int gif = gidx - f * gpf;
+        if (pages != nullptr) f = __ldg(pages + f);   // a page holds one flush of all KV heads
         const int64_t kblk = (((int64_t)f * p.hkv + kv) * gpf + gif) * D;
         const int64_t vblk = (((int64_t)f * p.hkv + kv) * bt.res_cap + gif * 32) * NB;
         const uint32_t dst = smem_u32(ring + slot * STAGE_B);

@@ -34,6 +34,7 @@ struct KiviBatch {
     const uint8_t* qv[kMaxBatch];
     const void* res_k[kMaxBatch];   // [Hkv][res_cap][D] F32 or F16
     const void* res_v[kMaxBatch];
+    const int32_t* flush_pages[kMaxBatch];   // paged form: flush f of sequence b lives in page flush_pages[b][f]; null = flush f
     int32_t q_tokens[kMaxBatch];
     int32_t res_tokens[kMaxBatch];
     int32_t chunk_groups[kMaxBatch];

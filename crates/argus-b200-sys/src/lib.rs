@@ -56,6 +56,16 @@ pub struct ArgusB200KiviSeq {
     pub res_tokens: i64,
 }
 
+/// `argus_b200_kivi_paged_seq`: one sequence of a paged KIVI call (a page = one flush of all KV heads).
+#[repr(C)]
+pub struct ArgusB200KiviPagedSeq {
+    pub flush_pages: *const i32,
+    pub res_k: *const c_void,
+    pub res_v: *const c_void,
+    pub q_tokens: i64,
+    pub res_tokens: i64,
+}
+
 /// `argus_b200_exchange`: peer buffers of a sequence-sharded decode step.
 #[repr(C)]
 pub struct ArgusB200Exchange {
@@ -102,6 +112,12 @@ extern "C" {
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, seqs: *const ArgusB200KiviSeq, n_seqs: c_int,
         out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int, head_dim: c_int, res_cap: c_int, bits: c_int,
         res_dtype: c_int, scale: f32, extras: *const ArgusB200DecodeExtras,
+    ) -> c_int;
+    pub fn argus_b200_kivi_attention_paged(
+        ctx: *mut ArgusB200Ctx, stream: *mut c_void, q: *const f32, qk_pool: *const c_void, qv_pool: *const c_void,
+        seqs: *const ArgusB200KiviPagedSeq, n_seqs: c_int, out: *mut f32, num_heads_q: c_int, num_heads_kv: c_int,
+        head_dim: c_int, res_cap: c_int, bits: c_int, res_dtype: c_int, scale: f32,
+        extras: *const ArgusB200DecodeExtras,
     ) -> c_int;
     pub fn argus_b200_exchange_wait_merge(
         ctx: *mut ArgusB200Ctx, stream: *mut c_void, own_part: *const f32, exchange: *const ArgusB200Exchange, step: c_int,

@@ -250,6 +250,26 @@ ARGUS_B200_API int argus_b200_kivi_attention_batched(argus_b200_ctx* ctx, void* 
                                                      int bits, int res_dtype, float scale,
                                                      const argus_b200_decode_extras* extras);
 
+/* The same over PAGED packed caches (batched serving; no reference counterpart: the engine's packed cache is one
+ * contiguous buffer per layer, engine/src/kv/quant_window_cache.rs:844-965). A page holds ONE flush of res_cap tokens
+ * for all KV heads: its K blocks [Hkv][res_cap/32][D] sit at block index page * Hkv*(res_cap/32)*D of qk_pool and its
+ * V blocks [Hkv][res_cap][D/32] at block index page * Hkv*res_cap*(D/32) of qv_pool - the layout one flush has in the
+ * contiguous form, so a flush can be written with argus_b200_kivi_flush_pack at those block indices. flush_pages is a
+ * DEVICE array of q_tokens / res_cap page numbers; `seqs` is a HOST array read during the call; the residual rings
+ * stay per sequence. For the same tokens the results are bit-identical to argus_b200_kivi_attention_batched. */
+typedef struct argus_b200_kivi_paged_seq {
+    const int32_t* flush_pages;
+    const void* res_k;
+    const void* res_v;
+    int64_t q_tokens;
+    int64_t res_tokens;
+} argus_b200_kivi_paged_seq;
+ARGUS_B200_API int argus_b200_kivi_attention_paged(argus_b200_ctx* ctx, void* stream, const float* q, const void* qk_pool,
+                                                   const void* qv_pool, const argus_b200_kivi_paged_seq* seqs, int n_seqs,
+                                                   float* out, int num_heads_q, int num_heads_kv, int head_dim,
+                                                   int res_cap, int bits, int res_dtype, float scale,
+                                                   const argus_b200_decode_extras* extras);
+
 /* ───────────── Score reducer: CudaScoreReduceBackend (lib.rs:2938-2948) ───────────── */
 
 /* CudaScoreReduceArgs, lib.rs:2909-2933 (byte-for-byte). */

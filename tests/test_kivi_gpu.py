@@ -231,6 +231,65 @@ def test_batched_kivi_q4_h2o_reduced(be, res_f16):
         assert got_keep == orc.h2o_keep(T, 4, 64, 128, sf[:T])
 
 
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_paged_kivi_matches_contiguous_and_oracle(be, bits):
+    """Flushes of three sequences scattered over one page pool (a page = one flush of all KV heads, in shuffled order
+    with unused pages between): outputs and score vectors are bit-identical to the contiguous call, which is checked
+    against the oracle."""
+    from argus_engine_b200 import DecodeExtras
+
+    hq, hkv, d, rc = 32, 8, 128, 128
+    lens = [128 * 9 + 50, 128 * 4, 77]
+    case = pack_with_oracle(wl.kivi_source(11, lens, hq, hkv, d, rc, bits))
+    B, stride = len(lens), 128 * 10
+    bb = {2: 12, 4: 20, 8: 36}[bits]
+    kpage = hkv * (rc // 32) * d * bb
+    vpage = hkv * rc * (d // 32) * bb
+    flushes = [case.q_tokens[i] // rc for i in range(B)]
+    n_pages = sum(flushes) + 5
+    rng = np.random.default_rng(5)
+    order = rng.permutation(n_pages)[:sum(flushes)].astype(np.int32)
+    qk_pool = rng.integers(0, 256, n_pages * kpage, dtype=np.uint8)     # unused pages hold garbage
+    qv_pool = rng.integers(0, 256, n_pages * vpage, dtype=np.uint8)
+    tables, at = [], 0
+    for i in range(B):
+        t = order[at:at + flushes[i]]
+        at += flushes[i]
+        kb = np.asarray(case.qk[i]).view(np.uint8).reshape(-1)
+        vb = np.asarray(case.qv[i]).view(np.uint8).reshape(-1)
+        for f, page in enumerate(t):
+            qk_pool[page * kpage:(page + 1) * kpage] = kb[f * kpage:(f + 1) * kpage]
+            qv_pool[page * vpage:(page + 1) * vpage] = vb[f * vpage:(f + 1) * vpage]
+        tables.append(_dev(t) if len(t) else None)
+    scale = 1 / np.sqrt(d)
+
+    def extras():
+        return DecodeExtras(head_scores=torch.zeros(B, hkv, stride, device="cuda"),
+                            flat_scores=torch.zeros(B, stride, device="cuda"), score_stride=stride)
+
+    seqs = [(_dev(case.qk[i]), _dev(case.qv[i]), _dev(case.res_k[i]), _dev(case.res_v[i]), case.q_tokens[i],
+             case.res_tokens[i]) for i in range(B)]
+    out_c = torch.full((B, hq, d), float("nan"), device="cuda")
+    ex_c = extras()
+    be.kivi_attention_batched(_dev(case.q), seqs, out_c, hq, hkv, d, rc, bits, scale, extras=ex_c)
+    pseqs = [(tables[i], _dev(case.res_k[i]), _dev(case.res_v[i]), case.q_tokens[i], case.res_tokens[i]) for i in range(B)]
+    out_p = torch.full((B, hq, d), float("nan"), device="cuda")
+    ex_p = extras()
+    be.kivi_attention_paged(_dev(case.q), _dev(qk_pool), _dev(qv_pool), pseqs, out_p, hq, hkv, d, rc, bits, scale,
+                            extras=ex_p)
+    torch.cuda.synchronize()
+    assert be.check_status() == 0
+    assert torch.equal(out_p, out_c)
+    assert torch.equal(ex_p.head_scores, ex_c.head_scores) and torch.equal(ex_p.flat_scores, ex_c.flat_scores)
+    for i in range(B):
+        np.testing.assert_allclose(out_p[i].cpu().numpy(), _oracle_kivi(case, i), atol=OUT_ATOL, rtol=OUT_RTOL)
+    # a sequence with packed tokens and no page table is refused
+    from argus_engine_b200 import ArgusB200Error
+    with pytest.raises(ArgusB200Error):
+        be.kivi_attention_paged(_dev(case.q), _dev(qk_pool), _dev(qv_pool), [(None,) + pseqs[0][1:]] + pseqs[1:], out_p,
+                                hq, hkv, d, rc, bits, scale)
+
+
 @pytest.mark.parametrize("case_id", [0, 1])
 def test_score_reduce_vs_oracle(be, case_id):
     """CudaScoreReduceBackend: the hand-computed case of engine/src/bin/test_cuda_gpu_score_device.rs:36-118
