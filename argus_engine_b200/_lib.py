@@ -87,10 +87,12 @@ def load_library() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
-        raise ImportError(f"{LIB_PATH} is missing: run `python -m argus_engine_b200.build` "
+    # ARGUS_B200_LIB_PATH selects another build of the same library (the time-stamped diagnostic twin, say).
+    path = os.environ.get("ARGUS_B200_LIB_PATH") or LIB_PATH
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: run `python -m argus_engine_b200.build` "
                           "(or __graft_entry__.build()) first; there is no CPU fallback")
-    lib = C.CDLL(LIB_PATH)
+    lib = C.CDLL(path)
     vp, i32, i64 = C.c_void_p, C.c_int, C.c_int64
     lib.argus_b200_create.argtypes = [i32, C.c_size_t, C.POINTER(vp)]
     lib.argus_b200_create_in_context.argtypes = [vp, i32, C.c_size_t, C.POINTER(vp)]

@@ -15,23 +15,30 @@ NVCC_FLAGS = [
 ]
 
 
-def _stale() -> bool:
-    if not os.path.exists(OUT):
+OUT_STAMPED = os.path.join(HERE, "libargus_b200_stamped.so")
+
+
+def _stale(out: str = OUT) -> bool:
+    if not os.path.exists(out):
         return True
-    t = os.path.getmtime(OUT)
+    t = os.path.getmtime(out)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "argus_b200.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every CUDA source into one shared library beside this file. Returns its path."""
-    if not force and not _stale():
-        return OUT
+def build(force: bool = False, verbose: bool = False, stamped: bool = False) -> str:
+    """Compile every CUDA source into one shared library beside this file. Returns its path.
+
+    stamped=True builds the diagnostic twin libargus_b200_stamped.so (-DARGUS_XC_PROFILE: the sharded decode's exchange
+    tail records globaltimer stamps that `python -m argus_engine_b200.exchange_stamps` prints); never the default."""
+    out_path = OUT_STAMPED if stamped else OUT
+    if not force and not _stale(out_path):
+        return out_path
     objs = []
     procs = []
     for src in SOURCES:
-        obj = os.path.join(CSRC, src.replace(".cu", ".o"))
-        cmd = ["nvcc", *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        obj = os.path.join(CSRC, src.replace(".cu", ".stamped.o" if stamped else ".o"))
+        cmd = ["nvcc", *NVCC_FLAGS, *(["-DARGUS_XC_PROFILE"] if stamped else []), "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -44,9 +51,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= pr.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call(["nvcc", "-shared", "-o", OUT, *objs, "-Xcompiler", "-fPIC"])
-    return OUT
+    subprocess.check_call(["nvcc", "-shared", "-o", out_path, *objs, "-Xcompiler", "-fPIC"])
+    return out_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, stamped="--stamped" in sys.argv))

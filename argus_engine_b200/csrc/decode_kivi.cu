@@ -57,6 +57,45 @@ __device__ __forceinline__ uint32_t deq_pair(__half2 codes, uint32_t d2, uint32_
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// Per-pair header entry of the shared-memory tables: {d,d'} and {m,m'} of the two elements that share an MMA operand
+// register; the 4-bit form also carries {d/16, d'/16} for the codes that are used where they sit (bits 4-7).
+template <int BITS>
+struct KvHeader { using type = uint2; };
+template <>
+struct KvHeader<4> { using type = uint4; };
+
+template <int BITS>
+__device__ __forceinline__ typename KvHeader<BITS>::type make_header(uint32_t h0, uint32_t h1) {
+    const uint32_t d2 = __byte_perm(h0, h1, 0x5410), m2 = __byte_perm(h0, h1, 0x7632);
+    if constexpr (BITS == 4) {
+        const __half2 s = __hmul2(*reinterpret_cast<const __half2*>(&d2), __half2half2(__ushort_as_half(0x2C00)));   // 1/16
+        return make_uint4(d2, m2, *reinterpret_cast<const uint32_t*>(&s), 0u);
+    } else {
+        return make_uint2(d2, m2);
+    }
+}
+
+// The four dequantised operand registers of one pair of 4-code pieces. 4-bit codes: the codes in bits 4-7 of each half
+// are masked in place (1024 + 16c is exact in F16) and multiplied by d/16, which leaves one shift per four registers
+// instead of three; 16c * (d/16) equals c * d bit for bit unless d/16 is subnormal (d < 2^-10).
+template <int BITS>
+__device__ __forceinline__ void deq_four(uint32_t xa, uint32_t xb, const typename KvHeader<BITS>::type& h,
+                                         uint32_t (&out)[4]) {
+    if constexpr (BITS == 4) {
+        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+        const uint32_t xs = xa >> 8;
+        uint32_t v0 = (xa & 0x000F000Fu) | 0x64006400u, v1 = (xa & 0x00F000F0u) | 0x64006400u;
+        uint32_t v2 = (xs & 0x000F000Fu) | 0x64006400u, v3 = (xs & 0x00F000F0u) | 0x64006400u;
+        out[0] = deq_pair(__hsub2(*reinterpret_cast<__half2*>(&v0), k1024), h.x, h.y);
+        out[1] = deq_pair(__hsub2(*reinterpret_cast<__half2*>(&v1), k1024), h.z, h.y);
+        out[2] = deq_pair(__hsub2(*reinterpret_cast<__half2*>(&v2), k1024), h.x, h.y);
+        out[3] = deq_pair(__hsub2(*reinterpret_cast<__half2*>(&v3), k1024), h.z, h.y);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[j] = deq_pair(codes_of<BITS>(xa, xb, j), h.x, h.y);
+    }
+}
+
 template <int BITS>
 __device__ __forceinline__ uint32_t load_piece(const uint8_t* p) {
     if constexpr (BITS == 2) return *p;
@@ -98,7 +137,7 @@ struct DecodeKiviCfg {
     static constexpr int RING_B = WARPS * STAGES * STAGE_B;
     static constexpr int KH_N = D / 2;                // {d2, m2} per channel pair
     static constexpr int VH_N = 16 * (D / 32);        // {d2, m2} per (token pair, channel block)
-    static constexpr int HDR_B = WARPS * (KH_N + VH_N) * 8;
+    static constexpr int HDR_B = WARPS * (KH_N + VH_N) * (int)sizeof(typename KvHeader<BITS>::type);
     static constexpr int BAR_OFF = RING_B + HDR_B;
     static constexpr int PIPE_B = BAR_OFF + WARPS * STAGES * 8;
     static constexpr int EPI_B = EpilogueSmem<D, WARPS>::BYTES;
@@ -212,8 +251,9 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
     const int32_t* pages = bt.flush_pages[b];
 
     uint8_t* ring = smem + warp * STAGES * STAGE_B;
-    uint2* kh = reinterpret_cast<uint2*>(smem + Cfg::RING_B) + warp * (Cfg::KH_N + Cfg::VH_N);
-    uint2* vh = kh + Cfg::KH_N;
+    using Header = typename KvHeader<BITS>::type;
+    Header* kh = reinterpret_cast<Header*>(smem + Cfg::RING_B) + warp * (Cfg::KH_N + Cfg::VH_N);
+    Header* vh = kh + Cfg::KH_N;
     const uint32_t bar0 = smem_u32(smem + Cfg::BAR_OFF) + warp * STAGES * 8;
 
     if (lane == 0) {
@@ -264,12 +304,16 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
         }
     }
 
-    float o[NT][4];
+    // O^T accumulators: m-tile (blk, h) row quad / quad+8 is channel 32*blk + 4*quad + 2*h (+1), columns 2*qlane (+1)
+    // are query heads. The transposed product needs half the MMAs and half the registers of O = P·V with 16 head rows.
+    constexpr int MT = 2 * NB;
+    float o[MT][4];
 #pragma unroll
-    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    for (int n = 0; n < MT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     float* logit_row = nullptr;
     if (p.logits != nullptr && head_ok) logit_row = p.logits + ((int64_t)b * p.hq + head) * p.logit_stride;
+    const bool logit_vec = (reinterpret_cast<uintptr_t>(p.logits) & 15) == 0 && (p.logit_stride & 3) == 0;
     bool timed_out = false;
 
     for (int j = 0; j < my_tiles; ++j) {
@@ -290,13 +334,13 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
         for (int i = lane; i < Cfg::KH_N; i += 32) {
             const uint32_t h0 = *reinterpret_cast<const uint32_t*>(kt + (2 * i) * BB);
             const uint32_t h1 = *reinterpret_cast<const uint32_t*>(kt + (2 * i + 1) * BB);
-            kh[i] = make_uint2(__byte_perm(h0, h1, 0x5410), __byte_perm(h0, h1, 0x7632));
+            kh[i] = make_header<BITS>(h0, h1);
         }
         for (int i = lane; i < Cfg::VH_N; i += 32) {
             const int blk = i >> 4, t = i & 15;        // pairs (t, t+16)
             const uint32_t h0 = *reinterpret_cast<const uint32_t*>(vt + (t * NB + blk) * BB);
             const uint32_t h1 = *reinterpret_cast<const uint32_t*>(vt + ((t + 16) * NB + blk) * BB);
-            vh[i] = make_uint2(__byte_perm(h0, h1, 0x5410), __byte_perm(h0, h1, 0x7632));
+            vh[i] = make_header<BITS>(h0, h1);
         }
         __syncwarp();
 
@@ -309,7 +353,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int cha = ks * 16 + 2 * qlane;
-            const uint2 ha = kh[cha >> 1], hb = kh[(cha >> 1) + 4];
+            const Header ha = kh[cha >> 1], hb = kh[(cha >> 1) + 4];
             const uint8_t* pk = kt + cha * BB + 4 + PIECE * ((quad >> 1) + 4 * (quad & 1));
             uint32_t xa0 = load_piece<BITS>(pk), xa1 = load_piece<BITS>(pk + BB);
             uint32_t xb0 = load_piece<BITS>(pk + 8 * BB), xb1 = load_piece<BITS>(pk + 9 * BB);
@@ -317,12 +361,11 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                 xa0 |= xa1 << 16;
                 xb0 |= xb1 << 16;
             }
+            uint32_t b0[4], b1[4];
+            deq_four<BITS>(xa0, xa1, ha, b0);
+            deq_four<BITS>(xb0, xb1, hb, b1);
 #pragma unroll
-            for (int jp = 0; jp < 4; ++jp) {
-                const uint32_t b0 = deq_pair(codes_of<BITS>(xa0, xa1, jp), ha.x, ha.y);
-                const uint32_t b1 = deq_pair(codes_of<BITS>(xb0, xb1, jp), hb.x, hb.y);
-                mma_f16_16816(c[jp], qf[ks], b0, b1);
-            }
+            for (int jp = 0; jp < 4; ++jp) mma_f16_16816(c[jp], qf[ks], b0[jp], b1[jp]);
         }
         // accumulator column 2*qlane+i of n-tile jp  <->  token 4*qlane + 16*i + jp of the group
         const int tokb = (g0 + warp + j * WARPS) * 32;
@@ -333,10 +376,17 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const float x = c[jp][i] + c[jp][i + 2];
-                if (logit_row != nullptr) logit_row[tokb + 4 * qlane + 16 * i + jp] = x;
                 s[jp][i] = x;
                 tile_max = fmaxf(tile_max, x);
             }
+        if (logit_row != nullptr) {   // a lane holds tokens 4q + 16i + {0..3}: one 16-byte store per i where rows allow it
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float* dst = logit_row + tokb + 4 * qlane + 16 * i;
+                if (logit_vec) *reinterpret_cast<float4*>(dst) = make_float4(s[0][i], s[1][i], s[2][i], s[3][i]);
+                else { dst[0] = s[0][i]; dst[1] = s[1][i]; dst[2] = s[2][i]; dst[3] = s[3][i]; }
+            }
+        }
         tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
         tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
         const float m_new = fmaxf(m_run, tile_max);
@@ -352,29 +402,24 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                 psum += s[jp][i];
             }
         l_run = l_run * alpha + psum;
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {   // this lane's columns are heads 2*qlane and 2*qlane+1
+            const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * qlane), a1 = __shfl_sync(0xffffffffu, alpha, 8 * qlane + 4);
 #pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                o[n][0] *= alpha; o[n][1] *= alpha; o[n][2] *= alpha; o[n][3] *= alpha;
+            for (int n = 0; n < MT; ++n) {
+                o[n][0] *= a0; o[n][1] *= a1; o[n][2] *= a0; o[n][3] *= a1;
             }
         }
-        // O[head][channel] += P · V. k-step u: A columns 2q+i <- n-tile 2u, 8+2q+i <- n-tile 2u+1, i.e.
-        // tokens (4q+2u, 4q+16+2u | 4q+2u+1, 4q+17+2u); MMA column `quad` of n-tile (blk, jc) is channel 32blk+4quad+jc.
+        // O^T[channel][head] += V^T · P^T. k-step u: A columns (2q, 2q+1 | 2q+8, 2q+9) and B rows alike are tokens
+        // (4q+2u, 4q+16+2u | 4q+2u+1, 4q+17+2u); B column `quad` is this lane's own head, so P goes from the S
+        // accumulators into the B registers without leaving the lane (rounded to F16 once, like the V codes' scales).
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            uint32_t pa[4];
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const float p0 = s[2 * u + n][0], p1 = s[2 * u + n][1];
-                const uint32_t hi = pack_half2(p0, p1);
-                const float2 hif = unpack_half2(hi);
-                pa[n * 2 + 0] = hi;
-                pa[n * 2 + 1] = pack_half2(p0 - hif.x, p1 - hif.y);
-            }
-            const int ta = 4 * qlane + 2 * u;   // b0b1 pairs tokens (ta, ta+16), b2b3 pairs (ta+1, ta+17)
+            const uint32_t pb0 = pack_half2(s[2 * u][0], s[2 * u][1]);
+            const uint32_t pb1 = pack_half2(s[2 * u + 1][0], s[2 * u + 1][1]);
+            const int ta = 4 * qlane + 2 * u;
 #pragma unroll
             for (int blk = 0; blk < NB; ++blk) {
-                const uint2 ha = vh[blk * 16 + qlane * 4 + 2 * u], hb = vh[blk * 16 + qlane * 4 + 2 * u + 1];
+                const Header ha = vh[blk * 16 + qlane * 4 + 2 * u], hb = vh[blk * 16 + qlane * 4 + 2 * u + 1];
                 const uint8_t* pv = vt + (ta * NB + blk) * BB + 4 + PIECE * quad;
                 uint32_t xa0 = load_piece<BITS>(pv), xa1 = load_piece<BITS>(pv + 16 * NB * BB);
                 uint32_t xb0 = load_piece<BITS>(pv + NB * BB), xb1 = load_piece<BITS>(pv + 17 * NB * BB);
@@ -382,11 +427,13 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                     xa0 |= xa1 << 16;
                     xb0 |= xb1 << 16;
                 }
+                uint32_t va[4], vb[4];
+                deq_four<BITS>(xa0, xa1, ha, va);
+                deq_four<BITS>(xb0, xb1, hb, vb);
 #pragma unroll
-                for (int jc = 0; jc < 4; ++jc) {
-                    const uint32_t b0 = deq_pair(codes_of<BITS>(xa0, xa1, jc), ha.x, ha.y);
-                    const uint32_t b1 = deq_pair(codes_of<BITS>(xb0, xb1, jc), hb.x, hb.y);
-                    mma_f16_16816(o[blk * 4 + jc], pa, b0, b1);
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t a[4] = {va[2 * h], va[2 * h + 1], vb[2 * h], vb[2 * h + 1]};
+                    mma_f16_16816(o[blk * 2 + h], a, pb0, pb1);
                 }
             }
         }
@@ -397,7 +444,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
         for (int s = 0; s < STAGES; ++s) (void)mbar_wait(bar0 + s * 8, 0);
         if (p.status != nullptr) atomicExch(p.status, 1);
 #pragma unroll
-        for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        for (int n = 0; n < MT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
         m_run = -INFINITY;
         l_run = 0.f;
     }
@@ -405,16 +452,14 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
     __syncthreads();
 
-    // accumulator (n-tile blk*4+jc, column 2*qlane+i) is channel 32*blk + 8*qlane + 4*i + jc
+    // accumulator (m-tile blk*2+h, register 2*r+i) is channel 32*blk + 4*quad + 2*h + r of head 2*qlane + i
 #pragma unroll
     for (int blk = 0; blk < NB; ++blk)
 #pragma unroll
-        for (int jc = 0; jc < 4; ++jc)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int n = blk * 4 + jc;
-                sm_o[(warp * 8 + quad) * D + 32 * blk + 8 * qlane + 4 * i + jc] = o[n][i] + o[n][i + 2];
-            }
+        for (int i = 0; i < 2; ++i) {
+            const float4 v4 = make_float4(o[blk * 2][i], o[blk * 2][2 + i], o[blk * 2 + 1][i], o[blk * 2 + 1][2 + i]);
+            *reinterpret_cast<float4*>(&sm_o[(warp * 8 + 2 * qlane + i) * D + 32 * blk + 4 * quad]) = v4;
+        }
     if (qlane == 0) sm_ml[warp * 8 + quad] = make_float2(m_run, l_run);
     __syncthreads();
     decode_epilogue<D, WARPS>(smem, p, b, kv, item, item0, n_splits);
@@ -432,12 +477,15 @@ static cudaError_t launch_kivi_t(const DecodeParams& p, const KiviBatch& bt, int
 }
 
 static int kivi_q4_variant() {
-    static const int variant = getenv("ARGUS_B200_KIVI_VARIANT") ? atoi(getenv("ARGUS_B200_KIVI_VARIANT")) : 0;
+    const int variant = getenv("ARGUS_B200_KIVI_VARIANT") ? atoi(getenv("ARGUS_B200_KIVI_VARIANT")) : 0;
     return variant;
 }
 
 // CTAs of the selected instantiation that are resident per SM: the split planner fills exactly one such wave.
-int decode_kivi_ctas_per_sm(int head_dim, int bits) { return (head_dim == 128 && bits == 4 && kivi_q4_variant() != 1) ? 3 : 2; }
+int decode_kivi_ctas_per_sm(int head_dim, int bits) {
+    if (head_dim == 128 && bits == 4) return kivi_q4_variant() == 2 ? 4 : (kivi_q4_variant() == 1 || kivi_q4_variant() == 3) ? 2 : 3;
+    return 2;
+}
 
 // CTA slots per SM the split planner fills. More CTAs than are resident, so that the block scheduler hands out the
 // tail: measured on B=8 x 32K tokens, Q4 (3 resident): 2 -> 185 us, 3 -> 154, 5 -> 144, 8 -> 144; Q8 (2 resident):
@@ -450,6 +498,8 @@ cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int h
         if (bits == 4) {
             const int variant = kivi_q4_variant();
             if (variant == 1) return launch_kivi_t<128, 4, 4, 4>(p, bt, n_items, st);
+            if (variant == 2) return launch_kivi_t<128, 4, 4, 2, 4>(p, bt, n_items, st);
+            if (variant == 3) return launch_kivi_t<128, 4, 8, 2, 2>(p, bt, n_items, st);
             return launch_kivi_t<128, 4, 4, 3, 3>(p, bt, n_items, st);   // 3 CTAs per SM: +17 % over 2 CTAs of 4 stages
         }
         if (bits == 8) return launch_kivi_t<128, 8, 4, 3>(p, bt, n_items, st);
