@@ -51,7 +51,7 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
     memset(&bt, 0, sizeof(bt));
     bt.res_cap = res_cap;
     bt.res_is_f16 = (res_dtype == ARGUS_B200_KV_F16);
-    bt.res_chunk = 128;
+    bt.res_chunk = 32;   // 8 token steps per warp: the residual rows go through plain F32 arithmetic, one token at a time
     int64_t qlens[kMaxBatch];
     int64_t max_len = 0, max_res = 0;
     for (int i = 0; i < n_seqs; ++i) {
@@ -99,13 +99,12 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
 
     // Packed part: the same proportional planner as the F16 path, in tokens, then expressed in 32-token groups.
     int32_t chunk[kMaxBatch], nsplit[kMaxBatch];
-    // About 5/3 of the resident CTA slots (3 per SM for the Q4 head_dim-128 instantiation, 2 otherwise): planning 2 per
-    // SM where 3 are resident left a third of the slots empty, and somewhat more CTAs than slots lets the block scheduler
-    // even out the tail (185 -> 144 us on the benchmark shape). ARGUS_B200_KIVI_WAVES / _SLOTS override for experiments.
+    // The planner fills decode_kivi_plan_slots_per_sm() CTA slots per SM (measured there); ARGUS_B200_KIVI_WAVES / _SLOTS
+    // override for experiments.
     const int waves = ctx->opt.kivi_waves > 0 ? ctx->opt.kivi_waves : 1;
     const int slots_per_sm = ctx->opt.kivi_slots > 0 ? ctx->opt.kivi_slots : decode_kivi_plan_slots_per_sm(d, bits);
     plan_splits(qlens, n_seqs, hkv, ctx->num_sms * slots_per_sm, waves, 4 * 32 * 2, chunk, nsplit);
-    int items = 0;
+    int items = 0, res_items = 0;
     for (int i = 0; i < n_seqs; ++i) {
         const int groups = (int)(qlens[i] / 32);
         int cg = std::max(1, (chunk[i] + 31) / 32);
@@ -115,13 +114,16 @@ int kivi_entry(Context* ctx, cudaStream_t st, const float* q, const argus_b200_k
         bt.chunk_groups[i] = cg;
         bt.n_qsplits[i] = nq;
         bt.item_start[i] = items;
+        bt.res_start[i] = res_items;
         items += nq + nr;
+        res_items += nr;
         if (nq + nr > kMaxSplits) {
             ctx->set_error("kivi attention: sequence %d needs %d splits (max %d)", i, nq + nr, kMaxSplits);
             return ARGUS_B200_E_WORKSPACE;
         }
     }
     bt.item_start[n_seqs] = items;
+    bt.res_start[n_seqs] = res_items;
 
     size_t cur = 0;
     if ((size_t)n_seqs * hkv > ctx->n_tickets) return ARGUS_B200_E_WORKSPACE;

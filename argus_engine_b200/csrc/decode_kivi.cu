@@ -32,68 +32,66 @@ struct KvBlock {
     static constexpr int PIECE = BITS / 2;   // bytes holding 4 consecutive codes
 };
 
-// codes (exact small integers as F16 pairs) of position j (0..3) inside a pair of 4-code pieces:
-// x = piece(lo element) | piece(hi element) << 16 for BITS 2/4; for BITS 8 the two pieces come separately.
+// Scale folding. A K block is 32 tokens of ONE channel, a V block 32 channels of ONE token, each with a scale d and a
+// minimum m: value = d*c + m. Both scales run along the contraction index of their product, so they move to the other
+// operand and the codes go into the tensor cores as they are:
+//   s[h][t] = sum_ch (q[h][ch] * d[ch]) * c[t][ch]  +  sum_ch q[h][ch] * m[ch]        (one extra MMA per k-step)
+//   o[ch][h] = sum_t c[t][ch] * (p[h][t] * d[t][blk(ch)])  +  sum_t p[h][t] * m[t][blk(ch)]   (one extra MMA per k-step)
+// which costs a few multiplications per 32-token group instead of a subtract and a fused multiply-add per code pair.
+//
+// The codes are used where they sit: a code c in bits [s, s+w) of a 16-bit lane, everything else masked off, is the
+// subnormal F16 number c * 2^(s-24), exact, and tensor-core products of F16 inputs are exact in the FP32 accumulator.
+// The four codes of a piece therefore carry different powers of two (kCodeUnscale), taken out of the accumulators
+// after the MMAs. x = piece(lo element) | piece(hi element) << 16 for 2- and 4-bit codes; for 8-bit codes the two
+// pieces (four bytes each) come separately.
 template <int BITS>
-__device__ __forceinline__ __half2 codes_of(uint32_t xa, uint32_t xb, int j) {
-    uint32_t v;
-    if constexpr (BITS == 8) {
-        // bytes j of xa and xb -> low bytes of the two halves, exponent byte 0x64 above each
-        uint32_t t;
-        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(xa), "r"(xb), "r"((uint32_t)j | ((uint32_t)(4 + j) << 4)));
-        // t = [xa.bj, xb.bj, xa.b0, xa.b0] -> spread to the low bytes of the two halves
-        asm("prmt.b32 %0, %1, %2, 0x7170;" : "=r"(v) : "r"(t), "r"(0x64646464u));
-    } else if constexpr (BITS == 4) {
-        v = ((xa >> (4 * j)) & 0x000F000Fu) | 0x64006400u;
-    } else {
-        v = ((xa >> (2 * j)) & 0x00030003u) | 0x64006400u;
-    }
-    const __half2 h = *reinterpret_cast<__half2*>(&v);
-    return __hsub2(h, __half2half2(__ushort_as_half(0x6400)));   // exact: (1024 + c) - 1024
-}
-
-__device__ __forceinline__ uint32_t deq_pair(__half2 codes, uint32_t d2, uint32_t m2) {
-    const __half2 r = __hfma2(codes, *reinterpret_cast<__half2*>(&d2), *reinterpret_cast<__half2*>(&m2));
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
-
-// Per-pair header entry of the shared-memory tables: {d,d'} and {m,m'} of the two elements that share an MMA operand
-// register; the 4-bit form also carries {d/16, d'/16} for the codes that are used where they sit (bits 4-7).
-template <int BITS>
-struct KvHeader { using type = uint2; };
-template <>
-struct KvHeader<4> { using type = uint4; };
-
-template <int BITS>
-__device__ __forceinline__ typename KvHeader<BITS>::type make_header(uint32_t h0, uint32_t h1) {
-    const uint32_t d2 = __byte_perm(h0, h1, 0x5410), m2 = __byte_perm(h0, h1, 0x7632);
+__device__ __forceinline__ void raw_codes(uint32_t xa, uint32_t xb, uint32_t (&out)[4]) {
     if constexpr (BITS == 4) {
-        const __half2 s = __hmul2(*reinterpret_cast<const __half2*>(&d2), __half2half2(__ushort_as_half(0x2C00)));   // 1/16
-        return make_uint4(d2, m2, *reinterpret_cast<const uint32_t*>(&s), 0u);
-    } else {
-        return make_uint2(d2, m2);
-    }
-}
-
-// The four dequantised operand registers of one pair of 4-code pieces. 4-bit codes: the codes in bits 4-7 of each half
-// are masked in place (1024 + 16c is exact in F16) and multiplied by d/16, which leaves one shift per four registers
-// instead of three; 16c * (d/16) equals c * d bit for bit unless d/16 is subnormal (d < 2^-10).
-template <int BITS>
-__device__ __forceinline__ void deq_four(uint32_t xa, uint32_t xb, const typename KvHeader<BITS>::type& h,
-                                         uint32_t (&out)[4]) {
-    if constexpr (BITS == 4) {
-        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
         const uint32_t xs = xa >> 8;
-        uint32_t v0 = (xa & 0x000F000Fu) | 0x64006400u, v1 = (xa & 0x00F000F0u) | 0x64006400u;
-        uint32_t v2 = (xs & 0x000F000Fu) | 0x64006400u, v3 = (xs & 0x00F000F0u) | 0x64006400u;
-        out[0] = deq_pair(__hsub2(*reinterpret_cast<__half2*>(&v0), k1024), h.x, h.y);
-        out[1] = deq_pair(__hsub2(*reinterpret_cast<__half2*>(&v1), k1024), h.z, h.y);
-        out[2] = deq_pair(__hsub2(*reinterpret_cast<__half2*>(&v2), k1024), h.x, h.y);
-        out[3] = deq_pair(__hsub2(*reinterpret_cast<__half2*>(&v3), k1024), h.z, h.y);
+        out[0] = xa & 0x000F000Fu;
+        out[1] = xa & 0x00F000F0u;
+        out[2] = xs & 0x000F000Fu;
+        out[3] = xs & 0x00F000F0u;
+    } else if constexpr (BITS == 2) {
+        out[0] = xa & 0x00030003u;
+        out[1] = xa & 0x000C000Cu;
+        out[2] = xa & 0x00300030u;
+        out[3] = xa & 0x00C000C0u;
     } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) out[j] = deq_pair(codes_of<BITS>(xa, xb, j), h.x, h.y);
+        for (int j = 0; j < 4; ++j) {
+            uint32_t t, v;   // byte j of xa and of xb -> low bytes of the two halves, zero above each
+            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(xa), "r"(xb), "r"((uint32_t)j | ((uint32_t)(4 + j) << 4)));
+            asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(v) : "r"(t), "r"(0u));
+            out[j] = v;
+        }
     }
+}
+// 2^24 over the power of two that position j of raw_codes carries
+template <int BITS>
+__device__ __forceinline__ constexpr float code_unscale(int j) {
+    return BITS == 4 ? ((j & 1) ? 1048576.f : 16777216.f)
+         : BITS == 2 ? (j == 0 ? 16777216.f : j == 1 ? 4194304.f : j == 2 ? 1048576.f : 262144.f)
+                     : 16777216.f;
+}
+
+__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+// (hi, lo) halves of the product (a_hi + a_lo) * d: hi = rn(a_hi*d), lo = rn(a_lo*d + (a_hi*d - hi)), the inner term exact
+__device__ __forceinline__ void scale_split(uint32_t a_hi, uint32_t a_lo, uint32_t d, uint32_t& hi, uint32_t& lo) {
+    const __half2 ah = *reinterpret_cast<const __half2*>(&a_hi), al = *reinterpret_cast<const __half2*>(&a_lo);
+    const __half2 dd = *reinterpret_cast<const __half2*>(&d);
+    const __half2 h = __hmul2(ah, dd);
+    const __half2 l = __hfma2(al, dd, __hfma2(ah, dd, __hneg2(h)));
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+// Per-pair header entry of the shared-memory tables: {d,d'} and {m,m'} of the two elements that share an operand register.
+__device__ __forceinline__ uint2 make_header(uint32_t h0, uint32_t h1) {
+    return make_uint2(__byte_perm(h0, h1, 0x5410), __byte_perm(h0, h1, 0x7632));
 }
 
 template <int BITS>
@@ -137,7 +135,7 @@ struct DecodeKiviCfg {
     static constexpr int RING_B = WARPS * STAGES * STAGE_B;
     static constexpr int KH_N = D / 2;                // {d2, m2} per channel pair
     static constexpr int VH_N = 16 * (D / 32);        // {d2, m2} per (token pair, channel block)
-    static constexpr int HDR_B = WARPS * (KH_N + VH_N) * (int)sizeof(typename KvHeader<BITS>::type);
+    static constexpr int HDR_B = WARPS * (KH_N + VH_N) * 8;
     static constexpr int BAR_OFF = RING_B + HDR_B;
     static constexpr int PIPE_B = BAR_OFF + WARPS * STAGES * 8;
     static constexpr int EPI_B = EpilogueSmem<D, WARPS>::BYTES;
@@ -156,17 +154,24 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
     const int quad = lane >> 2, qlane = lane & 3;
 
     const int kv = blockIdx.x % p.hkv;
-    const int gs = blockIdx.x / p.hkv;
-    int b = 0;
-    while (b + 1 < p.n_seqs && bt.item_start[b + 1] <= gs) ++b;
-    const int split = gs - bt.item_start[b];
+    const int gs = blockIdx.x / p.hkv;   // launch slot: residual splits of all sequences, then the packed splits
+    const int n_res = bt.res_start[p.n_seqs];
+    int b = 0, split;
+    if (gs < n_res) {
+        while (b + 1 < p.n_seqs && bt.res_start[b + 1] <= gs) ++b;
+        split = bt.n_qsplits[b] + (gs - bt.res_start[b]);
+    } else {
+        const int gq = gs - n_res;   // packed splits before sequence b: item_start[b] - res_start[b]
+        while (b + 1 < p.n_seqs && bt.item_start[b + 1] - bt.res_start[b + 1] <= gq) ++b;
+        split = gq - (bt.item_start[b] - bt.res_start[b]);
+    }
     const int n_splits = bt.item_start[b + 1] - bt.item_start[b];
     const int n_qsplits = bt.n_qsplits[b];
     const int q_tokens = bt.q_tokens[b];
 
     float* sm_o = reinterpret_cast<float*>(smem + EpilogueSmem<D, WARPS>::O_OFF);
     float2* sm_ml = reinterpret_cast<float2*>(smem + EpilogueSmem<D, WARPS>::ML_OFF);
-    const int64_t item = (int64_t)gs * p.hkv + kv;
+    const int64_t item = (int64_t)(bt.item_start[b] + split) * p.hkv + kv;
     const int64_t item0 = (int64_t)bt.item_start[b] * p.hkv + kv;
 
     if (split >= n_qsplits) {
@@ -251,7 +256,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
     const int32_t* pages = bt.flush_pages[b];
 
     uint8_t* ring = smem + warp * STAGES * STAGE_B;
-    using Header = typename KvHeader<BITS>::type;
+    using Header = uint2;
     Header* kh = reinterpret_cast<Header*>(smem + Cfg::RING_B) + warp * (Cfg::KH_N + Cfg::VH_N);
     Header* vh = kh + Cfg::KH_N;
     const uint32_t bar0 = smem_u32(smem + Cfg::BAR_OFF) + warp * STAGES * 8;
@@ -310,6 +315,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
     float o[MT][4];
 #pragma unroll
     for (int n = 0; n < MT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float ob[4] = {0.f, 0.f, 0.f, 0.f};   // P·m: row blk (lanes with quad == blk < NB), columns = heads 2*qlane (+1)
     float m_run = -INFINITY, l_run = 0.f;
     float* logit_row = nullptr;
     if (p.logits != nullptr && head_ok) logit_row = p.logits + ((int64_t)b * p.hq + head) * p.logit_stride;
@@ -334,22 +340,24 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
         for (int i = lane; i < Cfg::KH_N; i += 32) {
             const uint32_t h0 = *reinterpret_cast<const uint32_t*>(kt + (2 * i) * BB);
             const uint32_t h1 = *reinterpret_cast<const uint32_t*>(kt + (2 * i + 1) * BB);
-            kh[i] = make_header<BITS>(h0, h1);
+            kh[i] = make_header(h0, h1);
         }
         for (int i = lane; i < Cfg::VH_N; i += 32) {
             const int blk = i >> 4, t = i & 15;        // pairs (t, t+16)
             const uint32_t h0 = *reinterpret_cast<const uint32_t*>(vt + (t * NB + blk) * BB);
             const uint32_t h1 = *reinterpret_cast<const uint32_t*>(vt + ((t + 16) * NB + blk) * BB);
-            vh[i] = make_header<BITS>(h0, h1);
+            vh[i] = make_header(h0, h1);
         }
         __syncwarp();
 
         // S[head][token]: MMA column `quad` of n-tile jp is token 4*piece + jp of the group, where lane group
         // `quad` reads code piece (quad>>1) + 4*(quad&1). That permutation makes the tokens one lane later pairs
         // for P·V lie 16 apart, so that the four lanes of a quad do not all hit the same shared-memory banks.
-        float c[4][4];
+        // A = q * d of this group (rows 0-7 the F16 head, rows 8-15 the remainder), B = the codes; cb collects q·m.
+        float c[4][4], cb[4];
 #pragma unroll
         for (int n = 0; n < 4; ++n) c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.f;
+        cb[0] = cb[1] = cb[2] = cb[3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int cha = ks * 16 + 2 * qlane;
@@ -361,12 +369,17 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                 xa0 |= xa1 << 16;
                 xb0 |= xb1 << 16;
             }
+            uint32_t a[4];
+            scale_split(qf[ks][0], qf[ks][1], ha.x, a[0], a[1]);
+            scale_split(qf[ks][2], qf[ks][3], hb.x, a[2], a[3]);
+            mma_f16_16816(cb, qf[ks], ha.y, hb.y);
             uint32_t b0[4], b1[4];
-            deq_four<BITS>(xa0, xa1, ha, b0);
-            deq_four<BITS>(xb0, xb1, hb, b1);
+            raw_codes<BITS>(xa0, xa1, b0);
+            raw_codes<BITS>(xb0, xb1, b1);
 #pragma unroll
-            for (int jp = 0; jp < 4; ++jp) mma_f16_16816(c[jp], qf[ks], b0[jp], b1[jp]);
+            for (int jp = 0; jp < 4; ++jp) mma_f16_16816(c[jp], a, b0[jp], b1[jp]);
         }
+        const float s_bias = cb[0] + cb[2];   // every column of cb holds the same sum: q·m of this lane's head
         // accumulator column 2*qlane+i of n-tile jp  <->  token 4*qlane + 16*i + jp of the group
         const int tokb = (g0 + warp + j * WARPS) * 32;
         float s[4][2];
@@ -375,7 +388,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
         for (int jp = 0; jp < 4; ++jp)
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const float x = c[jp][i] + c[jp][i + 2];
+                const float x = fmaf(c[jp][i] + c[jp][i + 2], code_unscale<BITS>(jp), s_bias);
                 s[jp][i] = x;
                 tile_max = fmaxf(tile_max, x);
             }
@@ -408,18 +421,28 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
             for (int n = 0; n < MT; ++n) {
                 o[n][0] *= a0; o[n][1] *= a1; o[n][2] *= a0; o[n][3] *= a1;
             }
+            ob[0] *= a0;
+            ob[1] *= a1;
         }
         // O^T[channel][head] += V^T · P^T. k-step u: A columns (2q, 2q+1 | 2q+8, 2q+9) and B rows alike are tokens
         // (4q+2u, 4q+16+2u | 4q+2u+1, 4q+17+2u); B column `quad` is this lane's own head, so P goes from the S
-        // accumulators into the B registers without leaving the lane (rounded to F16 once, like the V codes' scales).
+        // accumulators into the B registers without leaving the lane. A = the codes, B = P * d of (token, channel
+        // block); ob collects P·m, its row `blk` (lanes with quad == blk) against the same unscaled P.
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const uint32_t pb0 = pack_half2(s[2 * u][0], s[2 * u][1]);
             const uint32_t pb1 = pack_half2(s[2 * u + 1][0], s[2 * u + 1][1]);
             const int ta = 4 * qlane + 2 * u;
+            {
+                const int bq = quad < NB ? quad : 0;
+                const uint32_t ma = vh[bq * 16 + qlane * 4 + 2 * u].y, mb = vh[bq * 16 + qlane * 4 + 2 * u + 1].y;
+                const uint32_t am[4] = {quad < NB ? ma : 0u, 0u, quad < NB ? mb : 0u, 0u};
+                mma_f16_16816(ob, am, pb0, pb1);
+            }
 #pragma unroll
             for (int blk = 0; blk < NB; ++blk) {
-                const Header ha = vh[blk * 16 + qlane * 4 + 2 * u], hb = vh[blk * 16 + qlane * 4 + 2 * u + 1];
+                const uint32_t da = vh[blk * 16 + qlane * 4 + 2 * u].x, db = vh[blk * 16 + qlane * 4 + 2 * u + 1].x;
+                const uint32_t pd0 = hmul2_u(pb0, da), pd1 = hmul2_u(pb1, db);
                 const uint8_t* pv = vt + (ta * NB + blk) * BB + 4 + PIECE * quad;
                 uint32_t xa0 = load_piece<BITS>(pv), xa1 = load_piece<BITS>(pv + 16 * NB * BB);
                 uint32_t xb0 = load_piece<BITS>(pv + NB * BB), xb1 = load_piece<BITS>(pv + 17 * NB * BB);
@@ -428,12 +451,12 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                     xb0 |= xb1 << 16;
                 }
                 uint32_t va[4], vb[4];
-                deq_four<BITS>(xa0, xa1, ha, va);
-                deq_four<BITS>(xb0, xb1, hb, vb);
+                raw_codes<BITS>(xa0, xa1, va);
+                raw_codes<BITS>(xb0, xb1, vb);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const uint32_t a[4] = {va[2 * h], va[2 * h + 1], vb[2 * h], vb[2 * h + 1]};
-                    mma_f16_16816(o[blk * 2 + h], a, pb0, pb1);
+                    mma_f16_16816(o[blk * 2 + h], a, pd0, pd1);
                 }
             }
         }
@@ -445,6 +468,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
         if (p.status != nullptr) atomicExch(p.status, 1);
 #pragma unroll
         for (int n = 0; n < MT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        ob[0] = ob[1] = 0.f;
         m_run = -INFINITY;
         l_run = 0.f;
     }
@@ -452,12 +476,17 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
     __syncthreads();
 
-    // accumulator (m-tile blk*2+h, register 2*r+i) is channel 32*blk + 4*quad + 2*h + r of head 2*qlane + i
+    // accumulator (m-tile blk*2+h, register 2*r+i) is channel 32*blk + 4*quad + 2*h + r of head 2*qlane + i, still
+    // carrying the power of two of code position 2*h + r; the P·m sum of (blk, head) sits in the lane with quad == blk
 #pragma unroll
     for (int blk = 0; blk < NB; ++blk)
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const float4 v4 = make_float4(o[blk * 2][i], o[blk * 2][2 + i], o[blk * 2 + 1][i], o[blk * 2 + 1][2 + i]);
+            const float bias = __shfl_sync(0xffffffffu, ob[i], blk * 4 + qlane);
+            const float4 v4 = make_float4(fmaf(o[blk * 2][i], code_unscale<BITS>(0), bias),
+                                          fmaf(o[blk * 2][2 + i], code_unscale<BITS>(1), bias),
+                                          fmaf(o[blk * 2 + 1][i], code_unscale<BITS>(2), bias),
+                                          fmaf(o[blk * 2 + 1][2 + i], code_unscale<BITS>(3), bias));
             *reinterpret_cast<float4*>(&sm_o[(warp * 8 + 2 * qlane + i) * D + 32 * blk + 4 * quad]) = v4;
         }
     if (qlane == 0) sm_ml[warp * 8 + quad] = make_float2(m_run, l_run);
@@ -476,32 +505,17 @@ static cudaError_t launch_kivi_t(const DecodeParams& p, const KiviBatch& bt, int
     return cudaGetLastError();
 }
 
-static int kivi_q4_variant() {
-    const int variant = getenv("ARGUS_B200_KIVI_VARIANT") ? atoi(getenv("ARGUS_B200_KIVI_VARIANT")) : 0;
-    return variant;
-}
-
 // CTAs of the selected instantiation that are resident per SM: the split planner fills exactly one such wave.
-int decode_kivi_ctas_per_sm(int head_dim, int bits) {
-    if (head_dim == 128 && bits == 4) return kivi_q4_variant() == 2 ? 4 : (kivi_q4_variant() == 1 || kivi_q4_variant() == 3) ? 2 : 3;
-    return 2;
-}
+int decode_kivi_ctas_per_sm(int head_dim, int bits) { return (head_dim == 128 && bits == 4) ? 3 : 2; }
 
-// CTA slots per SM the split planner fills. More CTAs than are resident, so that the block scheduler hands out the
-// tail: measured on B=8 x 32K tokens, Q4 (3 resident): 2 -> 185 us, 3 -> 154, 5 -> 144, 8 -> 144; Q8 (2 resident):
-// 2 -> 191, 3 -> 152, 4 -> 154.
-int decode_kivi_plan_slots_per_sm(int head_dim, int bits) { return decode_kivi_ctas_per_sm(head_dim, bits) == 3 ? 5 : 3; }
+// CTA slots per SM the split planner fills: one resident wave where three CTAs fit (B=8 x 32K tokens, Q4: 3 -> 102 us,
+// 4 -> 111, 5 -> 113, 6 -> 107, 7 -> 106, 9 -> 111), one and a half where two fit.
+int decode_kivi_plan_slots_per_sm(int head_dim, int bits) { return 3; }
 
 cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int head_dim, int bits, int n_items,
                                cudaStream_t st) {
     if (head_dim == 128) {
-        if (bits == 4) {
-            const int variant = kivi_q4_variant();
-            if (variant == 1) return launch_kivi_t<128, 4, 4, 4>(p, bt, n_items, st);
-            if (variant == 2) return launch_kivi_t<128, 4, 4, 2, 4>(p, bt, n_items, st);
-            if (variant == 3) return launch_kivi_t<128, 4, 8, 2, 2>(p, bt, n_items, st);
-            return launch_kivi_t<128, 4, 4, 3, 3>(p, bt, n_items, st);   // 3 CTAs per SM: +17 % over 2 CTAs of 4 stages
-        }
+        if (bits == 4) return launch_kivi_t<128, 4, 4, 3, 3>(p, bt, n_items, st);   // 3 CTAs per SM
         if (bits == 8) return launch_kivi_t<128, 8, 4, 3>(p, bt, n_items, st);
         if (bits == 2) return launch_kivi_t<128, 2, 4, 4>(p, bt, n_items, st);
     } else if (head_dim == 64) {

@@ -28,7 +28,9 @@ struct DecodeBatch {
 };
 
 // KIVI-packed sequences. Splits [0, n_qsplits[b]) of sequence b cover chunk_groups[b] 32-token groups of the
-// packed part each; the remaining splits cover res_chunk tokens of the residual window each.
+// packed part each; the remaining splits cover res_chunk tokens of the residual window each. The grid runs the
+// residual splits of ALL sequences first (res_start = their prefix sum) and the packed splits after them: a residual
+// split is the slowest CTA per token, and one that starts last is a tail nothing overlaps.
 struct KiviBatch {
     const uint8_t* qk[kMaxBatch];
     const uint8_t* qv[kMaxBatch];
@@ -40,6 +42,7 @@ struct KiviBatch {
     int32_t chunk_groups[kMaxBatch];
     int32_t n_qsplits[kMaxBatch];
     int32_t item_start[kMaxBatch + 1];
+    int32_t res_start[kMaxBatch + 1];
     int32_t res_cap;
     int32_t res_chunk;
     int32_t res_is_f16;
