@@ -17,7 +17,6 @@
 // softmax does not care and P·V uses the same order. The residual window is a separate split handled in
 // plain F32 FMA. Everything after the main loop (warp merge, split merge, score finalize) is shared with
 // the F16 kernel.
-#include <stdlib.h>
 
 #include "decode_epilogue.cuh"
 #include "context.h"
@@ -75,6 +74,9 @@ __device__ __forceinline__ constexpr float code_unscale(int j) {
                      : 16777216.f;
 }
 
+#ifndef KIVI_SPLIT_QD
+#define KIVI_SPLIT_QD 1
+#endif
 __device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
     const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
     return *reinterpret_cast<const uint32_t*>(&r);
@@ -340,7 +342,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
         for (int i = lane; i < Cfg::KH_N; i += 32) {
             const uint32_t h0 = *reinterpret_cast<const uint32_t*>(kt + (2 * i) * BB);
             const uint32_t h1 = *reinterpret_cast<const uint32_t*>(kt + (2 * i + 1) * BB);
-            kh[i] = make_header(h0, h1);
+            kh[(i & ~7) + (i & 3) * 2 + ((i >> 2) & 1)] = make_header(h0, h1);   // pairs (p, p+4) of a k-step side by side
         }
         for (int i = lane; i < Cfg::VH_N; i += 32) {
             const int blk = i >> 4, t = i & 15;        // pairs (t, t+16)
@@ -361,7 +363,7 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int cha = ks * 16 + 2 * qlane;
-            const Header ha = kh[cha >> 1], hb = kh[(cha >> 1) + 4];
+            const uint4 hab = *reinterpret_cast<const uint4*>(&kh[ks * 8 + 2 * qlane]);   // {d, m} of (cha, cha+1 | cha+8, cha+9)
             const uint8_t* pk = kt + cha * BB + 4 + PIECE * ((quad >> 1) + 4 * (quad & 1));
             uint32_t xa0 = load_piece<BITS>(pk), xa1 = load_piece<BITS>(pk + BB);
             uint32_t xb0 = load_piece<BITS>(pk + 8 * BB), xb1 = load_piece<BITS>(pk + 9 * BB);
@@ -370,9 +372,15 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                 xb0 |= xb1 << 16;
             }
             uint32_t a[4];
-            scale_split(qf[ks][0], qf[ks][1], ha.x, a[0], a[1]);
-            scale_split(qf[ks][2], qf[ks][3], hb.x, a[2], a[3]);
-            mma_f16_16816(cb, qf[ks], ha.y, hb.y);
+            if constexpr (KIVI_SPLIT_QD) {
+                scale_split(qf[ks][0], qf[ks][1], hab.x, a[0], a[1]);
+                scale_split(qf[ks][2], qf[ks][3], hab.z, a[2], a[3]);
+            } else {   // one F16 rounding of q*d: the same size of error as rounding a dequantised K element to F16
+                a[0] = hmul2_u(qf[ks][0], hab.x);
+                a[2] = hmul2_u(qf[ks][2], hab.z);
+                a[1] = a[3] = 0u;
+            }
+            mma_f16_16816(cb, qf[ks], hab.y, hab.w);
             uint32_t b0[4], b1[4];
             raw_codes<BITS>(xa0, xa1, b0);
             raw_codes<BITS>(xb0, xb1, b1);
@@ -435,14 +443,14 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
             const int ta = 4 * qlane + 2 * u;
             {
                 const int bq = quad < NB ? quad : 0;
-                const uint32_t ma = vh[bq * 16 + qlane * 4 + 2 * u].y, mb = vh[bq * 16 + qlane * 4 + 2 * u + 1].y;
-                const uint32_t am[4] = {quad < NB ? ma : 0u, 0u, quad < NB ? mb : 0u, 0u};
+                const uint4 mm = *reinterpret_cast<const uint4*>(&vh[bq * 16 + qlane * 4 + 2 * u]);
+                const uint32_t am[4] = {quad < NB ? mm.y : 0u, 0u, quad < NB ? mm.w : 0u, 0u};
                 mma_f16_16816(ob, am, pb0, pb1);
             }
 #pragma unroll
             for (int blk = 0; blk < NB; ++blk) {
-                const uint32_t da = vh[blk * 16 + qlane * 4 + 2 * u].x, db = vh[blk * 16 + qlane * 4 + 2 * u + 1].x;
-                const uint32_t pd0 = hmul2_u(pb0, da), pd1 = hmul2_u(pb1, db);
+                const uint4 dd = *reinterpret_cast<const uint4*>(&vh[blk * 16 + qlane * 4 + 2 * u]);
+                const uint32_t pd0 = hmul2_u(pb0, dd.x), pd1 = hmul2_u(pb1, dd.z);
                 const uint8_t* pv = vt + (ta * NB + blk) * BB + 4 + PIECE * quad;
                 uint32_t xa0 = load_piece<BITS>(pv), xa1 = load_piece<BITS>(pv + 16 * NB * BB);
                 uint32_t xb0 = load_piece<BITS>(pv + NB * BB), xb1 = load_piece<BITS>(pv + 17 * NB * BB);
@@ -509,8 +517,9 @@ static cudaError_t launch_kivi_t(const DecodeParams& p, const KiviBatch& bt, int
 int decode_kivi_ctas_per_sm(int head_dim, int bits) { return (head_dim == 128 && bits == 4) ? 3 : 2; }
 
 // CTA slots per SM the split planner fills: one resident wave where three CTAs fit (B=8 x 32K tokens, Q4: 3 -> 102 us,
-// 4 -> 111, 5 -> 113, 6 -> 107, 7 -> 106, 9 -> 111), one and a half where two fit.
-int decode_kivi_plan_slots_per_sm(int head_dim, int bits) { return 3; }
+// 4 -> 111, 5 -> 113, 6 -> 107, 7 -> 106, 9 -> 111), two waves where two fit (Q8: 2 -> 124, 3 -> 149, 4 -> 120, 5 -> 137,
+// 6 -> 127; Q2: 2 -> 113, 3 -> 139, 4 -> 110, 5 -> 128, 6 -> 117).
+int decode_kivi_plan_slots_per_sm(int head_dim, int bits) { return decode_kivi_ctas_per_sm(head_dim, bits) == 3 ? 3 : 4; }
 
 cudaError_t launch_decode_kivi(const DecodeParams& p, const KiviBatch& bt, int head_dim, int bits, int n_items,
                                cudaStream_t st) {

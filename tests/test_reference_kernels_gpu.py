@@ -115,3 +115,58 @@ def test_prefill_matches_reference_kernel(be, S, T):
     assert be.flash_attention_prefill(q, k, v, got, hq, hkv, S, T, d, cap, B, True)
     torch.cuda.synchronize()
     np.testing.assert_allclose(got.cpu().numpy(), want.cpu().numpy(), atol=2e-3, rtol=1e-2)
+
+
+def _median_us(fn, n=10):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+    for a, b in ev:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return sorted(a.elapsed_time(b) for a, b in ev)[n // 2] * 1e3
+
+
+def test_faster_than_the_reference_kernels_on_the_same_gpu(be, capsys):
+    """The reference's own CUDA kernels with the reference's launch shapes (engine/src/backend/cuda_pc.rs:1793-1800,
+    crates/techniques/kivi/src/gpu_kivi_cuda.rs:197-206) timed beside this library on the same inputs: the single short
+    decode (T=2048, D=64) and one KIVI Q4 sequence of 32 768 tokens. Prints the four times (run with -s to see them)."""
+    from argus_engine_b200.kivi_cache import KiviDeviceCache
+
+    hq, hkv, d, T = 32, 8, 64, 2048
+    case = wl.decode_case(0, [T], hq, hkv, d)
+    q, k, v = _dev(case.q[0]), _dev(case.k[0]), _dev(case.v[0])
+    o = torch.zeros(hq, d, device="cuda")
+    m = ref.RefModule("kernels.cubin")
+    ref_decode = _median_us(lambda: m.launch(
+        "attention_gen_f16kv_naive", (hq, 1, 1), (256, 1, 1), T * 4,
+        [ref.ptr(q), ref.ptr(k), ref.ptr(v), ref.ptr(o), C.c_int(hq), C.c_int(hkv), C.c_int(d), C.c_int(T), C.c_int(T),
+         C.c_void_p(0), C.c_int(0)]), 20)
+    our_decode = _median_us(lambda: be.attention_gen(q, k, v, o, hq, hkv, d, T), 20)
+
+    hq, hkv, d, T = 32, 8, 128, 32768
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    cache = KiviDeviceCache(be, hkv, d, T, 128, 4)
+    cache.update(torch.randn(T, hkv, d, device="cuda", generator=gen), torch.randn(T, hkv, d, device="cuda", generator=gen))
+    q = torch.randn(hq, d, device="cuda", generator=gen)
+    o_ref, o_our = torch.zeros(hq, d, device="cuda"), torch.zeros(hq, d, device="cuda")
+    s_ref = torch.zeros(hq, T, device="cuda")
+    scale = float(1 / np.sqrt(d))
+    mk = ref.RefModule("kivi_attn.cubin")
+    ref_kivi = _median_us(lambda: mk.launch(
+        "kernel_attn_gen_kivi_q4", (hq, 1, 1), (64, 1, 1), 256,
+        [ref.ptr(q), ref.ptr(cache.qk), ref.ptr(cache.qv), ref.ptr(cache.res_k), ref.ptr(cache.res_v), ref.ptr(o_ref),
+         ref.ptr(s_ref), C.c_int(hq), C.c_int(hkv), C.c_int(d), C.c_int(cache.q_tokens), C.c_int(cache.res_pos), C.c_int(128),
+         C.c_float(scale), C.c_int(T), C.c_int(1)]), 3)
+    seq = [cache.seq()]
+    our_kivi = _median_us(lambda: be.kivi_attention_batched(q[None], seq, o_our[None], hq, hkv, d, 128, 4, scale), 10)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(o_our.cpu().numpy(), o_ref.cpu().numpy(), atol=2e-3, rtol=1e-2)
+    with capsys.disabled():
+        print(f"\n[reference kernels on this GPU] decode T=2048 D=64: reference {ref_decode:.1f} us, library {our_decode:.1f} us | "
+              f"KIVI Q4 one sequence T=32768: reference {ref_kivi / 1e3:.2f} ms, library {our_kivi:.1f} us")
+    assert our_decode * 5 < ref_decode
+    assert our_kivi * 50 < ref_kivi
