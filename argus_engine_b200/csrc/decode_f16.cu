@@ -245,6 +245,28 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
 // loads of a head group are requested before the first is used (the kernel is a stream over the logits, and one load
 // in flight per thread leaves it bound by latency).
 template <int N>
+__device__ __forceinline__ void load_floats(const float* src, float (&x)[N]) {
+    if constexpr (N >= 4) {
+#pragma unroll
+        for (int i = 0; i < N; i += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            x[i] = v.x; x[i + 1] = v.y; x[i + 2] = v.z; x[i + 3] = v.w;
+        }
+    } else {
+        x[0] = *src;
+    }
+}
+template <int N>
+__device__ __forceinline__ void store_floats(float* dst, const float (&x)[N]) {
+    if constexpr (N >= 4) {
+#pragma unroll
+        for (int i = 0; i < N; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
+    } else {
+        *dst = x[0];
+    }
+}
+
+template <int N>
 __device__ __forceinline__ void finalize_tokens(const FinalizeParams& f, int b, int t, int kv0, int kv1, bool want_flat) {
     const float inv_g = 1.0f / (float)f.group;
     float flat[N];
@@ -252,69 +274,61 @@ __device__ __forceinline__ void finalize_tokens(const FinalizeParams& f, int b, 
     for (int i = 0; i < N; ++i) flat[i] = 0.f;
     for (int kv = kv0; kv < kv1; ++kv) {
         const int64_t h0 = (int64_t)b * f.hq + kv * f.group;
-        float x[kMaxGroup][N];
-#pragma unroll
-        for (int r = 0; r < kMaxGroup; ++r) {
-            if (r < f.group) {
-                const float* src = f.logits + (h0 + r) * f.logit_stride + t;
-                if constexpr (N == 4) {
-                    const float4 v = *reinterpret_cast<const float4*>(src);
-                    x[r][0] = v.x; x[r][1] = v.y; x[r][2] = v.z; x[r][3] = v.w;
-                } else {
-                    x[r][0] = *src;
-                }
-            }
-        }
         float gsum[N];
 #pragma unroll
         for (int i = 0; i < N; ++i) gsum[i] = 0.f;
+        for (int r0 = 0; r0 < f.group; r0 += 4) {   // four heads' loads in flight at a time (registers), r ascending
+            float x[4][N], lse4[4];
 #pragma unroll
-        for (int r = 0; r < kMaxGroup; ++r) {
-            if (r < f.group) {
-                const float lse = f.lse2[h0 + r];
-                float pr[N];
-#pragma unroll
-                for (int i = 0; i < N; ++i) {
-                    pr[i] = exp2f(x[r][i] - lse);
-                    gsum[i] += pr[i];
-                    flat[i] += pr[i];
+            for (int rr = 0; rr < 4; ++rr) {
+                const int r = r0 + rr;
+                if (r < f.group) {
+                    lse4[rr] = f.lse2[h0 + r];
+                    load_floats<N>(f.logits + (h0 + r) * f.logit_stride + t, x[rr]);
                 }
-                if (f.scores != nullptr) {
-                    float* dst = f.scores + (h0 + r) * f.score_stride + t;
-                    if constexpr (N == 4) *reinterpret_cast<float4*>(dst) = make_float4(pr[0], pr[1], pr[2], pr[3]);
-                    else *dst = pr[0];
+            }
+#pragma unroll
+            for (int rr = 0; rr < 4; ++rr) {
+                const int r = r0 + rr;
+                if (r < f.group) {
+                    const float lse = lse4[rr];
+                    float pr[N];
+#pragma unroll
+                    for (int i = 0; i < N; ++i) {
+                        pr[i] = exp2f(x[rr][i] - lse);
+                        gsum[i] += pr[i];
+                        if (want_flat) flat[i] += pr[i];
+                    }
+                    if (f.scores != nullptr) store_floats<N>(f.scores + (h0 + r) * f.score_stride + t, pr);
                 }
             }
         }
         if (f.head_scores != nullptr) {
-            float* dst = f.head_scores + ((int64_t)b * f.hkv + kv) * f.score_stride + t;
-            if constexpr (N == 4) *reinterpret_cast<float4*>(dst) = make_float4(gsum[0] * inv_g, gsum[1] * inv_g, gsum[2] * inv_g, gsum[3] * inv_g);
-            else *dst = gsum[0] * inv_g;
+#pragma unroll
+            for (int i = 0; i < N; ++i) gsum[i] *= inv_g;
+            store_floats<N>(f.head_scores + ((int64_t)b * f.hkv + kv) * f.score_stride + t, gsum);
         }
     }
-    if (want_flat) {
-        float* dst = f.flat_scores + (int64_t)b * f.score_stride + t;
-        if constexpr (N == 4) *reinterpret_cast<float4*>(dst) = make_float4(flat[0], flat[1], flat[2], flat[3]);
-        else *dst = flat[0];
-    }
+    if (want_flat) store_floats<N>(f.flat_scores + (int64_t)b * f.score_stride + t, flat);
 }
 
-// One thread per (sequence, four consecutive tokens) and - when no flat sum over all heads is wanted - per KV head
+// One thread per (sequence, TPT consecutive tokens) and - when no flat sum over all heads is wanted - per KV head
 // (gridDim.z = Hkv). 16-byte accesses where the rows allow them.
-__global__ void __launch_bounds__(256) finalize_scores_kernel(const __grid_constant__ FinalizeParams f) {
+template <int TPT>
+__global__ void __launch_bounds__(256, 4) finalize_scores_kernel(const __grid_constant__ FinalizeParams f) {
     const int b = blockIdx.y;
-    const int t = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int t = (blockIdx.x * blockDim.x + threadIdx.x) * TPT;
     const int T = f.seq_len[b];
     if (t >= T) return;
     const bool want_flat = f.flat_scores != nullptr;
     const int kv0 = gridDim.z > 1 ? blockIdx.z : 0, kv1 = gridDim.z > 1 ? kv0 + 1 : f.hkv;
-    const bool vec = ((f.logit_stride | f.score_stride) & 3) == 0 && t + 4 <= T &&
+    const bool vec = ((f.logit_stride | f.score_stride) & 3) == 0 && t + TPT <= T &&
                      ((reinterpret_cast<uintptr_t>(f.logits) | reinterpret_cast<uintptr_t>(f.scores) |
                        reinterpret_cast<uintptr_t>(f.head_scores) | reinterpret_cast<uintptr_t>(f.flat_scores)) & 15) == 0;
     if (vec) {
-        finalize_tokens<4>(f, b, t, kv0, kv1, want_flat);
+        finalize_tokens<TPT>(f, b, t, kv0, kv1, want_flat);
     } else {
-        for (int i = 0; i < 4 && t + i < T; ++i) finalize_tokens<1>(f, b, t + i, kv0, kv1, want_flat);
+        for (int i = 0; i < TPT && t + i < T; ++i) finalize_tokens<1>(f, b, t + i, kv0, kv1, want_flat);
     }
 }
 
@@ -347,7 +361,7 @@ cudaError_t launch_decode_f16(const DecodeParams& p, const DecodeBatch& bt, int 
 cudaError_t launch_finalize_scores(const FinalizeParams& f, int max_len, cudaStream_t st) {
     if (max_len <= 0) return cudaSuccess;
     dim3 grid(((max_len + 3) / 4 + 255) / 256, f.n_seqs, f.flat_scores == nullptr ? f.hkv : 1);
-    finalize_scores_kernel<<<grid, 256, 0, st>>>(f);
+    finalize_scores_kernel<4><<<grid, 256, 0, st>>>(f);
     return cudaGetLastError();
 }
 

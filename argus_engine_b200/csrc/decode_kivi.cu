@@ -1,5 +1,5 @@
 // Split-KV GQA decode attention over a KIVI-packed KV cache (Q2/Q4/Q8 blocks + full-precision residual
-// window), sm_100a, with dequantisation fused into the tile load.
+// window), sm_100a, reading the packed bytes once and never materialising a dequantised value.
 //
 // Stands behind CudaQuantAttnBackend::attention_gen_quant (crates/argus-extension-api/src/lib.rs:3087-3104;
 // the kernels it replaces are kernel_attn_gen_kivi_q{2,4,8}, crates/techniques/kivi/src/kivi_attn.cu:34,220,403).
@@ -12,11 +12,11 @@
 // Both the K and the V bytes of one (kv_head, 32-token group) are contiguous (D*block_bytes each), so a
 // warp tile is fetched with two bulk async copies (cp.async.bulk + mbarrier) and stays in the packed form
 // in shared memory. Lanes pull 4-token (resp. 4-channel) code pieces of the two channels (tokens) that one
-// MMA operand register pairs, widen them with the 0x6400 magic-number trick, apply {d, m} with one HFMA2,
-// and feed mma.sync. Tokens of a group are visited in a permuted order that makes those pieces contiguous;
-// softmax does not care and P·V uses the same order. The residual window is a separate split handled in
-// plain F32 FMA. Everything after the main loop (warp merge, split merge, score finalize) is shared with
-// the F16 kernel.
+// MMA operand register pairs and feed them to mma.sync as they are; the scales d and minima m are folded onto
+// the other operand (see "Scale folding" below). Tokens of a group are visited in a permuted order that makes
+// those pieces contiguous; softmax does not care and P·V uses the same order. The residual window is a
+// separate split handled in plain F32 FMA. Everything after the main loop (warp merge, split merge, score
+// finalize) is shared with the F16 kernel.
 
 #include "decode_epilogue.cuh"
 #include "context.h"
