@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(256, 4) finalize_scores_kernel(const __grid_co
     if (t >= T) return;
     const bool want_flat = f.flat_scores != nullptr;
     const int kv0 = gridDim.z > 1 ? blockIdx.z : 0, kv1 = gridDim.z > 1 ? kv0 + 1 : f.hkv;
-    const bool vec = ((f.logit_stride | f.score_stride) & 3) == 0 && t + TPT <= T &&
+    const bool vec = ((f.logit_stride | f.score_stride) & (TPT - 1)) == 0 && t + TPT <= T &&
                      ((reinterpret_cast<uintptr_t>(f.logits) | reinterpret_cast<uintptr_t>(f.scores) |
                        reinterpret_cast<uintptr_t>(f.head_scores) | reinterpret_cast<uintptr_t>(f.flat_scores)) & 15) == 0;
     if (vec) {
@@ -360,6 +360,7 @@ cudaError_t launch_decode_f16(const DecodeParams& p, const DecodeBatch& bt, int 
 
 cudaError_t launch_finalize_scores(const FinalizeParams& f, int max_len, cudaStream_t st) {
     if (max_len <= 0) return cudaSuccess;
+    // four tokens per thread (eight measured slower: 117 us against 115 us for the KIVI step with the H2O vector)
     dim3 grid(((max_len + 3) / 4 + 255) / 256, f.n_seqs, f.flat_scores == nullptr ? f.hkv : 1);
     finalize_scores_kernel<4><<<grid, 256, 0, st>>>(f);
     return cudaGetLastError();
