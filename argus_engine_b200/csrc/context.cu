@@ -160,9 +160,9 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
         // sequence-sharded form: one sequence, the (o, lse) partial goes to the peers from inside the kernel
         if (n_seqs != 1 || paged || want_scores || xc->n_ranks <= 0 || xc->n_ranks > kMaxRanks || xc->rank < 0 ||
             xc->rank >= xc->n_ranks || !xc->peer_lines || !xc->step_counters || (xc->phases & 3) == 0 ||
-            xc->parity_stride_lines < (int64_t)xc->n_ranks * hkv * xc_lines_per_head(g, d)) {
+            xc->parity_stride_lines < (int64_t)xc->n_ranks * hkv * xc_lines_per_head(g, d) || (xc->parity_stride_lines & 7)) {
             ctx->set_error("attention_gen_sharded: one contiguous sequence, no score outputs, 1..%d ranks and a parity stride "
-                           "of at least n_ranks*Hkv*lines_per_head lines are required", kMaxRanks);
+                           "of at least n_ranks*Hkv*lines_per_head units (a multiple of 8) are required", kMaxRanks);
             return ARGUS_B200_E_INVALID;
         }
         if (xc_smem_end(xc->n_ranks, g, d) > (size_t)decode_f16_smem_bytes(d)) {
@@ -171,8 +171,8 @@ int decode_f16_entry(Context* ctx, cudaStream_t st, const float* q, const argus_
             return ARGUS_B200_E_UNSUPPORTED;
         }
         for (int s = 0; s < xc->n_ranks; ++s)
-            if (!xc->peer_lines[s] || (reinterpret_cast<uintptr_t>(xc->peer_lines[s]) & 15)) {
-                ctx->set_error("attention_gen_sharded: receive buffer of rank %d is null or not 16-byte aligned", s);
+            if (!xc->peer_lines[s] || (reinterpret_cast<uintptr_t>(xc->peer_lines[s]) & 127)) {
+                ctx->set_error("attention_gen_sharded: receive buffer of rank %d is null or not 128-byte aligned", s);
                 return ARGUS_B200_E_INVALID;
             }
     }

@@ -27,34 +27,45 @@ __device__ unsigned long long g_xc_prof[64 * 8];
 #endif
 
 // ───────── sequence-sharded decode: exchange of the (o, lse) rows of one KV head's query heads ─────────
-// Every 16-byte line that crosses NVLink carries its own arrival flags: {float a, int step, float b, int step}. A peer
-// store of 8 aligned bytes becomes visible as a whole, so a reader that finds `step` in both flag words of a line has
-// both floats, with no fence on either side and no separate flag traffic: the latency of an exchange is one store
-// plus one NVLink crossing (measured on two B200s: about 5 us for the whole tail, against 33 us for "store rows,
-// fence at system scope, store flags, poll flags, read rows"). Flags are step numbers, so nothing is ever cleared: a
-// line of the buffer set that step n uses last held step n-2.
+// Every 128-byte line that crosses NVLink carries its own arrival flag: 30 data words, then the step number twice.
+// A line is written by ONE warp-wide store instruction - eight consecutive lanes store 16 bytes each, which the
+// load/store unit turns into one aligned 128-byte write that stays whole on NVLink - and read the same way, so a
+// reader that finds `step` in both flag words has the 30 data words of the same write (the property NCCL's LL128
+// protocol is built on), with no fence on either side and no separate flag traffic. Flags are step numbers, so
+// nothing is ever cleared: a line of the buffer set that step n uses last held step n-2.
+// The first form used 16-byte lines {float, step, float, step}: correct by the 8-byte store guarantee alone, but at
+// eight ranks 28 900 sixteen-byte writes per rank and step made the tail last 14-16 us (4128 writes at two ranks:
+// 5-8 us); a 128-byte line moves 15 times the data per write.
 //
-// The head group's data is the float sequence [g rows of D outputs | g natural-log lse values] = g*(D+1) floats,
-// two per line. Rank r's receive buffer holds, per buffer set, [n_ranks][Hkv][lines_per_head] lines.
-__host__ __device__ constexpr int xc_lines_per_head(int g, int d) { return (g * (d + 1) + 1) / 2; }
+// The head group's data is the float sequence [g rows of D outputs | g natural-log lse values] = g*(D+1) floats, 30
+// per line; a warp store covers four lines, so the line count is rounded up to a multiple of four. Rank r's receive
+// buffer holds, per buffer set, [n_ranks][Hkv][lines_per_head] units of 16 bytes (8 per line), 128-byte aligned.
+constexpr int kXcLineWords = 30;
+__host__ __device__ constexpr int xc_lines128(int g, int d) { return ((g * (d + 1) + kXcLineWords - 1) / kXcLineWords + 3) & ~3; }
+__host__ __device__ constexpr int xc_lines_per_head(int g, int d) { return 8 * xc_lines128(g, d); }
 // floats between two ranks' slots in the shared-memory region (a multiple of 4: the rows are written as float4)
 __host__ __device__ constexpr int xc_slot_floats(int g, int d) { return (g * (d + 1) + 3) & ~3; }
 
 // Push: `stage` holds this CTA's g*(D+1) floats (shared or global memory); they go to slot `rank` of every other rank.
+// Work unit = (peer, four lines); the warps of the CTA take the units in turn.
 template <int NT>
 __device__ __forceinline__ void xc_push(const PeerExchange& x, const float* stage, int kv, int hkv, int g, int d, int step,
                                         long long poff) {
-    const int nf = g * (d + 1), lph = xc_lines_per_head(g, d);
-    for (int s = 0; s < x.n_ranks; ++s) {
-        if (s == x.rank) continue;
-        int4* dst = static_cast<int4*>(x.lines[s]) + poff + ((long long)x.rank * hkv + kv) * lph;
-        for (int i = threadIdx.x; i < lph; i += NT) {
-            const float a = stage[2 * i], b = (2 * i + 1 < nf) ? stage[2 * i + 1] : 0.f;
-            // volatile: one 16-byte store, not to be split, merged or deferred by the compiler
-            asm volatile("st.volatile.global.v4.s32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "r"(__float_as_int(a)), "r"(step),
-                         "r"(__float_as_int(b)), "r"(step)
-                         : "memory");
+    const int nf = g * (d + 1), lph = xc_lines_per_head(g, d), quads = xc_lines128(g, d) / 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 7;
+    for (int unit = warp; unit < (x.n_ranks - 1) * quads; unit += NT / 32) {
+        const int sp = unit / quads, line = (unit - sp * quads) * 4 + (lane >> 3);
+        const int s = sp + (sp >= x.rank ? 1 : 0);
+        int w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int word = 4 * sub + k, idx = line * kXcLineWords + word;
+            w[k] = word >= kXcLineWords ? step : (idx < nf ? __float_as_int(stage[idx]) : 0);
         }
+        int4* dst = static_cast<int4*>(x.lines[s]) + poff + ((long long)x.rank * hkv + kv) * lph + line * 8 + sub;
+        // volatile: one 16-byte store per lane, not to be split, merged or deferred by the compiler
+        asm volatile("st.volatile.global.v4.s32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                     : "memory");
     }
 }
 
@@ -65,44 +76,54 @@ __device__ __forceinline__ void xc_push(const PeerExchange& x, const float* stag
 template <int NT>
 __device__ __forceinline__ bool xc_wait_merge(const PeerExchange& x, float* rows, int* ok_flag, int kv, int hq, int hkv, int g,
                                               int d, int step, long long poff, float* out, float* merged_lse) {
-    const int nf = g * (d + 1), nfp = xc_slot_floats(g, d), lph = xc_lines_per_head(g, d), h0 = kv * g;
+    const int nf = g * (d + 1), nfp = xc_slot_floats(g, d), lph = xc_lines_per_head(g, d), quads = xc_lines128(g, d) / 4;
+    const int h0 = kv * g, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 7;
     if (threadIdx.x == 0) *ok_flag = 1;
     __syncthreads();
-    // All (peer, line) pairs of this head are spread over the threads, kXcLoads loads in flight per thread: the lines are
-    // independent, and one dependent round trip per line and per peer made the wait grow by 2.6 us per rank.
-    constexpr int kXcLoads = 8;
-    const int4* base = static_cast<const int4*>(x.lines[x.rank]) + poff + (long long)kv * lph;
-    const int total = (x.n_ranks - 1) * lph;
+    // Work unit = (peer, four lines) = one warp-wide 16-byte load; kXcLoads units in flight per warp, the lines being
+    // independent (one dependent round trip per line and per peer made the wait grow with the number of ranks).
+    constexpr int kXcLoads = 4;
+    const int4* base = static_cast<const int4*>(x.lines[x.rank]) + poff + (long long)kv * lph + lane;
+    const int total = (x.n_ranks - 1) * quads;
     auto load_line = [](const int4* ptr) {
         int4 v;
         asm volatile("ld.volatile.global.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr) : "memory");
         return v;
     };
-    for (int first = threadIdx.x; first < total; first += NT * kXcLoads) {
+    auto arrived = [&](const int4& v) {   // lane 8j+7 holds the two flag words of line j of the quad
+        return __all_sync(0xffffffffu, sub != 7 || (v.z == step && v.w == step));
+    };
+    for (int first = warp; first < total; first += (NT / 32) * kXcLoads) {
         int4 v[kXcLoads];
         const int4* src[kXcLoads];
         int slot[kXcLoads], line[kXcLoads];
 #pragma unroll
         for (int u = 0; u < kXcLoads; ++u) {
-            const int idx = first + u * NT;
-            const int sp = idx < total ? idx / lph : 0;
+            const int unit = first + u * (NT / 32);
+            const int sp = unit < total ? unit / quads : 0;
             slot[u] = sp + (sp >= x.rank ? 1 : 0);
-            line[u] = idx < total ? idx - sp * lph : -1;
-            src[u] = base + (long long)slot[u] * hkv * lph + (line[u] < 0 ? 0 : line[u]);
+            line[u] = unit < total ? (unit - sp * quads) * 4 + (lane >> 3) : -1;
+            src[u] = base + (long long)slot[u] * hkv * lph + (unit < total ? (unit - sp * quads) * 32 : 0);
             if (line[u] >= 0) v[u] = load_line(src[u]);
         }
 #pragma unroll
         for (int u = 0; u < kXcLoads; ++u) {
-            if (line[u] < 0) continue;
-            bool ok = v[u].y == step && v[u].w == step;
-            for (int it = 0; !ok && it < (1 << 20); ++it) {   // about a second before giving up
+            if (line[u] < 0) continue;   // uniform across the warp
+            bool ok = arrived(v[u]);
+            // about a second before giving up; once a line of this head has been given up, the others get one more look
+            const int limit = *reinterpret_cast<volatile int*>(ok_flag) != 0 ? (1 << 20) : 1;
+            for (int it = 0; !ok && it < limit; ++it) {
                 if (it > 256) __nanosleep(it > 4096 ? 1000 : 100);
                 v[u] = load_line(src[u]);
-                ok = v[u].y == step && v[u].w == step;
+                ok = arrived(v[u]);
             }
             if (!ok) *ok_flag = 0;
-            rows[slot[u] * nfp + 2 * line[u]] = __int_as_float(v[u].x);
-            if (2 * line[u] + 1 < nf) rows[slot[u] * nfp + 2 * line[u] + 1] = __int_as_float(v[u].z);
+            const int w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int word = 4 * sub + k, idx = line[u] * kXcLineWords + word;
+                if (word < kXcLineWords && idx < nf) rows[slot[u] * nfp + idx] = __int_as_float(w4[k]);
+            }
         }
     }
     __syncthreads();

@@ -75,8 +75,8 @@ class ShardedDecoder:
 
 class PeerBuffers:
     """Receive buffers of the in-kernel exchange, in memory every rank of the node can address (torch symmetric memory
-    over NVLink). Per rank: two sets (even / odd steps) of [N][Hkv][lines_per_head] 16-byte lines {float, step, float,
-    step}, zero-initialised; see argus_b200_attention_gen_sharded in the C header."""
+    over NVLink). Per rank: two sets (even / odd steps) of [N][Hkv][lines_per_head] 16-byte units (128-byte lines of 30
+    data words and the step number twice), zero-initialised; see argus_b200_attention_gen_sharded in the C header."""
 
     def __init__(self, be, num_heads_q: int, num_heads_kv: int, head_dim: int, group=None):
         import torch.distributed._symmetric_memory as symm_mem

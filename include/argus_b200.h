@@ -333,11 +333,14 @@ ARGUS_B200_API int argus_b200_lse_merge(argus_b200_ctx* ctx, void* stream, const
  * ranks' rows of those heads from its OWN receive buffer and writes the merged rows to `out` [Hq][D] (and `merged_lse`
  * [Hq] if set).
  *
- * Wire format: 16-byte lines {float a, int step, float b, int step}. An aligned 8-byte peer store becomes visible as a
- * whole, so a reader that finds the current step number in both flag words of a line has both floats: no fence, no
- * separate flag traffic, latency of one store plus one NVLink crossing. A head group's g*(D+1) floats ([g][D] outputs,
- * then [g] lse) take lines_per_head = ceil(g*(D+1)/2) lines; a receive buffer is two sets (even / odd steps,
- * `parity_stride_lines` lines apart) of [n_ranks][Hkv][lines_per_head] lines, zero-initialised once (steps start at 1).
+ * Wire format: 128-byte lines of 30 data words followed by the step number twice. A line is written by one warp-wide
+ * store (eight lanes x 16 bytes, one aligned 128-byte NVLink write) and read the same way, so a reader that finds the
+ * current step number in both flag words has the data of the same write: no fence, no separate flag traffic, latency
+ * of one store plus one NVLink crossing. A head group's g*(D+1) floats ([g][D] outputs, then [g] lse) take
+ * ceil(g*(D+1)/30) lines, rounded up to a multiple of four; buffer sizes are counted in UNITS OF 16 BYTES:
+ * lines_per_head = 8 x that line count (argus_b200_exchange_lines_per_head). A receive buffer is 128-byte aligned and
+ * holds two sets (even / odd steps, `parity_stride_lines` units apart, a multiple of 8) of
+ * [n_ranks][Hkv][lines_per_head] units, zero-initialised once (steps start at 1).
  * peer_lines[s] is the address, valid on this GPU, of rank s's receive buffer (e.g. a torch symmetric-memory
  * allocation). The step number lives in device memory: `step_counters` is an int[Hkv] array of this rank,
  * zero-initialised once and bumped by the kernel itself (one counter per KV head), so the call replays from a CUDA
@@ -360,7 +363,7 @@ ARGUS_B200_API int argus_b200_attention_gen_sharded(argus_b200_ctx* ctx, void* s
                                                     const void* v_shard, float* out, int num_heads_q, int num_heads_kv,
                                                     int head_dim, int64_t shard_len, int kv_dtype, int64_t head_stride,
                                                     int64_t pos_stride, const argus_b200_exchange* exchange);
-/* Lines one head group occupies in a receive buffer (see above). */
+/* 16-byte units one head group occupies in a receive buffer (see above). */
 ARGUS_B200_API int argus_b200_exchange_lines_per_head(int num_heads_q, int num_heads_kv, int head_dim);
 /* The receiving half alone: one CTA per KV head waits (bounded) for the other ranks' lines of step `step` in this rank's
  * receive buffer and merges them with `own_part` ([Hq][D] outputs then [Hq] lse, as argus_b200_attention_gen with

@@ -232,6 +232,38 @@ def test_batched_kivi_q4_h2o_reduced(be, res_f16):
 
 
 @pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("d,g", [(128, 4), (64, 8)])
+def test_degenerate_blocks_through_the_folded_scales(be, bits, d, g):
+    """Blocks whose scale or minimum is special - constant channels and tokens (d == 0), all-zero blocks, a range that
+    underflows F16 (d stored as 0), large offsets with a small range (|m| >> d), a strongly scaled query - go through
+    q*d / p*d and the bias MMAs like any other block and still match the oracle."""
+    hkv, T = 2, 128 * 3 + 40
+    src = wl.kivi_source(77 + bits, [T], hkv * g, hkv, d, 128, bits)
+    k, v = src.k[0], src.v[0]
+    rng = np.random.default_rng(3)
+    k[:, 0, 0] = 3.25                                   # constant K channel: every block has d == 0
+    k[:, 0, 1] = 0.0                                    # all-zero channel
+    k[:, 0, 2] = rng.standard_normal(T) * 1e-30         # range far below the smallest F16 scale
+    k[:, 0, 3] = 100.0 + rng.standard_normal(T) * 0.01  # |m| >> d
+    k[:, 1, 5] = -50.0 + rng.standard_normal(T)
+    v[7, :, :] = 1.0                                    # constant V token
+    v[8, :, :] = 0.0
+    v[:, 1, 32:64] = 200.0 + rng.standard_normal((T, 32)).astype(np.float32) * 0.05
+    v[9, 0, :32] = np.arange(32) * 0.5                  # .5 ties along a V block
+    src.q[0] *= 4.0
+    case = pack_with_oracle(src)
+    want, want_p = _oracle_kivi(case, 0, scores=True)
+    out = torch.full((case.hq, d), float("nan"), device="cuda")
+    sc = torch.full((case.hq, T), -1.0)
+    rc = be.attention_gen_quant(_dev(case.q[0]), _dev(case.qk[0]), _dev(case.qv[0]), _dev(case.res_k[0]), _dev(case.res_v[0]),
+                                out, case.hq, hkv, d, case.q_tokens[0], case.res_tokens[0], 128, 1.0 / np.sqrt(d), bits,
+                                scores_out=sc)
+    assert rc == 0 and be.check_status() == 0
+    np.testing.assert_allclose(out.cpu().numpy(), want, atol=OUT_ATOL, rtol=OUT_RTOL)
+    np.testing.assert_allclose(sc.numpy(), want_p, atol=P_ATOL, rtol=P_RTOL)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
 def test_paged_kivi_matches_contiguous_and_oracle(be, bits):
     """Flushes of three sequences scattered over one page pool (a page = one flush of all KV heads, in shuffled order
     with unused pages between): outputs and score vectors are bit-identical to the contiguous call, which is checked

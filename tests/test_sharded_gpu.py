@@ -43,7 +43,7 @@ def test_virtual_ranks_match_unsharded_oracle(T, N):
 
 
 def _line_buffers(be, n_ranks, hq, hkv, d):
-    """One receive buffer per (virtual) rank: two sets of [n_ranks][Hkv][lines_per_head] 16-byte lines, zeroed."""
+    """One receive buffer per (virtual) rank: two sets of [n_ranks][Hkv][lines_per_head] 16-byte units, zeroed."""
     lph = be.exchange_lines_per_head(hq, hkv, d)
     stride = n_ranks * hkv * lph
     bufs = [torch.zeros(2 * stride * 4, dtype=torch.int32, device="cuda") for _ in range(n_ranks)]
@@ -53,7 +53,7 @@ def _line_buffers(be, n_ranks, hq, hkv, d):
 @pytest.mark.parametrize("T,N,hq", [(20000, 4, 64), (300, 8, 64), (3, 2, 64), (5000, 3, 8)])
 def test_decode_with_in_kernel_push_virtual_ranks(T, N, hq):
     """The single-launch sharded step with all ranks' buffers on one GPU. Every virtual rank runs the decode kernel over
-    its slice with the peer push in its epilogue (phase 1: the head groups' rows travel as flagged 16-byte lines into
+    its slice with the peer push in its epilogue (phase 1: the head groups' rows travel as flagged 128-byte lines into
     slot r of every rank's receive buffer, the step counters are bumped on the device); then every rank collects and
     merges with the stand-alone kernel (phase 2), so no kernel waits for a later launch. Three steps use both buffer
     sets and reuse one. hq = 8 gives one query head per KV head (an odd number of floats per head group). Against the
