@@ -301,7 +301,7 @@ def headline_c5(be, dist, world, rank, args, peaks, sampler):
             sys.stderr.write(f"[bench] peer buffers unavailable ({e}); using the NCCL gather\n")
             fused = False
             dec = make_gpu_decoder(be, k, v, n_local, hq, hkv, d)
-        exchange = ("flagged 16-byte lines pushed to the peers, collected and merged in the decode kernel's epilogue "
+        exchange = ("flagged 128-byte lines pushed to the peers, collected and merged in the decode kernel's epilogue "
                     "(one launch per step)" if fused else "decode kernel, NCCL all-gather, merge kernel")
         step = lambda: dec.step(q, out)   # noqa: E731
     else:
