@@ -23,6 +23,16 @@
 
 namespace argus {
 
+// Optional phase stamps (compiled in with -DARGUS_XC_PROFILE only): min / max over the CTAs of a launch of the
+// globaltimer at CTA entry, first tile ready, end of the tile loop and end of the epilogue.
+#ifdef ARGUS_XC_PROFILE
+__device__ unsigned long long g_phase_prof[8];
+#define PH_STAMP(i) { if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+    atomicMin(&g_phase_prof[2 * (i)], t_); atomicMax(&g_phase_prof[2 * (i) + 1], t_); } }
+#else
+#define PH_STAMP(i)
+#endif
+
 template <int D, int WARPS, int STAGES>
 struct DecodeF16Cfg {
     static constexpr int WT = 16;                 // tokens per warp tile
@@ -47,6 +57,7 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int quad = lane >> 2, qlane = lane & 3;
+    PH_STAMP(0)
 
     // ── which item ──
     const int kv = blockIdx.x % p.hkv;
@@ -153,6 +164,9 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
     for (int j = 0; j < my_tiles; ++j) {
         cp_async_wait<STAGES - 2>();
         __syncwarp();
+#ifdef ARGUS_XC_PROFILE
+        if (j == 0) PH_STAMP(1)
+#endif
         {
             const int jn = j + STAGES - 1;
             if (jn < my_tiles) issue(jn, jn % STAGES, page_next);
@@ -235,8 +249,10 @@ decode_f16_kernel(const __grid_constant__ DecodeParams p, const __grid_constant_
     }
     if (qlane == 0) sm_ml[warp * 8 + quad] = make_float2(m_run, l_run);
     __syncthreads();
+    PH_STAMP(2)
 
     decode_epilogue<D, WARPS>(smem, p, b, kv, (int64_t)gs * p.hkv + kv, (int64_t)bt.item_start[b] * p.hkv + kv, n_splits);
+    PH_STAMP(3)
 }
 
 // p_t = exp2(logit_t - lse2) per query head, plus the GQA reductions of the score policy
@@ -369,6 +385,14 @@ cudaError_t launch_finalize_scores(const FinalizeParams& f, int max_len, cudaStr
 #ifdef ARGUS_XC_PROFILE
 extern "C" __attribute__((visibility("default"))) int argus_b200_debug_xc_profile(unsigned long long* host_out) {
     return (int)cudaMemcpyFromSymbol(host_out, g_xc_prof, sizeof(g_xc_prof));
+}
+// reads the phase stamps {min, max} x {entry, first tile, loop end, epilogue end} and re-arms them for the next launch
+extern "C" __attribute__((visibility("default"))) int argus_b200_debug_phase_profile(unsigned long long* host_out) {
+    cudaError_t e = cudaMemcpyFromSymbol(host_out, g_phase_prof, sizeof(g_phase_prof));
+    unsigned long long init[8];
+    for (int i = 0; i < 8; ++i) init[i] = (i & 1) ? 0ull : ~0ull;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_phase_prof, init, sizeof(init));
+    return (int)e;
 }
 #endif
 

@@ -1,6 +1,7 @@
-"""Where a sequence-sharded decode step spends its time, per rank: the whole launch (CUDA events) and, per KV head, the
+"""Where a sequence-sharded decode step spends its time, per rank: the whole launch (CUDA events), per KV head the
 three globaltimer stamps of the exchange in the decode kernel's epilogue - tail start (the head's last split has merged
-locally), rows pushed to every peer, peers' rows collected and merged.
+locally), rows pushed to every peer, peers' rows collected and merged - and, over the CTAs of one launch, the earliest
+and latest first-tile arrival, end of the tile loop and end of the epilogue.
 
 Needs the time-stamped twin of the library (`python -m argus_engine_b200.build --stamped`, never the default build) and
 one process per GPU:
@@ -69,6 +70,14 @@ def main() -> int:
     e1.record()
     torch.cuda.synchronize()
     step_us = e0.elapsed_time(e1) * 1e3 / args.replays
+    ph = (C.c_ulonglong * 8)()
+    lib.argus_b200_debug_phase_profile(ph)   # re-arm the min / max phase stamps, then one more replay
+    dist.barrier()
+    graph.replay()
+    torch.cuda.synchronize()
+    lib.argus_b200_debug_phase_profile(ph)
+    pv = np.array(list(ph), dtype=np.float64)
+    pv = (pv - pv[0]) / 1e3   # us after the first CTA's entry: [entry min,max | first tile min,max | loop end min,max | epilogue end min,max]
     buf = (C.c_ulonglong * 512)()
     lib.argus_b200_debug_xc_profile(buf)   # stamps of the last replay, ns of this GPU's globaltimer
     a = np.array(list(buf), dtype=np.int64).reshape(64, 8)[:hkv, :3]
@@ -76,18 +85,23 @@ def main() -> int:
             "pushed_after_tail_us": ((a[:, 1] - a[:, 0]) / 1e3).tolist(),
             "merged_after_tail_us": ((a[:, 2] - a[:, 0]) / 1e3).tolist(),
             "tail_spread_us": float((a[:, 0].max() - a[:, 0].min()) / 1e3),
-            "first_tail_to_last_merge_us": float((a[:, 2].max() - a[:, 0].min()) / 1e3)}
+            "first_tail_to_last_merge_us": float((a[:, 2].max() - a[:, 0].min()) / 1e3),
+            "phases_us": pv.tolist()}
     rows = [None] * world
     dist.all_gather_object(rows, mine)
     if rank == 0:
         print(f"sharded decode, {args.tokens} tokens over {world} GPUs, {args.replays} graph replays")
         print("rank  step us  status  pushed-after-tail us (min..max over KV heads)  merged-after-tail us (min..max)  "
               "tail spread us  first tail -> last merge us")
-        for r in rows:
+        for r in (rows if world > 1 else []):   # one rank has no exchange: its step is the decode kernel + the merge kernel
             p_, m_ = r["pushed_after_tail_us"], r["merged_after_tail_us"]
             print(f"{r['rank']:4d}  {r['step_us']:7.1f}  {r['status']:6d}  {min(p_):6.2f} .. {max(p_):6.2f}"
                   f"{'':24s}{min(m_):6.2f} .. {max(m_):6.2f}{'':9s}{r['tail_spread_us']:8.2f}  "
                   f"{r['first_tail_to_last_merge_us']:8.2f}")
+        print("rank  first tile ready us (earliest..latest CTA)  tile loop ends us  epilogue ends us   (after the first CTA's entry)")
+        for r in rows:
+            p_ = r["phases_us"]
+            print(f"{r['rank']:4d}  {p_[2]:6.1f} .. {p_[3]:6.1f}{'':22s}{p_[4]:6.1f} .. {p_[5]:6.1f}   {p_[6]:6.1f} .. {p_[7]:6.1f}")
         print(f"max over ranks: step {max(r['step_us'] for r in rows):.1f} us; "
               f"merged-after-tail {max(max(r['merged_after_tail_us']) for r in rows):.2f} us")
     dist.barrier()
