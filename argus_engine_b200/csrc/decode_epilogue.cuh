@@ -81,9 +81,11 @@ __device__ __forceinline__ bool xc_wait_merge(const PeerExchange& x, float* rows
     if (threadIdx.x == 0) *ok_flag = 1;
     __syncthreads();
     // Work unit = (peer, four lines) = one warp-wide 16-byte load; kXcLoads units in flight per warp, the lines being
-    // independent: at eight ranks the 63 units of a head are requested in one go (four at a time cost 3-4 us of
-    // dependent round trips, one per line and peer 18-22 us).
-    constexpr int kXcLoads = 16;
+    // independent (one dependent round trip per line and per peer made the wait grow with the number of ranks).
+    // Four at a time is the measured optimum at eight ranks (106 us per step): sixteen at a time, with or without a
+    // joint retry of everything still pending, gave 108-115 us - the first requests go out before the peers' lines
+    // can have arrived and each of them pays another round trip.
+    constexpr int kXcLoads = 4;
     const int4* base = static_cast<const int4*>(x.lines[x.rank]) + poff + (long long)kv * lph + lane;
     const int total = (x.n_ranks - 1) * quads;
     auto load_line = [](const int4* ptr) {
@@ -94,34 +96,36 @@ __device__ __forceinline__ bool xc_wait_merge(const PeerExchange& x, float* rows
     auto arrived = [&](const int4& v) {   // lane 8j+7 holds the two flag words of line j of the quad
         return __all_sync(0xffffffffu, sub != 7 || (v.z == step && v.w == step));
     };
-    auto slot_of = [&](int unit) { const int sp = unit / quads; return sp + (sp >= x.rank ? 1 : 0); };
-    auto addr_of = [&](int unit) { return base + (long long)slot_of(unit) * hkv * lph + (unit % quads) * 32; };
     for (int first = warp; first < total; first += (NT / 32) * kXcLoads) {
         int4 v[kXcLoads];
+        const int4* src[kXcLoads];
+        int slot[kXcLoads], line[kXcLoads];
 #pragma unroll
         for (int u = 0; u < kXcLoads; ++u) {
             const int unit = first + u * (NT / 32);
-            if (unit < total) v[u] = load_line(addr_of(unit));
+            const int sp = unit < total ? unit / quads : 0;
+            slot[u] = sp + (sp >= x.rank ? 1 : 0);
+            line[u] = unit < total ? (unit - sp * quads) * 4 + (lane >> 3) : -1;
+            src[u] = base + (long long)slot[u] * hkv * lph + (unit < total ? (unit - sp * quads) * 32 : 0);
+            if (line[u] >= 0) v[u] = load_line(src[u]);
         }
 #pragma unroll
         for (int u = 0; u < kXcLoads; ++u) {
-            const int unit = first + u * (NT / 32);
-            if (unit >= total) continue;   // uniform across the warp
+            if (line[u] < 0) continue;   // uniform across the warp
             bool ok = arrived(v[u]);
             // about a second before giving up; once a line of this head has been given up, the others get one more look
             const int limit = *reinterpret_cast<volatile int*>(ok_flag) != 0 ? (1 << 20) : 1;
             for (int it = 0; !ok && it < limit; ++it) {
                 if (it > 256) __nanosleep(it > 4096 ? 1000 : 100);
-                v[u] = load_line(addr_of(unit));
+                v[u] = load_line(src[u]);
                 ok = arrived(v[u]);
             }
             if (!ok) *ok_flag = 0;
-            const int slot = slot_of(unit), line = (unit % quads) * 4 + (lane >> 3);
             const int w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int word = 4 * sub + k, idx = line * kXcLineWords + word;
-                if (word < kXcLineWords && idx < nf) rows[slot * nfp + idx] = __int_as_float(w4[k]);
+                const int word = 4 * sub + k, idx = line[u] * kXcLineWords + word;
+                if (word < kXcLineWords && idx < nf) rows[slot[u] * nfp + idx] = __int_as_float(w4[k]);
             }
         }
     }
