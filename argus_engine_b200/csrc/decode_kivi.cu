@@ -74,9 +74,6 @@ __device__ __forceinline__ constexpr float code_unscale(int j) {
                      : 16777216.f;
 }
 
-#ifndef KIVI_SPLIT_QD
-#define KIVI_SPLIT_QD 1
-#endif
 __device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
     const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
     return *reinterpret_cast<const uint32_t*>(&r);
@@ -372,14 +369,9 @@ decode_kivi_kernel(const __grid_constant__ DecodeParams p, const __grid_constant
                 xb0 |= xb1 << 16;
             }
             uint32_t a[4];
-            if constexpr (KIVI_SPLIT_QD) {
-                scale_split(qf[ks][0], qf[ks][1], hab.x, a[0], a[1]);
-                scale_split(qf[ks][2], qf[ks][3], hab.z, a[2], a[3]);
-            } else {   // one F16 rounding of q*d: the same size of error as rounding a dequantised K element to F16
-                a[0] = hmul2_u(qf[ks][0], hab.x);
-                a[2] = hmul2_u(qf[ks][2], hab.z);
-                a[1] = a[3] = 0u;
-            }
+            // value and remainder of q*d: dropping the remainder rows was measured (-2 us of 103) and not taken
+            scale_split(qf[ks][0], qf[ks][1], hab.x, a[0], a[1]);
+            scale_split(qf[ks][2], qf[ks][3], hab.z, a[2], a[3]);
             mma_f16_16816(cb, qf[ks], hab.y, hab.w);
             uint32_t b0[4], b1[4];
             raw_codes<BITS>(xa0, xa1, b0);
