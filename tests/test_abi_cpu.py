@@ -77,3 +77,17 @@ def test_ctypes_offsets_match_the_guards_of_the_header_and_crate():
     sr = _lib.ScoreReduceArgs
     assert (sr.decay_factor.offset, sr.n_layers.offset, sr.layer_flat_importance.offset) == (32, 40, 88)
     assert C.sizeof(_lib.ExchangeC) == 48 and _lib.ExchangeC.n_ranks.offset == 32
+
+
+def test_exchange_buffer_units_cover_the_head_group_in_whole_lines():
+    """argus_b200_exchange_lines_per_head (host-only, no GPU): 16-byte units of a head group's receive slot. The wire
+    format is 128-byte lines of 30 data words + 2 flag words, four lines per warp store, so the count is a multiple of
+    32 units and holds g*(D+1) floats."""
+    from argus_engine_b200 import load_library
+
+    lib = load_library()
+    for hq, hkv, d in [(64, 8, 128), (32, 8, 128), (8, 8, 128), (32, 8, 64), (16, 2, 64)]:
+        units = lib.argus_b200_exchange_lines_per_head(hq, hkv, d)
+        g = hq // hkv
+        lines = units // 8
+        assert units % 32 == 0 and lines * 30 >= g * (d + 1) and (lines - 4) * 30 < g * (d + 1)
